@@ -1,0 +1,134 @@
+// Shared host/device helpers for the sm_100a operator library.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <atomic>
+#include "../../include/c_runtime_api.h"
+
+namespace tf {
+
+// ---- error reporting (never abort; entry points return -1) -----------------
+void set_error(const char* fmt, ...);
+#define TF_FAIL(...) do { ::tf::set_error(__VA_ARGS__); return -1; } while (0)
+#define TF_REQUIRE(cond, ...) do { if (!(cond)) TF_FAIL(__VA_ARGS__); } while (0)
+#define TF_CUDA(expr) do { cudaError_t _e = (expr); if (_e != cudaSuccess) \
+    TF_FAIL("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); } while (0)
+
+// ---- launch accounting -------------------------------------------------------
+extern std::atomic<long long> g_launches;
+extern bool g_sync_every_op;          // TINYFLOW_SYNC=1
+extern int g_num_sms;                 // streaming multiprocessors of the current device
+int device_sm_count();
+
+// Post-launch hook: counts the launch, surfaces launch errors, optional sync.
+int after_launch(cudaStream_t s, const char* what, int nkernels = 1);
+#define TF_AFTER(s, what) do { if (::tf::after_launch((s), (what)) != 0) return -1; } while (0)
+
+// ---- streams ------------------------------------------------------------------
+// The caller's cell holds a cudaStream_t.  A null cell means the legacy default stream.
+inline cudaStream_t stream_of(void** cell) { return cell ? (cudaStream_t)(*cell) : (cudaStream_t)0; }
+void note_compute_stream(cudaStream_t s);   // remembered so side-stream copies can order after compute
+cudaStream_t last_compute_stream();
+
+// ---- shapes -------------------------------------------------------------------
+inline int64_t numel(const DLArray* a) {
+  int64_t n = 1;
+  for (int i = 0; i < a->ndim; ++i) n *= a->shape[i];
+  return n;
+}
+inline bool same_shape(const DLArray* a, const DLArray* b) {
+  if (a->ndim != b->ndim) return false;
+  for (int i = 0; i < a->ndim; ++i) if (a->shape[i] != b->shape[i]) return false;
+  return true;
+}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- device memory pool (thread-safe, size-class caching) --------------------
+// Returns nullptr when the device is out of memory even after the cache was released.
+void* pool_alloc(size_t bytes);
+void pool_free(void* p);
+// Scratch buffers that live as long as the library (grown on demand, never shrunk);
+// slot ids are per purpose so concurrent purposes do not collide.
+void* persistent_scratch(int slot, size_t bytes);
+
+// ---- grid sizing: whole multiples of the SM count -----------------------------
+inline int grid_for(int64_t work_items, int block, int per_thread = 1, int waves = 8) {
+  int64_t need = (work_items + (int64_t)block * per_thread - 1) / ((int64_t)block * per_thread);
+  if (need < 1) need = 1;
+  int64_t cap = (int64_t)device_sm_count() * waves;
+  if (need > cap) need = cap;                       // grid-stride loop covers the rest
+  else if (need > device_sm_count()) {              // round up to a multiple of the SM count
+    int sms = device_sm_count();
+    need = (need + sms - 1) / sms * sms;
+  }
+  return (int)need;
+}
+
+// ---- plan structs stored in slot 0 of a descriptor list ----------------------
+enum PlanKind : int { kPlanConv = 0x7f01, kPlanPool, kPlanAct, kPlanReduce, kPlanBN, kPlanTensor, kPlanDropout };
+
+struct ConvPlan {
+  int kind;
+  int N, C, H, W;        // input
+  int K, R, S;           // filter: K output channels, R x S window
+  int P, Q;              // output spatial
+  int pad_h, pad_w, stride_h, stride_w;
+  int dataformat;
+  void* tc_state;        // tensor-core path cache (packed operands, tensor maps)
+};
+struct PoolPlan {
+  int kind;
+  int N, C, H, W, P, Q;
+  int mode;              // 0 max, 1 average (divisor includes padding)
+  int pad_h, pad_w, stride_h, stride_w, win_h, win_w;
+  int dataformat;
+};
+struct TensorPlan {      // activation / dropout input descriptor
+  int kind;
+  int ndim;
+  int dims[5];
+  int dataformat;
+  int mode;
+  int64_t batch, inner;  // batch = dims[0], inner = product of the rest
+};
+struct ReducePlan {
+  int kind;
+  int ndim;
+  int in_dims[5];
+  int out_dims[5];
+};
+struct BNPlan {
+  int kind;
+  int mode;              // 0 per-activation, 1 spatial
+  int64_t N, C, HW;      // spatial: stats per C over N*HW; per-activation: stats per C*HW over N
+  float* save_mean;      // library-owned, sized to the statistic count
+  float* save_inv;
+  int64_t nstat;
+};
+struct DropoutState {
+  int kind;
+  float p;
+  unsigned long long seed;
+  int64_t count;
+};
+
+template <class T> T* plan_of(void*** cell, int kind) {
+  if (!cell || !*cell) return nullptr;
+  T* p = reinterpret_cast<T*>((*cell)[0]);
+  if (!p || p->kind != kind) return nullptr;
+  return p;
+}
+// Allocates the slot array the reference allocates (so a caller that frees it stays valid).
+template <class T> T* new_plan(void*** cell, int kind, int slots) {
+  void** arr = (void**)calloc(slots < 1 ? 1 : slots, sizeof(void*));
+  T* p = (T*)calloc(1, sizeof(T));
+  p->kind = kind;
+  arr[0] = p;
+  *cell = arr;
+  return p;
+}
+
+}  // namespace tf

@@ -1,0 +1,438 @@
+// Pooling and batch normalisation (NCHW fp32), forward and backward.  HBM-bound: each
+// tensor is read once and written once; statistics are reduced in registers / warp shuffles.
+#include "common.h"
+#include <math.h>
+
+namespace tf {
+
+// =====================================================================================
+// Pooling.  Window semantics follow cuDNN as used by the reference (src/gpu_op.cu:2880-2983):
+// output extent = 1 + (in + 2*pad - window) / stride; max ignores padded taps; average divides
+// by the full window area (padding included).  Two documented choices where cuDNN's behaviour
+// cannot be observed: a max window that covers only padding yields 0, and on ties the first
+// maximum in row-major window order receives the gradient.
+// =====================================================================================
+struct PoolGeom { int C, H, W, P, Q, ph, pw, sh, sw, kh, kw; };
+
+__device__ __forceinline__ int window_argmax(const float* __restrict__ plane, const PoolGeom& g, int p, int q, float* best_out) {
+  int h0 = p * g.sh - g.ph, w0 = q * g.sw - g.pw;
+  int best = -1;
+  float bv = 0.f;
+  for (int r = 0; r < g.kh; ++r) {
+    int h = h0 + r;
+    if (h < 0 || h >= g.H) continue;
+    for (int s = 0; s < g.kw; ++s) {
+      int w = w0 + s;
+      if (w < 0 || w >= g.W) continue;
+      float v = plane[h * g.W + w];
+      if (best < 0 || v > bv) { best = h * g.W + w; bv = v; }
+    }
+  }
+  *best_out = bv;
+  return best;
+}
+
+__global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ idx, int64_t total, PoolGeom g) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int PQ = g.P * g.Q;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t plane = i / PQ;
+    int pq = (int)(i % PQ), p = pq / g.Q, q = pq % g.Q;
+    float v;
+    int a = window_argmax(x + plane * g.H * g.W, g, p, q, &v);
+    if (y) y[i] = a < 0 ? 0.f : v;
+    if (idx) idx[i] = a;
+  }
+}
+// Gather form of the max-pool gradient: each input element sums dy over the windows whose
+// first maximum it is.  No atomics, deterministic, dx fully written.
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, int64_t total, PoolGeom g) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int HW = g.H * g.W, PQ = g.P * g.Q;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t plane = i / HW;
+    int hw = (int)(i % HW), h = hw / g.W, w = hw % g.W;
+    const float* xp = x + plane * HW;
+    const float* dp = dy + plane * PQ;
+    // windows (p,q) with p*sh - ph <= h < p*sh - ph + kh
+    int p_lo = (h + g.ph - g.kh + g.sh) / g.sh; if (h + g.ph - g.kh + 1 <= 0) p_lo = 0;
+    int p_hi = min(g.P - 1, (h + g.ph) / g.sh);
+    int q_lo = (w + g.pw - g.kw + g.sw) / g.sw; if (w + g.pw - g.kw + 1 <= 0) q_lo = 0;
+    int q_hi = min(g.Q - 1, (w + g.pw) / g.sw);
+    float acc = 0.f;
+    for (int p = p_lo; p <= p_hi; ++p)
+      for (int q = q_lo; q <= q_hi; ++q) {
+        float v;
+        if (window_argmax(xp, g, p, q, &v) == hw) acc += dp[p * g.Q + q];
+      }
+    dx[i] = acc;
+  }
+}
+__global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t total, PoolGeom g) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int PQ = g.P * g.Q;
+  float inv = 1.f / (float)(g.kh * g.kw);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t plane = i / PQ;
+    int pq = (int)(i % PQ), p = pq / g.Q, q = pq % g.Q;
+    const float* xp = x + plane * g.H * g.W;
+    int h0 = p * g.sh - g.ph, w0 = q * g.sw - g.pw;
+    float acc = 0.f;
+    for (int r = 0; r < g.kh; ++r) {
+      int h = h0 + r;
+      if (h < 0 || h >= g.H) continue;
+      for (int s = 0; s < g.kw; ++s) {
+        int w = w0 + s;
+        if (w >= 0 && w < g.W) acc += xp[h * g.W + w];
+      }
+    }
+    y[i] = acc * inv;
+  }
+}
+__global__ void __launch_bounds__(256) avgpool_bwd_kernel(const float* __restrict__ dy, float* __restrict__ dx, int64_t total, PoolGeom g) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int HW = g.H * g.W, PQ = g.P * g.Q;
+  float inv = 1.f / (float)(g.kh * g.kw);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t plane = i / HW;
+    int hw = (int)(i % HW), h = hw / g.W, w = hw % g.W;
+    const float* dp = dy + plane * PQ;
+    int p_lo = (h + g.ph - g.kh + g.sh) / g.sh; if (h + g.ph - g.kh + 1 <= 0) p_lo = 0;
+    int p_hi = min(g.P - 1, (h + g.ph) / g.sh);
+    int q_lo = (w + g.pw - g.kw + g.sw) / g.sw; if (w + g.pw - g.kw + 1 <= 0) q_lo = 0;
+    int q_hi = min(g.Q - 1, (w + g.pw) / g.sw);
+    float acc = 0.f;
+    for (int p = p_lo; p <= p_hi; ++p)
+      for (int q = q_lo; q <= q_hi; ++q) acc += dp[p * g.Q + q];
+    dx[i] = acc * inv;
+  }
+}
+
+static PoolGeom geom_of(const PoolPlan* p) {
+  PoolGeom g;
+  g.C = p->C; g.H = p->H; g.W = p->W; g.P = p->P; g.Q = p->Q;
+  g.ph = p->pad_h; g.pw = p->pad_w; g.sh = p->stride_h; g.sw = p->stride_w; g.kh = p->win_h; g.kw = p->win_w;
+  return g;
+}
+
+// =====================================================================================
+// Batch normalisation with unit scale and zero bias, batch statistics, eps = 1e-5
+// (src/gpu_op.cu:4224-4460).  Forward saves the mean and 1/sqrt(var+eps) it used; backward
+// computes  dx = inv * (dy - mean(dy) - xhat * mean(dy * xhat))  with xhat = (x - mean) * inv.
+//
+// Per-activation mode: one statistic per (c,h,w) feature, reduced over the batch only.  Threads
+// own consecutive features (coalesced across the warp for every sample) and keep their whole
+// batch column in registers, so x (and dy) cross HBM exactly once.
+// =====================================================================================
+constexpr float kBnEps = 1e-5f;
+constexpr int kBnMaxBatchInRegs = 64;
+
+template <int VEC> struct VecT;
+template <> struct VecT<1> { using type = float; };
+template <> struct VecT<2> { using type = float2; };
+template <> struct VecT<4> { using type = float4; };
+
+template <int NB, int VEC>
+__global__ void __launch_bounds__(128) bn_pa_fwd_regs_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ save_mean, float* __restrict__ save_inv, int N, int64_t F) {
+  using V = typename VecT<VEC>::type;
+  int64_t fv = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;       // vector index over features
+  int64_t FV = F / VEC;
+  if (fv >= FV) return;
+  const V* xv = reinterpret_cast<const V*>(x);
+  V* yv = reinterpret_cast<V*>(y);
+  float v[NB][VEC];
+#pragma unroll
+  for (int n = 0; n < NB; ++n) {
+    if (n < N) {
+      V t = xv[(int64_t)n * FV + fv];
+      const float* tp = reinterpret_cast<const float*>(&t);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) v[n][k] = tp[k];
+    }
+  }
+  float mean[VEC], inv[VEC];
+  float rn = 1.f / (float)N;
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    float s = 0.f;
+#pragma unroll
+    for (int n = 0; n < NB; ++n) if (n < N) s += v[n][k];
+    float m = s * rn, q = 0.f;
+#pragma unroll
+    for (int n = 0; n < NB; ++n) if (n < N) { float d = v[n][k] - m; q += d * d; }
+    mean[k] = m;
+    inv[k] = rsqrtf(q * rn + kBnEps);
+    // one Newton step brings rsqrtf to full fp32 accuracy
+    float a = q * rn + kBnEps;
+    inv[k] = inv[k] * (1.5f - 0.5f * a * inv[k] * inv[k]);
+  }
+#pragma unroll
+  for (int n = 0; n < NB; ++n) {
+    if (n < N) {
+      V t;
+      float* tp = reinterpret_cast<float*>(&t);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) tp[k] = (v[n][k] - mean[k]) * inv[k];
+      yv[(int64_t)n * FV + fv] = t;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) { save_mean[fv * VEC + k] = mean[k]; save_inv[fv * VEC + k] = inv[k]; }
+}
+
+template <int NB>
+__global__ void __launch_bounds__(128) bn_pa_bwd_regs_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, const float* __restrict__ save_mean, const float* __restrict__ save_inv, int N, int64_t F) {
+  int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (f >= F) return;
+  float m = save_mean[f], inv = save_inv[f];
+  float xh[NB], g[NB];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int n = 0; n < NB; ++n) {
+    if (n < N) {
+      xh[n] = (x[(int64_t)n * F + f] - m) * inv;
+      g[n] = dy[(int64_t)n * F + f];
+      s1 += g[n];
+      s2 += g[n] * xh[n];
+    }
+  }
+  float rn = 1.f / (float)N;
+  s1 *= rn; s2 *= rn;
+#pragma unroll
+  for (int n = 0; n < NB; ++n) if (n < N) dx[(int64_t)n * F + f] = inv * (g[n] - s1 - xh[n] * s2);
+}
+
+// Any batch size: three passes over the batch column (the re-reads are served by L2).
+__global__ void __launch_bounds__(128) bn_pa_fwd_loop_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ save_mean, float* __restrict__ save_inv, int N, int64_t F) {
+  int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (f >= F) return;
+  float rn = 1.f / (float)N, s = 0.f, q = 0.f;
+  for (int n = 0; n < N; ++n) s += x[(int64_t)n * F + f];
+  float m = s * rn;
+  for (int n = 0; n < N; ++n) { float d = x[(int64_t)n * F + f] - m; q += d * d; }
+  float inv = 1.f / sqrtf(q * rn + kBnEps);
+  for (int n = 0; n < N; ++n) y[(int64_t)n * F + f] = (x[(int64_t)n * F + f] - m) * inv;
+  save_mean[f] = m; save_inv[f] = inv;
+}
+__global__ void __launch_bounds__(128) bn_pa_bwd_loop_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, const float* __restrict__ save_mean, const float* __restrict__ save_inv, int N, int64_t F) {
+  int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (f >= F) return;
+  float m = save_mean[f], inv = save_inv[f], s1 = 0.f, s2 = 0.f, rn = 1.f / (float)N;
+  for (int n = 0; n < N; ++n) { float g = dy[(int64_t)n * F + f]; s1 += g; s2 += g * (x[(int64_t)n * F + f] - m) * inv; }
+  s1 *= rn; s2 *= rn;
+  for (int n = 0; n < N; ++n) dx[(int64_t)n * F + f] = inv * (dy[(int64_t)n * F + f] - s1 - (x[(int64_t)n * F + f] - m) * inv * s2);
+}
+
+// Spatial mode: one statistic per channel over N*H*W.  One block per channel.
+__device__ __forceinline__ float bsum(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__global__ void __launch_bounds__(512) bn_sp_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ save_mean, float* __restrict__ save_inv, int64_t N, int64_t C, int64_t HW) {
+  __shared__ float red[33];
+  int64_t c = blockIdx.x, cnt = N * HW;
+  float s = 0.f;
+  for (int64_t i = threadIdx.x; i < cnt; i += blockDim.x) s += x[((i / HW) * C + c) * HW + i % HW];
+  float m = bsum(s, red) / (float)cnt, q = 0.f;
+  for (int64_t i = threadIdx.x; i < cnt; i += blockDim.x) { float d = x[((i / HW) * C + c) * HW + i % HW] - m; q += d * d; }
+  float inv = 1.f / sqrtf(bsum(q, red) / (float)cnt + kBnEps);
+  for (int64_t i = threadIdx.x; i < cnt; i += blockDim.x) { int64_t o = ((i / HW) * C + c) * HW + i % HW; y[o] = (x[o] - m) * inv; }
+  if (threadIdx.x == 0) { save_mean[c] = m; save_inv[c] = inv; }
+}
+__global__ void __launch_bounds__(512) bn_sp_bwd_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, const float* __restrict__ save_mean, const float* __restrict__ save_inv, int64_t N, int64_t C, int64_t HW) {
+  __shared__ float red[33];
+  int64_t c = blockIdx.x, cnt = N * HW;
+  float m = save_mean[c], inv = save_inv[c], s1 = 0.f, s2 = 0.f;
+  for (int64_t i = threadIdx.x; i < cnt; i += blockDim.x) { int64_t o = ((i / HW) * C + c) * HW + i % HW; float g = dy[o]; s1 += g; s2 += g * (x[o] - m) * inv; }
+  s1 = bsum(s1, red) / (float)cnt;
+  s2 = bsum(s2, red) / (float)cnt;
+  for (int64_t i = threadIdx.x; i < cnt; i += blockDim.x) { int64_t o = ((i / HW) * C + c) * HW + i % HW; dx[o] = inv * (dy[o] - s1 - (x[o] - m) * inv * s2); }
+}
+
+template <int NB> static void launch_bn_fwd_regs(const float* x, float* y, float* sm, float* si, int N, int64_t F, cudaStream_t s) {
+  bool v2 = (F % 2 == 0) && aligned16(x) && aligned16(y) && NB <= 64;
+  if (v2) { int64_t FV = F / 2; bn_pa_fwd_regs_kernel<NB, 2><<<(unsigned)((FV + 127) / 128), 128, 0, s>>>(x, y, sm, si, N, F); }
+  else bn_pa_fwd_regs_kernel<NB, 1><<<(unsigned)((F + 127) / 128), 128, 0, s>>>(x, y, sm, si, N, F);
+}
+
+}  // namespace tf
+
+using namespace tf;
+
+extern "C" {
+
+int DLGpuPooling2DForwardGetOutShape(const int* input_shapes, int* output_shapes, int dataformat, int poolingMode,
+                                     const int padding_h, const int padding_w, const int u, const int v,
+                                     const int filter_h, const int filter_w, void*** cudnnlist) {
+  TF_REQUIRE(input_shapes && output_shapes && cudnnlist, "DLGpuPooling2DForwardGetOutShape: null argument");
+  TF_REQUIRE(u > 0 && v > 0 && filter_h > 0 && filter_w > 0 && padding_h >= 0 && padding_w >= 0, "DLGpuPooling2DForwardGetOutShape: bad window");
+  TF_REQUIRE(poolingMode == 0 || poolingMode == 1, "DLGpuPooling2DForwardGetOutShape: unknown mode %d", poolingMode);
+  PoolPlan* p = new_plan<PoolPlan>(cudnnlist, kPlanPool, 3);
+  p->dataformat = dataformat; p->mode = poolingMode;
+  p->N = input_shapes[0];
+  if (dataformat == 0) { p->C = input_shapes[1]; p->H = input_shapes[2]; p->W = input_shapes[3]; }
+  else { p->C = input_shapes[3]; p->H = input_shapes[1]; p->W = input_shapes[2]; }
+  p->pad_h = padding_h; p->pad_w = padding_w; p->stride_h = u; p->stride_w = v; p->win_h = filter_h; p->win_w = filter_w;
+  p->P = 1 + (p->H + 2 * padding_h - filter_h) / u;
+  p->Q = 1 + (p->W + 2 * padding_w - filter_w) / v;
+  TF_REQUIRE(p->P > 0 && p->Q > 0, "DLGpuPooling2DForwardGetOutShape: window larger than padded input");
+  output_shapes[0] = p->N;
+  if (dataformat == 0) { output_shapes[1] = p->C; output_shapes[2] = p->P; output_shapes[3] = p->Q; }
+  else { output_shapes[1] = p->P; output_shapes[2] = p->Q; output_shapes[3] = p->C; }
+  return 0;
+}
+
+static int check_pool(const PoolPlan* p, const DLArrayHandle in, const DLArrayHandle out, const char* what) {
+  TF_REQUIRE(p, "%s: descriptor was not built by DLGpuPooling2DForwardGetOutShape", what);
+  TF_REQUIRE(p->dataformat == 0, "%s: only NCHW is implemented", what);
+  TF_REQUIRE(in && numel(in) == (int64_t)p->N * p->C * p->H * p->W, "%s: input does not match the descriptor", what);
+  TF_REQUIRE(out && numel(out) == (int64_t)p->N * p->C * p->P * p->Q, "%s: output does not match the descriptor", what);
+  return 0;
+}
+
+int DLGpuPooling2DForward(const DLArrayHandle input, DLArrayHandle output, void*** cudnnlist, void** cudnnHandle, void** cudaStream) {
+  (void)cudnnHandle;
+  PoolPlan* p = plan_of<PoolPlan>(cudnnlist, kPlanPool);
+  if (check_pool(p, input, output, "DLGpuPooling2DForward")) return -1;
+  cudaStream_t s = stream_of(cudaStream);
+  int64_t total = numel(output);
+  note_compute_stream(s);
+  if (p->mode == 0) maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (float*)output->data, nullptr, total, geom_of(p));
+  else avgpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (float*)output->data, total, geom_of(p));
+  TF_AFTER(s, "DLGpuPooling2DForward");
+  return 0;
+}
+
+int DLGpuPooling2DBackward(const DLArrayHandle input, const DLArrayHandle output, const DLArrayHandle doutput, DLArrayHandle dinput,
+                           void*** cudnnlist, void** cudnnHandle, void** cudaStream) {
+  (void)cudnnHandle;
+  PoolPlan* p = plan_of<PoolPlan>(cudnnlist, kPlanPool);
+  if (check_pool(p, input, output, "DLGpuPooling2DBackward")) return -1;
+  TF_REQUIRE(doutput && dinput && numel(doutput) == numel(output) && numel(dinput) == numel(input), "DLGpuPooling2DBackward: gradient sizes do not match");
+  cudaStream_t s = stream_of(cudaStream);
+  int64_t total = numel(dinput);
+  note_compute_stream(s);
+  if (p->mode == 0) maxpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (const float*)doutput->data, (float*)dinput->data, total, geom_of(p));
+  else avgpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)doutput->data, (float*)dinput->data, total, geom_of(p));
+  TF_AFTER(s, "DLGpuPooling2DBackward");
+  return 0;
+}
+
+int TfPoolingArgmax(const DLArrayHandle input, int32_t* indices_dev, void*** cudnnlist, void** cudaStream) {
+  PoolPlan* p = plan_of<PoolPlan>(cudnnlist, kPlanPool);
+  TF_REQUIRE(p && p->dataformat == 0 && input && indices_dev && numel(input) == (int64_t)p->N * p->C * p->H * p->W, "TfPoolingArgmax: bad arguments");
+  cudaStream_t s = stream_of(cudaStream);
+  int64_t total = (int64_t)p->N * p->C * p->P * p->Q;
+  note_compute_stream(s);
+  maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, nullptr, indices_dev, total, geom_of(p));
+  TF_AFTER(s, "TfPoolingArgmax");
+  return 0;
+}
+
+// ---- batch normalisation --------------------------------------------------------------------
+int DLGpuBatchNormalizationGetCudnnlist(const int* input_shapes, int sizeofshape, int dataformat, int batchNormMode,
+                                        void** mean_p, void** Variance_p, void*** cudnnlist) {
+  (void)mean_p; (void)Variance_p;
+  TF_REQUIRE(input_shapes && cudnnlist && sizeofshape >= 2 && sizeofshape <= 5, "DLGpuBatchNormalizationGetCudnnlist: bad arguments");
+  TF_REQUIRE(batchNormMode == 0 || batchNormMode == 1, "DLGpuBatchNormalizationGetCudnnlist: unknown mode %d", batchNormMode);
+  TF_REQUIRE(dataformat == 0 || batchNormMode == 0, "DLGpuBatchNormalizationGetCudnnlist: spatial mode is implemented for NCHW only");
+  BNPlan* p = new_plan<BNPlan>(cudnnlist, kPlanBN, 3);
+  p->mode = batchNormMode;
+  p->N = input_shapes[0];
+  // channel axis: dim 1 for NCHW, last dim for NHWC
+  int64_t rest = 1;
+  for (int i = 1; i < sizeofshape; ++i) rest *= input_shapes[i];
+  p->C = dataformat == 0 ? input_shapes[1] : input_shapes[sizeofshape - 1];
+  p->HW = p->C ? rest / p->C : 0;
+  p->nstat = batchNormMode == 0 ? rest : p->C;
+  return 0;
+}
+
+static int bn_buffers(BNPlan* p, int* memorytoSaving) {
+  if (p->save_mean) return 0;
+  size_t bytes = sizeof(float) * (size_t)p->nstat;
+  p->save_mean = (float*)pool_alloc(bytes);
+  p->save_inv = p->save_mean ? (float*)pool_alloc(bytes) : nullptr;
+  if (!p->save_inv) {
+    if (p->save_mean) { pool_free(p->save_mean); p->save_mean = nullptr; }
+    if (memorytoSaving) *memorytoSaving = (int)bytes;
+    return 1;
+  }
+  return 0;
+}
+
+int DLGpuBatchNormalizationForward(const DLArrayHandle input, DLArrayHandle output, int batchNormMode, int n, void** mean_p, void** Variance_p,
+                                   void*** cudnnlist, void** cudnnHandle, int* memorytoSaving, void** cudaStream) {
+  (void)n; (void)cudnnHandle;
+  BNPlan* p = plan_of<BNPlan>(cudnnlist, kPlanBN);
+  TF_REQUIRE(p && p->mode == batchNormMode, "DLGpuBatchNormalizationForward: descriptor / mode mismatch");
+  TF_REQUIRE(input && output && numel(input) == numel(output) && numel(input) == p->N * p->C * p->HW, "DLGpuBatchNormalizationForward: arrays do not match the descriptor");
+  if (bn_buffers(p, memorytoSaving)) return 0;    // soft out-of-memory
+  if (mean_p) *mean_p = p->save_mean;
+  if (Variance_p) *Variance_p = p->save_inv;
+  cudaStream_t s = stream_of(cudaStream);
+  const float* x = (const float*)input->data;
+  float* y = (float*)output->data;
+  note_compute_stream(s);
+  if (p->mode == 0) {
+    int64_t F = p->nstat;
+    int N = (int)p->N;
+    if (N <= 8) launch_bn_fwd_regs<8>(x, y, p->save_mean, p->save_inv, N, F, s);
+    else if (N <= 32) launch_bn_fwd_regs<32>(x, y, p->save_mean, p->save_inv, N, F, s);
+    else if (N <= kBnMaxBatchInRegs) launch_bn_fwd_regs<64>(x, y, p->save_mean, p->save_inv, N, F, s);
+    else bn_pa_fwd_loop_kernel<<<(unsigned)((F + 127) / 128), 128, 0, s>>>(x, y, p->save_mean, p->save_inv, N, F);
+  } else {
+    bn_sp_fwd_kernel<<<(unsigned)p->C, 512, 0, s>>>(x, y, p->save_mean, p->save_inv, p->N, p->C, p->HW);
+  }
+  TF_AFTER(s, "DLGpuBatchNormalizationForward");
+  return 0;
+}
+
+int DLGpuBatchNormalizationBackward(const DLArrayHandle input, const DLArrayHandle doutput, DLArrayHandle dinput, int batchNormMode,
+                                    void** mean_p, void** Variance_p, void*** cudnnlist, void** cudnnHandle, int* memorytoSaving, void** cudaStream) {
+  (void)mean_p; (void)Variance_p; (void)cudnnHandle; (void)memorytoSaving;
+  BNPlan* p = plan_of<BNPlan>(cudnnlist, kPlanBN);
+  TF_REQUIRE(p && p->mode == batchNormMode, "DLGpuBatchNormalizationBackward: descriptor / mode mismatch");
+  TF_REQUIRE(p->save_mean && p->save_inv, "DLGpuBatchNormalizationBackward: forward has not run for this descriptor");
+  TF_REQUIRE(input && doutput && dinput && numel(input) == p->N * p->C * p->HW && numel(doutput) == numel(input) && numel(dinput) == numel(input), "DLGpuBatchNormalizationBackward: arrays do not match the descriptor");
+  cudaStream_t s = stream_of(cudaStream);
+  const float* x = (const float*)input->data;
+  const float* dy = (const float*)doutput->data;
+  float* dx = (float*)dinput->data;
+  note_compute_stream(s);
+  if (p->mode == 0) {
+    int64_t F = p->nstat;
+    int N = (int)p->N;
+    unsigned grid = (unsigned)((F + 127) / 128);
+    if (N <= 8) bn_pa_bwd_regs_kernel<8><<<grid, 128, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, N, F);
+    else if (N <= 32) bn_pa_bwd_regs_kernel<32><<<grid, 128, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, N, F);
+    else if (N <= kBnMaxBatchInRegs) bn_pa_bwd_regs_kernel<64><<<grid, 128, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, N, F);
+    else bn_pa_bwd_loop_kernel<<<grid, 128, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, N, F);
+  } else {
+    bn_sp_bwd_kernel<<<(unsigned)p->C, 512, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, p->N, p->C, p->HW);
+  }
+  TF_AFTER(s, "DLGpuBatchNormalizationBackward");
+  return 0;
+}
+
+// ---- 1-D / 3-D pooling: symbols only ------------------------------------------------------------
+int DLGpuPooling1DForwardGetOutShape(const int*, int*, int, int, const int, const int, const int, void***) { TF_FAIL("1-D pooling is not implemented"); }
+int DLGpuPooling3DForwardGetOutShape(const int*, int*, int, int, const int, const int, const int, const int, const int, const int, const int, const int, const int, void***) { TF_FAIL("3-D pooling is not implemented"); }
+int DLGpuPooling1DForward(const DLArrayHandle, DLArrayHandle, void***, void**) { TF_FAIL("1-D pooling is not implemented"); }
+int DLGpuPooling3DForward(const DLArrayHandle, DLArrayHandle, void***, void**) { TF_FAIL("3-D pooling is not implemented"); }
+int DLGpuPooling1DBackward(const DLArrayHandle, const DLArrayHandle, const DLArrayHandle, DLArrayHandle, void***, void**) { TF_FAIL("1-D pooling is not implemented"); }
+int DLGpuPooling3DBackward(const DLArrayHandle, const DLArrayHandle, const DLArrayHandle, DLArrayHandle, void***, void**) { TF_FAIL("3-D pooling is not implemented"); }
+
+}  // extern "C"

@@ -1,0 +1,200 @@
+"""Workload graphs for the five benchmark configurations, built with the mirrored ``ad`` API.
+
+Each builder returns a :class:`Model` (placeholders, loss, prediction node, parameter shapes in
+network order).  The graphs follow the reference's model scripts node for node:
+
+* :func:`mlp`        tests/mnist_dlsys.py:177-194 (784-256-100-10, ReLU, softmax-cross-entropy)
+* :func:`lenet5`     LeNet-5 with the layer sizes of the benchmark configuration, wired like the
+                     reference's LeNet (tests/LeNet5/LeNet5_mnist_test.py:72-125: conv+bias, ReLU, max-pool)
+* :func:`vgg16`      pycode/tinyflow/VGG16_test_leo.py:169-254
+* :func:`resnet50`   pycode/tinyflow/ResNet50_test_leo.py:27-261
+* :func:`inceptionv3` pycode/tinyflow/Inceptionv3_test_leo.py:558-1020
+
+Initial values are synthetic: He-normal weights (std = sqrt(2 / fan_in)), zero biases, drawn from a
+seeded ``numpy.random.RandomState``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import autodiff as ad
+
+
+@dataclass
+class Model:
+    name: str
+    X: object
+    y_: object
+    loss: object
+    y: object
+    param_shapes: dict = field(default_factory=dict)   # Variable node -> shape, network order
+    input_shape: tuple = ()
+    label_shape: tuple = ()
+    dropout_nodes: list = field(default_factory=list)
+
+    def init_params(self, seed=123, std=None):
+        """He-normal weights / zero biases as float32 numpy arrays, keyed by Variable node."""
+        rng = np.random.RandomState(seed)
+        out = {}
+        for node, shape in self.param_shapes.items():
+            if len(shape) == 1:
+                out[node] = np.zeros(shape, np.float32)
+                continue
+            fan_in = int(np.prod(shape[1:])) if len(shape) == 4 else shape[0]
+            s = std if std is not None else np.sqrt(2.0 / fan_in)
+            out[node] = rng.normal(0.0, s, size=shape).astype(np.float32)
+        return out
+
+    def set_dropout(self, rate):
+        for n in self.dropout_nodes:
+            n.dropout = rate
+
+
+def mlp(batch=1000, sizes=(784, 256, 100, 10)):
+    X, y_ = ad.Placeholder("X"), ad.Placeholder("y_")
+    params, h = {}, X
+    n_layers = len(sizes) - 1
+    Ws = [ad.Variable("W%d" % (i + 1)) for i in range(n_layers)]
+    bs = [ad.Variable("b%d" % (i + 1)) for i in range(n_layers)]
+    for i in range(n_layers):
+        z = ad.matmul_op(h, Ws[i])
+        z = z + ad.broadcastto_op(bs[i], z)
+        h = ad.relu_op(z) if i < n_layers - 1 else z
+    loss = ad.softmaxcrossentropy_op(h, y_)
+    for i in range(n_layers):
+        params[Ws[i]] = (sizes[i], sizes[i + 1])
+    for i in range(n_layers):
+        params[bs[i]] = (sizes[i + 1],)
+    return Model("mlp", X, y_, loss, h, params, (batch, sizes[0]), (batch, sizes[-1]))
+
+
+def lenet5(batch=256, classes=10):
+    X, y_ = ad.Placeholder("X"), ad.Placeholder("y_")
+    W1, b1 = ad.Variable("W1"), ad.Variable("b1")
+    W2, b2 = ad.Variable("W2"), ad.Variable("b2")
+    W3, b3 = ad.Variable("W3"), ad.Variable("b3")
+    W4, b4 = ad.Variable("W4"), ad.Variable("b4")
+    W5, b5 = ad.Variable("W5"), ad.Variable("b5")
+    c1 = ad.conv2withbias(X, W1, b1, "NCHW", "SAME", 1, 1)          # 1x28x28 -> 6x28x28
+    a1 = ad.activation_forward_op(c1, "NCHW", "relu")
+    p1 = ad.pooling_2d_forward_op(a1, "NCHW", "max", 0, 0, 2, 2, 2, 2)   # -> 6x14x14
+    c2 = ad.conv2withbias(p1, W2, b2, "NCHW", "VALID", 1, 1)        # -> 16x10x10
+    a2 = ad.activation_forward_op(c2, "NCHW", "relu")
+    p2 = ad.pooling_2d_forward_op(a2, "NCHW", "max", 0, 0, 2, 2, 2, 2)   # -> 16x5x5
+    f = ad.flatten_op(p2)
+    d3 = ad.fullyactivation_forward_op(ad.dense(f, W3, b3), "NCHW", "relu")
+    d4 = ad.fullyactivation_forward_op(ad.dense(d3, W4, b4), "NCHW", "relu")
+    y = ad.dense(d4, W5, b5)
+    loss = ad.softmaxcrossentropy_op(y, y_)
+    params = {W1: (6, 1, 5, 5), b1: (6,), W2: (16, 6, 5, 5), b2: (16,), W3: (400, 120), b3: (120,),
+              W4: (120, 84), b4: (84,), W5: (84, classes), b5: (classes,)}
+    return Model("lenet5", X, y_, loss, y, params, (batch, 1, 28, 28), (batch, classes))
+
+
+def _conv_relu(x, w, padding, sh, sw):
+    return ad.activation_forward_op(ad.convolution_2d_forward_op(x, w, "NCHW", padding, sh, sw), "NCHW", "relu")
+
+
+def vgg16(batch=64, classes=1000, image=224, dropout=0.5):
+    X, y_ = ad.Placeholder("X"), ad.Placeholder("y_")
+    cfg = [(64, 2), (128, 2), (256, 3), (512, 3), (512, 3)]
+    params, h, cin = {}, X, 3
+    conv_vars = []
+    for bi, (cout, reps) in enumerate(cfg, start=1):
+        for ri in range(1, reps + 1):
+            conv_vars.append((ad.Variable("W%d_%d" % (bi, ri)), (cout, cin, 3, 3)))
+            cin = cout
+    W6, W7, W8 = ad.Variable("W6"), ad.Variable("W7"), ad.Variable("W8")
+    b6, b7, b8 = ad.Variable("b6"), ad.Variable("b7"), ad.Variable("b8")
+    it = iter(conv_vars)
+    for cout, reps in cfg:
+        for _ in range(reps):
+            w, shape = next(it)
+            params[w] = shape
+            h = _conv_relu(h, w, "SAME", 1, 1)
+        h = ad.pooling_2d_forward_op(h, "NCHW", "max", 0, 0, 2, 2, 2, 2)
+    spatial = image // 32
+    flat = ad.flatten_op(h)
+    drops = []
+    fc6 = ad.dense(flat, W6, b6)
+    act6 = ad.fullyactivation_forward_op(fc6, "NCHW", "relu")
+    drop6 = ad.fullydropout_forward_op(act6, "NCHW", dropout); drops.append(drop6)
+    fc7 = ad.dense(drop6, W7, b7)
+    act7 = ad.fullyactivation_forward_op(fc7, "NCHW", "relu")
+    drop7 = ad.fullydropout_forward_op(act7, "NCHW", dropout); drops.append(drop7)
+    fc8 = ad.dense(drop7, W8, b8)
+    bn8 = ad.fullybn_forward_op(fc8, "NCHW")
+    y = ad.fullyactivation_forward_op(bn8, "NCHW", "softmax")
+    loss = ad.crossEntropy_loss(y, y_)
+    params.update({W6: (512 * spatial * spatial, 4096), W7: (4096, 4096), W8: (4096, classes),
+                   b6: (4096,), b7: (4096,), b8: (classes,)})
+    return Model("vgg16", X, y_, loss, y, params, (batch, 3, image, image), (batch, classes), drops)
+
+
+def _bottleneck(x, cin, filters, name, stride, projection, params):
+    """Residual bottleneck (identity_block / convolutional_block, ResNet50_test_leo.py:27-111)."""
+    f1, f2, f3 = filters
+    W1, W2, W3 = ad.Variable(name + "W1"), ad.Variable(name + "W2"), ad.Variable(name + "W3")
+    first_pad = "VALID" if projection else "SAME"
+    h = ad.convolution_2d_forward_op(x, W1, "NCHW", first_pad, stride, stride)
+    h = ad.activation_forward_op(ad.bn_forward_op(h, "NCHW", "pre_activation"), "NCHW", "relu")
+    h = ad.convolution_2d_forward_op(h, W2, "NCHW", "SAME", 1, 1)
+    h = ad.activation_forward_op(ad.bn_forward_op(h, "NCHW", "pre_activation"), "NCHW", "relu")
+    h = ad.convolution_2d_forward_op(h, W3, "NCHW", "VALID", 1, 1)
+    h = ad.bn_forward_op(h, "NCHW", "pre_activation")
+    params[W1], params[W2], params[W3] = (f1, cin, 1, 1), (f2, f1, 3, 3), (f3, f2, 1, 1)
+    if projection:
+        Ws = ad.Variable(name + "W_shortcut")
+        sc = ad.convolution_2d_forward_op(x, Ws, "NCHW", "VALID", stride, stride)
+        sc = ad.bn_forward_op(sc, "NCHW", "pre_activation")
+        params[Ws] = (f3, cin, 1, 1)
+    else:
+        sc = x
+    return ad.activation_forward_op(ad.add_op(h, sc), "NCHW", "relu")
+
+
+def resnet50(batch=64, classes=1000, image=224, dropout=0.5):
+    X, y_ = ad.Placeholder("X"), ad.Placeholder("y_")
+    W1, W6, b6, W7, b7 = ad.Variable("W1"), ad.Variable("W6"), ad.Variable("b6"), ad.Variable("W7"), ad.Variable("b7")
+    params = {W1: (64, 3, 7, 7)}
+    # the reference zero-pads with a 1x1 stride-1 max-pool that has padding 3 (ResNet50_test_leo.py:219)
+    h = ad.pooling_2d_forward_op(X, "NCHW", "max", 3, 3, 1, 1, 1, 1)
+    h = ad.convolution_2d_forward_op(h, W1, "NCHW", "VALID", 2, 2)
+    h = ad.activation_forward_op(ad.bn_forward_op(h, "NCHW", "pre_activation"), "NCHW", "relu")
+    h = ad.pooling_2d_forward_op(h, "NCHW", "max", 0, 0, 2, 2, 3, 3)
+    cin = 64
+    stages = [("2", [64, 64, 256], 3, 1), ("3", [128, 128, 512], 4, 2), ("4", [256, 256, 1024], 6, 2), ("5", [512, 512, 2048], 3, 2)]
+    for sname, filters, blocks, stride in stages:
+        for bi in range(blocks):
+            name = "%s%s_" % (sname, "abcdef"[bi])
+            h = _bottleneck(h, cin, filters, name, stride if bi == 0 else 1, bi == 0, params)
+            cin = filters[2]
+    final = image // 32
+    h = ad.pooling_2d_forward_op(h, "NCHW", "mean", 0, 0, 1, 1, final, final)
+    flat = ad.flatten_op(h)
+    dense6 = ad.dense(flat, W6, b6)
+    act6 = ad.fullyactivation_forward_op(dense6, "NCHW", "relu")
+    drop6 = ad.fullydropout_forward_op(act6, "NCHW", dropout)
+    dense7 = ad.dense(drop6, W7, b7)
+    y = ad.fullyactivation_forward_op(dense7, "NCHW", "softmax")
+    loss = ad.crossEntropy_loss(y, y_)
+    params.update({W6: (2048, 2048), W7: (2048, classes), b6: (2048,), b7: (classes,)})
+    return Model("resnet50", X, y_, loss, y, params, (batch, 3, image, image), (batch, classes), [drop6])
+
+
+BUILDERS = {"mlp": mlp, "lenet5": lenet5, "vgg16": vgg16, "resnet50": resnet50}
+
+
+def synthetic_batch(model: Model, seed=1234, rank=0, input_dist="normal"):
+    """Seeded synthetic inputs of the model's shapes: X ~ N(0,1) or U[0,1), uniformly drawn one-hot labels."""
+    rng = np.random.RandomState(seed + rank)
+    if input_dist == "uniform":
+        X = rng.uniform(0.0, 1.0, size=model.input_shape).astype(np.float32)
+    else:
+        X = rng.normal(0.0, 1.0, size=model.input_shape).astype(np.float32)
+    labels = rng.randint(0, model.label_shape[1], size=model.label_shape[0])
+    y = np.zeros(model.label_shape, np.float32)
+    y[np.arange(model.label_shape[0]), labels] = 1.0
+    return X, y
