@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Benchmark: train images/s for one forward + backward + SGD step of ResNet-50 (batch 64 per GPU,
+3x224x224 synthetic inputs, 1000 classes) through the mirrored executor and the C-ABI library.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload resnet50|vgg16|lenet5|mlp]
+
+With N > 1 launch under torchrun (one rank per GPU); rank 0 prints one JSON line.
+`--impl reference` times the CPU arm instead: the same graph evaluated by the numpy restatement of
+the reference's operators (oracle/) on this box's host cores, on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+# Algorithmic work per image of one training step (forward + backward-data + backward-filter of every
+# convolution / matmul, 2 flops per multiply-add), computed from the graph by `step_flops` below.
+WORKLOADS = {
+    "resnet50": dict(batch=64, image=224, classes=1000, lr=0.01, dist="normal"),
+    "vgg16": dict(batch=64, image=224, classes=1000, lr=0.01, dist="normal"),
+    "lenet5": dict(batch=256, lr=0.05, dist="uniform"),
+    "mlp": dict(batch=1000, lr=0.1, dist="uniform"),
+}
+
+
+def build_model(name, batch=None):
+    from tinyflow_b200 import models
+    cfg = dict(WORKLOADS[name])
+    if batch is not None:
+        cfg["batch"] = batch
+    if name in ("resnet50", "vgg16"):
+        return models.BUILDERS[name](batch=cfg["batch"], classes=cfg["classes"], image=cfg["image"]), cfg
+    return models.BUILDERS[name](batch=cfg["batch"]), cfg
+
+
+def step_flops(executor):
+    """Algorithmic flops of one step: 2*M*N*K per matmul node, 2*N*K*P*Q*C*R*S per convolution node
+    (forward, backward-data and backward-filter nodes each count once)."""
+    total = 0
+    shp = executor.node_to_shape_map
+    for node in executor.topo_order:
+        kind = type(node.op).__name__
+        if kind == "MatMulOp":
+            a, out = shp[node.inputs[0]], shp[node]
+            k = a[0] if node.matmul_attr_trans_A else a[1]
+            total += 2 * out[0] * out[1] * k
+        elif kind in ("Convolution2DForwardOp", "Convolution2DBackwardOp"):
+            x, w = shp[node.inputs[0]], shp[node.inputs[1]]
+            y = shp[node] if kind == "Convolution2DForwardOp" else shp[node.inputs[2]]
+            total += 2 * y[0] * y[1] * y[2] * y[3] * w[1] * w[2] * w[3]
+    return total
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, gpu_index):
+        super().__init__(daemon=True)
+        self.gpu = gpu_index
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.stop_flag = threading.Event()
+        self.proc = None
+
+    def run(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + q, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.proc.stdout:
+            if self.stop_flag.is_set():
+                break
+            parts = [p.strip() for p in line.split(",")]
+            try:
+                self.samples.append(float(parts[0]))
+                self.max_mhz = float(parts[1])
+            except (ValueError, IndexError):
+                continue
+            for nm, val in zip(names, parts[2:]):
+                if val.lower().startswith("active"):
+                    self.reasons.add(nm)
+
+    def finish(self):
+        self.stop_flag.set()
+        if self.proc is not None:
+            self.proc.terminate()          # the exact process this sampler started
+        s = sorted(self.samples)
+        busy = [x for x in s if x > 0]
+        med = busy[len(busy) // 2] if busy else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def measured_peaks():
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU arm: the numpy restatement of the reference's operators on the same graph
+# ---------------------------------------------------------------------------------------------------
+def cpu_step_time(workload, sample_batch, repeats=1):
+    """Seconds for one fp32 training step of `workload` at batch `sample_batch` on the host cores."""
+    import numpy as np
+    from oracle.graph_eval import OracleExecutor
+    from tinyflow_b200 import autodiff as ad, models
+    model, cfg = build_model(workload, batch=sample_batch)
+    model.set_dropout(0.0)
+    ex = ad.Executor(model.loss, model.y, cfg["lr"], None, None, None, optimizer="sgd")
+    X, Y = models.synthetic_batch(model, seed=1234, input_dist=cfg["dist"])
+    feed = {model.X: X, model.y_: Y}
+    feed.update(model.init_params(seed=123))
+    orc = OracleExecutor(ex.topo_order, np.float32)
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        orc.run(feed)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def cpu_threads():
+    try:
+        from threadpoolctl import threadpool_info
+        n = max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
+    except Exception:
+        n = 1
+    return n, len(os.sched_getaffinity(0))
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import numpy as np  # noqa: F401  (loads the BLAS whose thread count is reported)
+    workload = args.workload
+    cfg = WORKLOADS[workload]
+    sample = {"resnet50": 4, "vgg16": 2}.get(workload, cfg["batch"])
+    blas_threads, cores = cpu_threads()
+    for _ in range(args.warmup if workload in ("mlp", "lenet5") else min(args.warmup, 1)):
+        cpu_step_time(workload, sample)
+    t0 = time.perf_counter()
+    per_step = [cpu_step_time(workload, sample) for _ in range(args.steps)]
+    wall = time.perf_counter() - t0
+    sec = sum(per_step) / len(per_step)
+    value = sample / sec
+    line = {
+        "impl": "reference", "metric": "train images/sec (fwd+bwd+SGD) %s" % workload, "value": value, "unit": "images/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1000.0 * cfg["batch"] / sample,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "%s b%d fp32 fwd+bwd+SGD" % (workload, cfg["batch"]), "sample": "one step at batch %d (images/s does not depend on the batch for this arm)" % sample},
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": blas_threads, "kind": "port",
+                         "sample": "numpy fp32 restatement of the reference operators, batch %d, %d steps, %d BLAS threads on %d usable cores, %.1f s" % (sample, args.steps, blas_threads, cores, wall)},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus %d needs a torchrun launch with %d ranks" % (args.gpus, args.gpus))
+    physical_gpu = local_rank
+    if world > 1:
+        # one process per GPU; the executor addresses its GPU as gpu(0), as the reference hard-codes
+        os.environ["CUDA_VISIBLE_DEVICES"] = str(local_rank)
+
+    import ctypes
+    import numpy as np
+    import torch
+    from tinyflow_b200 import autodiff as ad, gpu_op, models, ndarray
+    from tinyflow_b200._base import _LIB, check_call
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda:0"))
+        id_path = "/tmp/tinyflow_b200_nccl_id_%s" % os.environ.get("MASTER_PORT", "0")
+        check_call(_LIB.TfDpInit(rank, world, id_path.encode()))
+
+    model, cfg = build_model(args.workload)
+    model.set_dropout(0.5 if args.workload in ("resnet50", "vgg16") else 0.0)
+    ex = ad.Executor(model.loss, model.y, cfg["lr"], None, None, None, optimizer="sgd")
+    ctx = ndarray.gpu(0)
+    Xn, Yn = models.synthetic_batch(model, seed=1234, rank=rank, input_dist=cfg["dist"])
+    params = model.init_params(seed=123)          # identical on every rank
+    feed = {n: ndarray.array(v, ctx) for n, v in params.items()}
+    Xd, Yd = ndarray.array(Xn, ctx), ndarray.array(Yn, ctx)
+    # pinned host staging for the end-to-end arm
+    Xh, Yh = ndarray.array(Xn, ndarray.cpu(0)), ndarray.array(Yn, ndarray.cpu(0))
+    batch = cfg["batch"]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_resident(fd):
+        fd[model.X], fd[model.y_] = Xd, Yd
+        loss, nxt = ex.run(fd)
+        return loss, nxt
+
+    def step_e2e(fd):
+        # host -> device copy of this step's inputs from pinned memory, device -> host read of the loss
+        fd[model.X] = Xh.copyto(ctx, None)
+        fd[model.y_] = Yh.copyto(ctx, None)
+        loss, nxt = ex.run(fd)
+        if world > 1:
+            check_call(_LIB.TfDpFlush(ex.cudaStream))
+        return loss.asnumpy(), nxt
+
+    def flush_dp():
+        if world > 1:
+            check_call(_LIB.TfDpFlush(ex.cudaStream))
+
+    for _ in range(args.warmup):
+        loss, feed = step_resident(feed)
+    flush_dp()
+    barrier()
+    flops = step_flops(ex)
+
+    # ---- timed region 1: inputs resident in HBM, device-timed with CUDA events on the executor's stream
+    stream_ptr = ctypes.cast(ex.cudaStream, ctypes.POINTER(ctypes.c_void_p)).contents.value
+    ext = torch.cuda.ExternalStream(stream_ptr)
+    sampler = ClockSampler(physical_gpu)
+    sampler.start()
+    time.sleep(0.3)
+    n0 = gpu_op.launch_count()
+    _LIB.TfKernelTimingEnable(1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_wall0 = time.perf_counter()
+    e0.record(ext)
+    for _ in range(args.steps):
+        loss, feed = step_resident(feed)
+    flush_dp()
+    e1.record(ext)
+    barrier()
+    wall = time.perf_counter() - t_wall0
+    dev_ms = e0.elapsed_time(e1)
+    launches = gpu_op.launch_count() - n0
+    report = ctypes.create_string_buffer(1 << 16)
+    _LIB.TfKernelTimingReport(report, len(report))
+    _LIB.TfKernelTimingEnable(0)
+    clocks = sampler.finish()
+    kernel_rows = json.loads(report.value.decode() or "[]")
+    final_loss = float(loss.asnumpy()[0])
+
+    # ---- timed region 2: end to end through the public API with host buffers
+    for _ in range(2):
+        _, feed = step_e2e(feed)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        lv, feed = step_e2e(feed)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+
+    ms = torch.tensor([max(dev_ms, 0.0), wall * 1000.0, e2e_s * 1000.0], dtype=torch.float64, device="cuda:0")
+    if dist is not None:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    dev_ms, wall_ms, e2e_ms = [float(x) for x in ms.tolist()]
+    # the CPU can run ahead of the GPU, never behind the device-side events by more than the queue depth:
+    # the slower of the two clocks is the honest step time
+    step_ms = max(dev_ms, wall_ms) / args.steps
+    value = world * batch / (step_ms / 1000.0)
+    e2e_value = world * batch / (e2e_ms / 1000.0 / args.steps)
+
+    peaks, peak_kind = measured_peaks()
+    roofline = None
+    if kernel_rows:
+        top = max(kernel_rows, key=lambda r: r["ms"])
+        total_ms = sum(r["ms"] for r in kernel_rows)
+        if top["flops"] > 0:
+            # 3xTF32 issues three tensor-core MMAs per algorithmic multiply-add; the denominator is the measured
+            # bf16 rate halved (TF32 runs at half the bf16 rate), sustained figure because the kernel runs inside a long step
+            peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) / 2.0
+            ach = top["flops"] / (top["ms"] / 1000.0) / 1e12
+            roofline = {"bound": "tensor", "kernel": top["name"], "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                        "traffic": None, "launches": top["launches"], "avg_us": 1000.0 * top["ms"] / max(top["launches"], 1),
+                        "peak_source": "%s bf16 sustained / 2 (tf32); algorithmic flops, issued tensor flops are 3x" % peak_kind,
+                        "share_of_timed_kernels": top["ms"] / total_ms if total_ms else None}
+        else:
+            peak = peaks["hbm_gbs"]
+            ach = top["bytes"] / (top["ms"] / 1000.0) / 1e9
+            roofline = {"bound": "hbm", "kernel": top["name"], "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
+                        "traffic": None, "launches": top["launches"], "avg_us": 1000.0 * top["ms"] / max(top["launches"], 1),
+                        "peak_source": peak_kind + " copy bandwidth"}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sample = {"resnet50": 4, "vgg16": 2}.get(args.workload, batch)
+        t = cpu_step_time(args.workload, sample)
+        threads, cores = cpu_threads()
+        cpu_baseline = {"value": sample / t, "unit": "images/s", "cores": threads, "kind": "port",
+                        "sample": "numpy fp32 restatement of the reference operators, one step at batch %d (%.1f s), %d BLAS threads on %d usable cores" % (sample, t, threads, cores)}
+
+    if rank == 0:
+        line = {
+            "metric": "train images/sec (fwd+bwd+SGD) %s" % args.workload, "value": value, "unit": "images/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "%s b%d/GPU %s fp32 fwd+bwd+SGD" % (args.workload, batch, "x".join(str(d) for d in model.input_shape[1:])),
+                       "global_batch": world * batch, "parallelism": "dp%d" % world, "l2": "per-step working set (GBs of activations) exceeds the 126 MB L2",
+                       "dropout": 0.5 if model.dropout_nodes else 0.0, "device_ms_per_step": dev_ms / args.steps, "host_ms_per_step": wall_ms / args.steps,
+                       "algorithmic_tflop_per_step": flops / 1e12, "final_loss": final_loss},
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(Xn.nbytes + Yn.nbytes), "d2h_bytes_per_step": 4},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": roofline,
+            "cpu_baseline": cpu_baseline,
+            "kernels": sorted(kernel_rows, key=lambda r: -r["ms"])[:8],
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        _LIB.TfDpShutdown()
+        dist.destroy_process_group()
+    sys.stdout.flush()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -271,6 +271,8 @@ int TfDpShutdown(void);
 int TfPoolingArgmax(const DLArrayHandle input, int32_t *indices_dev, void ***cudnnlist,
                     void **cudaStream);   /* first-maximum index (h*W+w in the input plane) per output */
 int TfDeviceSynchronize(void);
+int TfKernelTimingEnable(int level);      /* CUDA-event timing per kernel family: 0 off, 1 contractions, 2 all; resets the table */
+int TfKernelTimingReport(char *buf, int buflen);  /* JSON rows {name, launches, ms, flops, bytes} */
 int TfLaunchCount(long long *count);      /* kernels launched by this library so far */
 int TfSetContractionPath(int path);       /* 0 = auto, 1 = force CUDA-core path, 2 = force tcgen05 path */
 int TfLastError(char *buf, int buflen);   /* message of the last -1 return on this thread */

@@ -20,7 +20,7 @@ class OracleExecutor:
         self.dtype = dtype
         self.values = {}
         self.dropout_seeds = dropout_seeds or {}    # DropoutForward node -> seed used by the GPU run
-        self._geom = {}
+        self.adam_powers = None     # (b1^t, b2^t) of the step being checked; default: the node's current values
 
     def _conv_geom(self, node, x, w):
         return ops.conv_geometry(x.shape, w.shape, node.padding, node.u, node.v)
@@ -148,7 +148,8 @@ class OracleExecutor:
             self.values[node.inputs[0]] = ops.sgd(ins[0], ins[1], node.learning_rate)
             return None
         if kind == "AdamOp":
-            w, m, vv = ops.adam(ins[0], ins[1], ins[2], ins[3], dt(node.b1), dt(node.b2), dt(node.b1t[0]), dt(node.b2t[0]), dt(node.e), dt(node.learning_rate))
+            b1t, b2t = self.adam_powers if self.adam_powers else (node.b1t[0], node.b2t[0])
+            w, m, vv = ops.adam(ins[0], ins[1], ins[2], ins[3], dt(node.b1), dt(node.b2), dt(b1t), dt(b2t), dt(node.e), dt(node.learning_rate))
             self.values[node.inputs[0]], self.values[node.inputs[1]], self.values[node.inputs[2]] = w, m, vv
             return None
         if kind == "ExpOp":

@@ -1,0 +1,207 @@
+"""Graph-level parity: a full training step (forward + backward + optimiser) of each benchmark
+graph through the mirrored executor and the C-ABI, against the CPU oracle on the same seeded
+inputs.  Two checks per graph:
+
+* end to end: loss and every parameter gradient within rel 1e-4 of the float64 oracle;
+* node by node: every node's GPU output against the oracle applied to that node's GPU inputs,
+  which localises any disagreement to one kernel.
+"""
+import importlib.util
+import json
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def rel_err(got, want, floor=1e-3):
+    want = np.asarray(want, np.float64)
+    got = np.asarray(got, np.float64)
+    scale = np.maximum(np.abs(want), floor * max(np.abs(want).max(), 1e-30))
+    return float((np.abs(got - want) / scale).max())
+
+
+def run_step(model, feed_np, lr, optimizer="sgd", dropout=0.0):
+    from tinyflow_b200 import autodiff as ad, ndarray
+    model.set_dropout(dropout)
+    ex = ad.Executor(model.loss, model.y, lr, None, None, None, optimizer=optimizer)
+    ctx = ndarray.gpu(0)
+    feed = {n: ndarray.array(v, ctx) for n, v in feed_np.items()}
+    if optimizer == "adam":
+        for var in model.param_shapes:
+            m, v = ex.Variable_node_to_mv[var]
+            feed[m] = ndarray.array(np.zeros(model.param_shapes[var], np.float32), ctx)
+            feed[v] = ndarray.array(np.zeros(model.param_shapes[var], np.float32), ctx)
+    loss, next_feed = ex.run(feed)
+    return ex, loss, next_feed
+
+
+def oracle_step(ex, feed_np, dtype=np.float64):
+    from oracle.graph_eval import OracleExecutor
+    seeds = {n: n.seed[0] for n in ex.topo_order if hasattr(n, "seed")}
+    orc = OracleExecutor(ex.topo_order, dtype, dropout_seeds=seeds)
+    orc.adam_powers = (ex.b1t[0] / ex.b1, ex.b2t[0] / ex.b2)     # the powers the finished step used
+    feed = dict(feed_np)
+    for n in ex.topo_order:
+        if not n.inputs and n not in feed:            # Adam moments
+            base = next(v for v, mv in ex.Variable_node_to_mv.items() if n in mv)
+            feed[n] = np.zeros_like(feed_np[base])
+    # gradients are read before the optimiser node overwrites the parameter, so keep copies
+    vals = orc.run(feed)
+    return orc, vals
+
+
+def check_end_to_end(ex, model, feed_np, loss, next_feed, lr, rel=1e-4):
+    orc, vals = oracle_step(ex, feed_np)
+    assert rel_err(loss.asnumpy(), vals[model.loss]) <= rel, "loss"
+    worst = 0.0
+    for var in model.param_shapes:
+        gnode = ex.Variable_node_to_grad[var]
+        e = rel_err(ex.value_of(gnode).asnumpy(), vals[gnode])
+        worst = max(worst, e)
+        assert e <= rel, "gradient of %s: rel err %.3e" % (var.name, e)
+        if ex.optimizer == "sgd":
+            want = feed_np[var].astype(np.float64) - np.float32(lr) * vals[gnode]
+            assert rel_err(next_feed[var].asnumpy(), want) <= 1e-5, "updated %s" % var.name
+    return worst
+
+
+def check_node_by_node(ex, feed_np, rel=1e-4):
+    """Each node's GPU output vs the oracle evaluated on that node's own GPU inputs (parameters are
+    taken from the feed, because the optimiser nodes have already updated them in place)."""
+    from oracle.graph_eval import OracleExecutor
+    seeds = {n: n.seed[0] for n in ex.topo_order if hasattr(n, "seed")}
+    orc = OracleExecutor(ex.topo_order, np.float64, dropout_seeds=seeds)
+    worst = ("", 0.0)
+    for node in ex.topo_order:
+        if not node.inputs or node.issgd:
+            continue
+        ins = [np.asarray(feed_np[i], np.float64) if i in feed_np else ex.value_of(i).asnumpy().astype(np.float64) for i in node.inputs]
+        want = orc._eval(node, ins)
+        got = ex.value_of(node).asnumpy()
+        e = rel_err(got, want.reshape(got.shape))
+        if e > worst[1]:
+            worst = ("%d:%s%s" % (node.index, node.name, tuple(got.shape)), e)
+        assert e <= rel, "node %d (%s) %s: rel err %.3e" % (node.index, node.name, got.shape, e)
+    return worst
+
+
+def test_mlp_benchmark_config_against_reference_digest_and_oracle(lib_path):
+    """Configuration 1: MLP 784-256-100-10, batch 1000, one SGD step with lr 0.1.  The expected loss and
+    gradient samples come from the reference's own numpy executor (tests/golden/mlp_c1_digest.json)."""
+    from tinyflow_b200 import models
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(GOLDEN, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    d = json.load(open(os.path.join(GOLDEN, "mlp_c1_digest.json")))
+    X, Y, Ws, bs = mg.mlp_inputs(tuple(d["sizes"]), d["batch"], d["seed"])
+    bs = [np.zeros_like(b) for b in bs]
+    model = models.mlp(batch=d["batch"], sizes=tuple(d["sizes"]))
+    feed_np = {model.X: X, model.y_: Y}
+    feed_np.update(dict(zip(model.param_shapes, Ws + bs)))
+    ex, loss, nxt = run_step(model, feed_np, 0.1)
+    assert abs(float(loss.asnumpy()[0]) - d["loss"]) <= 1e-4 * abs(d["loss"])
+    for var in model.param_shapes:
+        gd = d["grads"][var.name]
+        g = ex.gradient_of(var).asnumpy().reshape(-1).astype(np.float64)
+        scale = max(gd["abs_sum"] / g.size, 1e-30)
+        assert abs(np.abs(g).sum() - gd["abs_sum"]) <= 1e-4 * gd["abs_sum"]
+        assert np.all(np.abs(g[gd["index"]] - np.array(gd["value"])) <= 1e-4 * np.maximum(np.abs(gd["value"]), scale))
+    check_end_to_end(ex, model, feed_np, loss, nxt, 0.1)
+    check_node_by_node(ex, feed_np)
+
+
+def test_mlp_small_against_reference_numpy_executor(lib_path):
+    from tinyflow_b200 import models
+    g = np.load(os.path.join(GOLDEN, "mlp_small.npz"))
+    model = models.mlp(batch=8, sizes=(12, 20, 16, 5))
+    feed_np = {model.X: g["X"], model.y_: g["Y"]}
+    feed_np.update({p: g[p.name] for p in model.param_shapes})
+    ex, loss, nxt = run_step(model, feed_np, 0.1)
+    assert rel_err(loss.asnumpy(), g["loss"]) <= 1e-4
+    for var in model.param_shapes:
+        assert rel_err(ex.gradient_of(var).asnumpy(), g["g" + var.name]) <= 1e-4, var.name
+
+
+def _feed(model, seed=1234, input_dist="normal"):
+    from tinyflow_b200 import models
+    X, Y = models.synthetic_batch(model, seed=seed, input_dist=input_dist)
+    feed = {model.X: X, model.y_: Y}
+    feed.update(model.init_params(seed=123))
+    return feed
+
+
+def test_lenet5_benchmark_config(lib_path):
+    """Configuration 2: LeNet-5, batch 256, 1x28x28 inputs in [0,1), He-normal init, one SGD step."""
+    from tinyflow_b200 import models
+    model = models.lenet5(batch=256)
+    feed_np = _feed(model, input_dist="uniform")
+    ex, loss, nxt = run_step(model, feed_np, 0.05)
+    check_end_to_end(ex, model, feed_np, loss, nxt, 0.05)
+    check_node_by_node(ex, feed_np)
+
+
+@pytest.mark.parametrize("optimizer", ["sgd", "adam"])
+def test_vgg16_reduced(lib_path, optimizer):
+    """VGG-16 graph (all 13 conv + 3 FC layers) at batch 4, 32x32 images."""
+    from tinyflow_b200 import models
+    model = models.vgg16(batch=4, image=32, classes=1000)
+    feed_np = _feed(model)
+    ex, loss, nxt = run_step(model, feed_np, 0.01, optimizer=optimizer)
+    check_node_by_node(ex, feed_np)
+    check_end_to_end(ex, model, feed_np, loss, nxt, 0.01, rel=1e-4)
+    if optimizer == "adam":
+        orc, vals = oracle_step(ex, feed_np)
+        for var in model.param_shapes:
+            assert rel_err(nxt[var].asnumpy(), vals[var]) <= 1e-4, var.name
+
+
+def test_resnet50_reduced_node_by_node(lib_path):
+    """ResNet-50 graph (all 53 convs, 53 per-activation batch-norms) at batch 8, 64x64 images, dropout active."""
+    from tinyflow_b200 import models
+    model = models.resnet50(batch=8, image=64, classes=1000)
+    feed_np = _feed(model)
+    ex, loss, nxt = run_step(model, feed_np, 0.01, dropout=0.5)
+    worst = check_node_by_node(ex, feed_np)
+    print("worst node", worst)
+    assert np.isfinite(loss.asnumpy()).all()
+
+
+def test_resnet50_reduced_end_to_end(lib_path):
+    from tinyflow_b200 import models
+    model = models.resnet50(batch=8, image=64, classes=1000)
+    feed_np = _feed(model)
+    ex, loss, nxt = run_step(model, feed_np, 0.01, dropout=0.0)
+    orc, vals = oracle_step(ex, feed_np)
+    assert rel_err(loss.asnumpy(), vals[model.loss]) <= 1e-4
+    errs = {var.name: rel_err(ex.gradient_of(var).asnumpy(), vals[ex.Variable_node_to_grad[var]]) for var in model.param_shapes}
+    bad = {k: v for k, v in errs.items() if v > 1e-4}
+    print("max gradient rel err", max(errs.values()))
+    assert not bad, bad
+
+
+def test_two_steps_reuse_pool_and_stay_finite(lib_path):
+    from tinyflow_b200 import models, ndarray
+    from tinyflow_b200._base import _LIB
+    import ctypes
+    model = models.resnet50(batch=4, image=64, classes=100)
+    feed_np = _feed(model)
+    ex, loss, nxt = run_step(model, feed_np, 0.01)
+    ctx = ndarray.gpu(0)
+    losses = [float(loss.asnumpy()[0])]
+    used = []
+    for _ in range(3):
+        nxt[model.X] = ndarray.array(feed_np[model.X], ctx)
+        nxt[model.y_] = ndarray.array(feed_np[model.y_], ctx)
+        loss, nxt = ex.run(nxt)
+        losses.append(float(loss.asnumpy()[0]))
+        a, b = ctypes.c_longlong(0), ctypes.c_longlong(0)
+        _LIB.TfAllocatorStats(ctypes.byref(a), ctypes.byref(b))
+        used.append(a.value + b.value)
+    assert all(np.isfinite(losses))
+    assert losses[-1] < losses[0]               # SGD on a fixed batch makes progress
+    assert used[-1] == used[0]                  # steady state: no new device memory after the first steps

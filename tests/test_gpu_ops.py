@@ -1,0 +1,410 @@
+"""Per-operator parity: every CUDA entry point, called through the C-ABI wrappers, against the
+CPU oracle on the same seeded inputs.  Tolerance for floating point: |got - want| <=
+1e-4 * max(|want|, 1e-3 * max|want|); indices and masks bit-exact."""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+RNG = np.random.RandomState(42)
+
+
+def close(got, want, rel=1e-4, floor=1e-3, what=""):
+    want = np.asarray(want, dtype=np.float64)
+    got = np.asarray(got, dtype=np.float64)
+    assert got.shape == want.shape, (what, got.shape, want.shape)
+    scale = np.maximum(np.abs(want), floor * (np.abs(want).max() if want.size else 1.0))
+    err = np.abs(got - want) / np.maximum(scale, 1e-30)
+    assert np.all(np.isfinite(got)), what
+    assert err.max() <= rel if err.size else True, "%s: max rel err %.3e at %s" % (what, err.max(), np.unravel_index(err.argmax(), err.shape))
+
+
+@pytest.fixture(scope="module")
+def env(lib_path):
+    from tinyflow_b200 import gpu_op, ndarray
+    import oracle.ops as ops
+
+    class Env:
+        pass
+    e = Env()
+    e.gpu_op, e.nd, e.ops = gpu_op, ndarray, ops
+    e.ctx = ndarray.gpu(0)
+    e.stream = gpu_op.create_cudaStream()
+    e.cudnn = gpu_op.create_cudnnHandle(e.stream)
+    e.cublas = gpu_op.create_cublasHandle(e.stream)
+    e.dev = lambda a: ndarray.array(np.asarray(a, dtype=np.float32), e.ctx)
+    e.empty = lambda s: ndarray.empty(s, e.ctx)
+    return e
+
+
+def f32(*shape, scale=1.0):
+    return (RNG.randn(*shape) * scale).astype(np.float32)
+
+
+# ---- runtime -----------------------------------------------------------------------------------
+def test_alloc_copy_roundtrip_and_block_reuse(env):
+    a = f32(37, 5)
+    d = env.dev(a)
+    np.testing.assert_array_equal(d.asnumpy(), a)
+    ptr = d.data_ptr
+    del d
+    d2 = env.empty((37, 5))
+    assert d2.data_ptr == ptr          # same size comes back from the pool
+    h = env.nd.array(a, env.nd.cpu(0))  # pinned host array
+    d3 = h.copyto(env.ctx, env.stream)
+    np.testing.assert_array_equal(d3.asnumpy(), a)
+    back = d3.copyto(env.nd.cpu(0), env.stream)
+    np.testing.assert_array_equal(back.asnumpy(), a)
+
+
+def test_soft_out_of_memory_protocol(env):
+    """A failed device allocation returns the missing byte count instead of an array (c_runtime_api.cc:109-114)."""
+    res = env.nd.empty((1 << 20, 1 << 20), env.ctx)       # 4 TiB
+    assert isinstance(res, int) and res > 0
+    ok = env.empty((4, 4))
+    assert isinstance(ok, env.nd.NDArray)
+
+
+def test_array_set_and_scalars(env):
+    d = env.empty((13, 7))
+    env.gpu_op.array_set(d, 2.5, env.stream)
+    np.testing.assert_array_equal(d.asnumpy(), np.full((13, 7), 2.5, np.float32))
+    a = f32(1001)
+    o = env.empty((1001,))
+    env.gpu_op.matrix_elementwise_add_by_const(env.dev(a), 1.25, o, env.stream)
+    np.testing.assert_array_equal(o.asnumpy(), a + np.float32(1.25))
+    env.gpu_op.matrix_elementwise_multiply_by_const(env.dev(a), -3.0, o, env.stream)
+    np.testing.assert_array_equal(o.asnumpy(), a * np.float32(-3.0))
+
+
+@pytest.mark.parametrize("n", [1, 3, 4, 1023, 4096, 100003])
+def test_elementwise_binary(env, n):
+    a, b = f32(n), f32(n)
+    o = env.empty((n,))
+    env.gpu_op.matrix_elementwise_add(env.dev(a), env.dev(b), o, env.stream)
+    np.testing.assert_array_equal(o.asnumpy(), a + b)
+    env.gpu_op.matrix_elementwise_multiply(env.dev(a), env.dev(b), o, env.stream)
+    np.testing.assert_array_equal(o.asnumpy(), a * b)
+    env.gpu_op.relu(env.dev(a), o)
+    np.testing.assert_array_equal(o.asnumpy(), np.maximum(a, 0))
+    env.gpu_op.relu_gradient(env.dev(a), env.dev(b), o)
+    np.testing.assert_array_equal(o.asnumpy(), np.where(a > 0, b, 0))
+
+
+def test_add_in_place_aliasing(env):
+    a, b = f32(777), f32(777)
+    da = env.dev(a)
+    env.gpu_op.matrix_elementwise_add(da, env.dev(b), da, env.stream)
+    np.testing.assert_array_equal(da.asnumpy(), a + b)
+
+
+def test_broadcast(env):
+    b = f32(100)
+    o = env.empty((64, 100))
+    env.gpu_op.broadcast_to(env.dev(b), o, "NHWC", env.stream)
+    np.testing.assert_array_equal(o.asnumpy(), np.broadcast_to(b, (64, 100)))
+    one = f32(1)
+    env.gpu_op.broadcast_to(env.dev(one), o, "NHWC", env.stream)
+    np.testing.assert_array_equal(o.asnumpy(), np.full((64, 100), one[0]))
+    c = f32(6)
+    o4 = env.empty((5, 6, 7, 3))
+    env.gpu_op.broadcast_to(env.dev(c), o4, "NCHW", env.stream)
+    np.testing.assert_array_equal(o4.asnumpy(), env.ops.broadcast_channel(c, (5, 6, 7, 3)))
+
+
+@pytest.mark.parametrize("shape,out", [((64, 4096), (4096,)), ((1000, 10), (10,)), ((64, 1000), (1,)), ((7, 33), (33,)), ((4096, 3), (3,))])
+def test_reduce_sum_bias_and_scalar(env, shape, out):
+    x = f32(*shape)
+    ins, outs = env.gpu_op.reduce_sum_get_real_shape(shape, out, "NHWC")
+    cell = env.gpu_op.reduce_sum_get_cudnnlist(ins, outs, "NHWC", env.cudnn)
+    o = env.empty(out)
+    assert env.gpu_op.reduce_sum_new(env.dev(x), o, cell, env.cudnn, env.stream) == 0
+    want = env.ops.reduce_sum(x.astype(np.float64), ins, outs).reshape(out)
+    close(o.asnumpy(), want, what="reduce_sum %s" % (shape,))
+
+
+def test_reduce_sum_channel(env):
+    x = f32(6, 5, 7, 9)
+    ins, outs = env.gpu_op.reduce_sum_get_real_shape(x.shape, (5,), "NCHW")
+    cell = env.gpu_op.reduce_sum_get_cudnnlist(ins, outs, "NCHW", env.cudnn)
+    o = env.empty((5,))
+    env.gpu_op.reduce_sum_new(env.dev(x), o, cell, env.cudnn, env.stream)
+    close(o.asnumpy(), x.astype(np.float64).sum(axis=(0, 2, 3)), what="channel reduce")
+
+
+def test_legacy_reductions(env):
+    x = f32(50, 70)
+    o = env.empty((70,))
+    env.gpu_op.reduce_sum_axis_zero(env.dev(x), o)
+    close(o.asnumpy(), x.astype(np.float64).sum(axis=0))
+    x3 = f32(4, 6, 5)
+    o2 = env.empty((4, 5))
+    env.gpu_op.reduce_sum(env.dev(x3), o2, axis=1)
+    close(o2.asnumpy(), x3.astype(np.float64).sum(axis=1))
+    o3 = env.empty((1,))
+    env.gpu_op.reduce_sum(env.dev(x3), o3, axis=-1)
+    close(o3.asnumpy(), [x3.astype(np.float64).sum()])
+    back = env.empty((4, 6, 5))
+    env.gpu_op.reduce_sum_backward(o2, back, 1)
+    np.testing.assert_array_equal(back.asnumpy(), np.repeat(o2.asnumpy()[:, None, :], 6, axis=1))
+
+
+# ---- matmul: the three shapes the reference asserts (tests/test_gpu_op.py:103-131) plus odd ones ------------
+MATMUL = [(500, 700, 1000, False, False), (1000, 500, 2000, False, True), (1000, 500, 2000, True, True),
+          (1000, 784, 256, False, False), (784, 1000, 256, True, False), (1000, 10, 100, False, True),
+          (64, 2048, 2048, False, False), (64, 2048, 1000, True, False), (3, 5, 7, False, False), (129, 65, 33, True, True)]
+
+
+@pytest.mark.parametrize("M,K,N,tA,tB", MATMUL)
+@pytest.mark.parametrize("path", [0, 1])
+def test_matmul(env, M, K, N, tA, tB, path):
+    A = f32(*((K, M) if tA else (M, K)))
+    B = f32(*((N, K) if tB else (K, N)))
+    C = env.empty((M, N))
+    env.gpu_op.set_contraction_path(path)
+    try:
+        env.gpu_op.matrix_multiply(env.dev(A), tA, env.dev(B), tB, C, env.cublas, env.stream)
+    finally:
+        env.gpu_op.set_contraction_path(0)
+    a64, b64 = A.astype(np.float64), B.astype(np.float64)
+    want = (a64.T if tA else a64) @ (b64.T if tB else b64)
+    close(C.asnumpy(), want, what="matmul %s" % ((M, K, N, tA, tB),))
+
+
+# ---- softmax family ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(1000, 10), (64, 1000), (3, 1), (257, 33)])
+def test_softmax_and_cross_entropy(env, rows, cols):
+    x = f32(rows, cols, scale=3.0)
+    t = np.eye(cols, dtype=np.float32)[RNG.randint(0, cols, rows)]
+    o = env.empty((rows, cols))
+    env.gpu_op.softmax(env.dev(x), o, env.stream)
+    close(o.asnumpy(), env.ops.softmax_rows(x.astype(np.float64)), what="softmax")
+    l = env.empty((1,))
+    env.gpu_op.softmax_cross_entropy(env.dev(x), env.dev(t), l, env.stream)
+    close(l.asnumpy(), env.ops.softmax_cross_entropy(x.astype(np.float64), t.astype(np.float64)), what="softmax-CE")
+
+
+def test_activation_modes(env):
+    for shape in [(8, 1, 1000), (4, 3, 5, 7)]:
+        x, dy = f32(*shape), f32(*shape)
+        x64, dy64 = x.astype(np.float64), dy.astype(np.float64)
+        for mode, fwd, bwd in [("relu", env.ops.relu, lambda y: env.ops.relu_grad(x64, dy64)),
+                               ("sigmoid", env.ops.sigmoid, lambda y: dy64 * y * (1 - y)),
+                               ("tanh", np.tanh, lambda y: dy64 * (1 - y * y)),
+                               ("softmax", env.ops.softmax_instance, lambda y: env.ops.softmax_instance_bwd(y, dy64))]:
+            cell = env.gpu_op.activation_get_cudnnlist(shape, "NCHW", mode)
+            y, dx = env.empty(shape), env.empty(shape)
+            dxd = env.dev(x)
+            env.gpu_op.activation_forward(dxd, y, mode, cell, env.cudnn, env.stream)
+            want_y = fwd(x64)
+            close(y.asnumpy(), want_y, what="act fwd " + mode)
+            env.gpu_op.activation_backward(dxd, dx, y, env.dev(dy), mode, cell, env.cudnn, env.stream)
+            close(dx.asnumpy(), bwd(want_y), rel=2e-4 if mode == "softmax" else 1e-4, what="act bwd " + mode)
+
+
+def test_relu_propagates_nan(env):
+    x = np.array([np.nan, -1.0, 2.0, 0.0] * 3, np.float32)
+    cell = env.gpu_op.activation_get_cudnnlist(x.shape, "NCHW", "relu") if False else None
+    o = env.empty(x.shape)
+    env.gpu_op.relu(env.dev(x), o)
+    got = o.asnumpy()
+    assert np.isnan(got[0]) and got[1] == 0 and got[2] == 2 and got[3] == 0
+
+
+def test_cross_and_cross_backward(env):
+    p = (np.abs(RNG.randn(64, 1000)) + 0.05).astype(np.float32)
+    t = np.eye(1000, dtype=np.float32)[RNG.randint(0, 1000, 64)]
+    d = f32(64, 1000)
+    b = 1.0 / p.size
+    o = env.empty(p.shape)
+    env.gpu_op.cross(env.dev(p), env.dev(t), o, b, env.stream)
+    close(o.asnumpy(), env.ops.cross(p.astype(np.float64), t, b), floor=1e-6, what="cross")
+    env.gpu_op.cross_backward(env.dev(p), env.dev(t), env.dev(d), o, b, env.stream)
+    close(o.asnumpy(), env.ops.cross_backward(p.astype(np.float64), t, d.astype(np.float64), b), floor=1e-6, what="cross bwd")
+
+
+def test_concat_forward_and_split(env):
+    a, b = f32(4, 5, 6, 7), f32(4, 9, 6, 7)
+    o = env.empty((4, 14, 6, 7))
+    env.gpu_op.concat_forward(env.dev(a), env.dev(b), o, env.stream)
+    np.testing.assert_array_equal(o.asnumpy(), np.concatenate([a, b], axis=1))
+    da, db = env.empty(a.shape), env.empty(b.shape)
+    env.gpu_op.concat_a_backward(env.dev(a), env.dev(b), o, da, env.stream)
+    env.gpu_op.concat_b_backward(env.dev(a), env.dev(b), o, db, env.stream)
+    np.testing.assert_array_equal(da.asnumpy(), a)
+    np.testing.assert_array_equal(db.asnumpy(), b)
+
+
+# ---- convolution ---------------------------------------------------------------------------------------------
+CONV = [
+    # N, C, H, W, K, R, S, padding, sh, sw
+    (2, 3, 9, 9, 4, 3, 3, "SAME", 1, 1),
+    (3, 8, 15, 15, 16, 1, 1, "VALID", 1, 1),
+    (2, 16, 14, 14, 32, 1, 1, "VALID", 2, 2),
+    (2, 3, 29, 29, 8, 7, 7, "VALID", 2, 2),
+    (4, 1, 28, 28, 6, 5, 5, "SAME", 1, 1),
+    (4, 6, 14, 14, 16, 5, 5, "VALID", 1, 1),
+    (2, 12, 17, 17, 20, 1, 7, "SAME", 1, 1),
+    (2, 12, 17, 17, 20, 7, 1, "SAME", 1, 1),
+    (2, 10, 13, 13, 12, 3, 3, "VALID", 2, 2),
+    (2, 64, 55, 55, 64, 3, 3, "SAME", 1, 1),
+    (2, 64, 55, 55, 256, 1, 1, "VALID", 1, 1),
+    (2, 256, 55, 55, 128, 1, 1, "VALID", 2, 2),
+    (2, 128, 28, 28, 128, 3, 3, "SAME", 1, 1),
+    (4, 512, 7, 7, 512, 3, 3, "SAME", 1, 1),
+    (4, 512, 7, 7, 2048, 1, 1, "VALID", 1, 1),
+    (3, 96, 14, 14, 160, 3, 3, "SAME", 1, 1),
+    (2, 40, 9, 9, 72, 1, 1, "SAME", 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", CONV)
+@pytest.mark.parametrize("path", [0, 1])
+def test_conv_forward_backward(env, case, path):
+    N, C, H, W, K, R, S, padding, sh, sw = case
+    x, w = f32(N, C, H, W), f32(K, C, R, S, scale=0.2)
+    g = env.ops.conv_geometry(x.shape, w.shape, padding, sh, sw)
+    out_shape, cell = env.gpu_op.convolution_2d_forward_get_out_shape(x.shape, w.shape, "NCHW", padding, sh, sw)
+    assert out_shape == (N, K, g["P"], g["Q"])
+    dy = f32(*out_shape)
+    dx_, dw_, dy_ = env.dev(x), env.dev(w), env.dev(dy)
+    y, dx, dw = env.empty(out_shape), env.empty(x.shape), env.empty(w.shape)
+    env.gpu_op.set_contraction_path(path)
+    try:
+        assert env.gpu_op.convolution_2d_forward(dx_, dw_, y, cell, env.cudnn, env.stream) == 0
+        assert env.gpu_op.convolution_backward_data(dx_, dy_, dw_, dx, cell, env.cudnn, env.stream) == 0
+        assert env.gpu_op.convolution_backward_filter(dx_, dy_, dw_, dw, cell, env.cudnn, env.stream) == 0
+    finally:
+        env.gpu_op.set_contraction_path(0)
+    x64, w64, dy64 = x.astype(np.float64), w.astype(np.float64), dy.astype(np.float64)
+    close(y.asnumpy(), env.ops.conv2d_fwd(x64, w64, g), what="conv fwd %s" % (case,))
+    close(dx.asnumpy(), env.ops.conv2d_dgrad(dy64, w64, g), what="conv dgrad %s" % (case,))
+    close(dw.asnumpy(), env.ops.conv2d_wgrad(x64, dy64, g), what="conv wgrad %s" % (case,))
+
+
+# ---- pooling ---------------------------------------------------------------------------------------------------
+POOL = [(2, 3, 8, 8, 0, 0, 2, 2, 2, 2), (2, 4, 112, 112, 0, 0, 2, 2, 3, 3), (2, 3, 24, 24, 3, 3, 1, 1, 1, 1),
+        (3, 5, 7, 7, 0, 0, 1, 1, 7, 7), (2, 6, 17, 17, 1, 1, 1, 1, 3, 3), (2, 6, 17, 17, 0, 0, 2, 2, 3, 3), (1, 2, 8, 8, 0, 0, 1, 1, 8, 8)]
+
+
+@pytest.mark.parametrize("case", POOL)
+@pytest.mark.parametrize("mode", ["max", "mean"])
+def test_pooling(env, case, mode):
+    N, C, H, W, ph, pw, sh, sw, kh, kw = case
+    x = f32(N, C, H, W)
+    if mode == "max":
+        x[0, 0, :4, :4] = 0.0        # a block of ties
+    g = env.ops.pool_geometry(x.shape, ph, pw, sh, sw, kh, kw)
+    out_shape, cell = env.gpu_op.pooling_2d_forward_get_out_shape(x.shape, "NCHW", mode, ph, pw, sh, sw, kh, kw)
+    assert out_shape == (N, C, g["P"], g["Q"])
+    dy = f32(*out_shape)
+    xd, y, dx = env.dev(x), env.empty(out_shape), env.empty(x.shape)
+    env.gpu_op.pooling_2d_forward(xd, y, cell, env.cudnn, env.stream)
+    env.gpu_op.pooling_2d_backward(xd, y, env.dev(dy), dx, cell, env.cudnn, env.stream)
+    if mode == "max":
+        want_y, want_idx = env.ops.maxpool_fwd(x, g)
+        np.testing.assert_array_equal(y.asnumpy(), want_y)        # a selection: exact
+        from tinyflow_b200._base import _LIB
+        idx_buf = env.empty(out_shape)                           # 4-byte elements: reuse as an int32 buffer
+        _LIB.TfPoolingArgmax(xd.handle, ctypes.c_void_p(idx_buf.data_ptr), cell, env.stream)
+        got_idx = idx_buf.asnumpy().view(np.int32)
+        np.testing.assert_array_equal(got_idx, want_idx)         # indices bit-exact
+        close(dx.asnumpy(), env.ops.maxpool_bwd(x.astype(np.float64), dy.astype(np.float64), g), what="maxpool bwd")
+    else:
+        close(y.asnumpy(), env.ops.avgpool_fwd(x.astype(np.float64), g), what="avgpool fwd")
+        close(dx.asnumpy(), env.ops.avgpool_bwd(dy.astype(np.float64), g), what="avgpool bwd")
+
+
+# ---- batch normalisation ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape,mode", [((64, 8, 7, 9), "pre_activation"), ((5, 3, 4, 4), "pre_activation"), ((32, 6, 5, 5), "pre_activation"),
+                                         ((100, 2, 3, 3), "pre_activation"), ((64, 1, 1000), "pre_activation"), ((8, 5, 6, 7), "spatial"),
+                                         ((64, 3, 55, 55), "pre_activation")])
+def test_batchnorm(env, shape, mode):
+    x, dy = f32(*shape, scale=2.0) + np.float32(0.7), f32(*shape)
+    mean_p, var_p, cell = env.gpu_op.bn_get_cudnnlist(shape, "NCHW", mode)
+    xd, y, dx = env.dev(x), env.empty(shape), env.empty(shape)
+    assert env.gpu_op.bn_forward(xd, y, mode, 0, mean_p, var_p, cell, env.cudnn, env.stream) == 0
+    assert env.gpu_op.bn_backward(xd, env.dev(dy), dx, mode, mean_p, var_p, cell, env.cudnn, env.stream) == 0
+    x64 = x.astype(np.float64)
+    close(y.asnumpy(), env.ops.bn_fwd(x64, mode)[0], what="bn fwd")
+    close(dx.asnumpy(), env.ops.bn_bwd(x64, dy.astype(np.float64), mode), what="bn bwd")
+
+
+# ---- dropout: the mask is bit-exact against the oracle's counter-based generator ------------------------------------
+@pytest.mark.parametrize("p", [0.0, 0.5, 0.3])
+def test_dropout_mask_consistency(env, p):
+    shape = (64, 1, 4096)
+    x, dy = f32(*shape), f32(*shape)
+    inputd = env.gpu_op.get_input_descriptor(shape, "NCHW")
+    y, dx = env.empty(shape), env.empty(shape)
+    reserve, cell, short = env.gpu_op.dropout_forward(env.dev(x), y, "NCHW", p, 17, inputd, env.cudnn, env.stream)
+    assert short == 0
+    env.gpu_op.dropout_backward(env.dev(dy), dx, reserve, cell, env.cudnn, env.stream)
+    want = env.ops.dropout(x, p, 17)
+    np.testing.assert_array_equal(y.asnumpy() != 0, want != 0)      # same mask
+    close(y.asnumpy(), want, rel=1e-6)
+    close(dx.asnumpy(), env.ops.dropout(dy, p, 17), rel=1e-6)          # backward reuses the forward mask
+    if p > 0:
+        keep = (y.asnumpy() != 0).mean()
+        assert abs(keep - (1 - p)) < 4 * np.sqrt(p * (1 - p) / x.size)
+
+
+# ---- optimisers -------------------------------------------------------------------------------------------------------
+def test_sgd_and_adam(env):
+    w, g = f32(1000, 33), f32(1000, 33)
+    wd = env.dev(w)
+    env.gpu_op.sgd_update(wd, env.dev(g), 0.1, env.stream)
+    close(wd.asnumpy(), env.ops.sgd(w.astype(np.float64), g.astype(np.float64), np.float32(0.1)), rel=1e-6)
+    m, v = np.abs(f32(1000, 33)) * 0.1, np.abs(f32(1000, 33)) * 0.01
+    wd, md, vd = env.dev(w), env.dev(m), env.dev(v)
+    env.gpu_op.adam_mv(md, vd, env.dev(g), 0.9, 0.999, env.stream)
+    env.gpu_op.adam_compute(wd, md, vd, 0.9, 0.999, 1e-8, 0.001, env.stream)
+    w2, m2, v2 = env.ops.adam(w.astype(np.float64), m.astype(np.float64), v.astype(np.float64), g.astype(np.float64),
+                              np.float32(0.9), np.float32(0.999), np.float32(0.9), np.float32(0.999), np.float32(1e-8), np.float32(0.001))
+    close(md.asnumpy(), m2, rel=1e-5)
+    close(vd.asnumpy(), v2, rel=1e-5)
+    close(wd.asnumpy(), w2, rel=1e-5)
+
+
+def test_multi_tensor_sgd_matches_per_tensor_updates(env):
+    shapes = [(17,), (33, 5), (1000,), (3, 3, 3, 3)]
+    ws, gs = [f32(*s) for s in shapes], [f32(*s) for s in shapes]
+    wd, gd = [env.dev(a) for a in ws], [env.dev(a) for a in gs]
+    sizes = [a.size for a in ws]
+    prefix = np.concatenate([[0], np.cumsum(sizes)]).astype(int).tolist()
+    n2 = env.gpu_op.get_n2_cuda_pointer([a.data_ptr for a in wd], [a.data_ptr for a in gd], len(ws))
+    info = env.gpu_op.get_index_to_VaribaleNumber_cuda_pointer([0] * len(ws), prefix, len(ws))
+    env.gpu_op.sgd_compute_o(n2, info, len(ws), 0.05)
+    for a, w, g in zip(wd, ws, gs):
+        close(a.asnumpy(), w - np.float32(0.05) * g, rel=1e-6)
+
+
+# ---- size-independent properties at benchmark sizes ---------------------------------------------------------------------
+def test_conv_linearity_and_adjointness_at_full_size(env):
+    """At ResNet-50 batch-64 size the oracle is too slow; check <conv(x,w), dy> == <x, dgrad(dy,w)> == <w, wgrad(x,dy)>."""
+    N, C, H, W, K = 64, 64, 55, 55, 64
+    x, w = f32(N, C, H, W), f32(K, C, 3, 3, scale=0.05)
+    out_shape, cell = env.gpu_op.convolution_2d_forward_get_out_shape(x.shape, w.shape, "NCHW", "SAME", 1, 1)
+    dy = f32(*out_shape)
+    xd, wd, dyd = env.dev(x), env.dev(w), env.dev(dy)
+    y, dx, dw = env.empty(out_shape), env.empty(x.shape), env.empty(w.shape)
+    env.gpu_op.convolution_2d_forward(xd, wd, y, cell, env.cudnn, env.stream)
+    env.gpu_op.convolution_backward_data(xd, dyd, wd, dx, cell, env.cudnn, env.stream)
+    env.gpu_op.convolution_backward_filter(xd, dyd, wd, dw, cell, env.cudnn, env.stream)
+    a = np.vdot(y.asnumpy().astype(np.float64), dy.astype(np.float64))
+    b = np.vdot(x.astype(np.float64), dx.asnumpy().astype(np.float64))
+    c = np.vdot(w.astype(np.float64), dw.asnumpy().astype(np.float64))
+    assert abs(a - b) <= 1e-5 * abs(a) and abs(a - c) <= 1e-5 * abs(a)
+
+
+def test_batchnorm_output_statistics_at_full_size(env):
+    shape = (64, 256, 55, 55)
+    x = f32(*shape, scale=3.0) + np.float32(1.5)
+    mean_p, var_p, cell = env.gpu_op.bn_get_cudnnlist(shape, "NCHW", "pre_activation")
+    y = env.empty(shape)
+    env.gpu_op.bn_forward(env.dev(x), y, "pre_activation", 0, mean_p, var_p, cell, env.cudnn, env.stream)
+    yn = y.asnumpy().astype(np.float64)
+    assert np.abs(yn.mean(axis=0)).max() < 1e-5
+    assert np.abs(yn.var(axis=0) - 1.0).max() < 1e-3     # var/(var+eps) with eps 1e-5 and var ~ 9

@@ -27,6 +27,21 @@ int device_sm_count();
 int after_launch(cudaStream_t s, const char* what, int nkernels = 1);
 #define TF_AFTER(s, what) do { if (::tf::after_launch((s), (what)) != 0) return -1; } while (0)
 
+// ---- optional per-kernel device timing (CUDA events on the launching stream) ------------
+// Off by default.  Level 1 times the dense contractions only, level 2 every instrumented kernel.
+// Construct before the launch; the destructor records the closing event.
+extern int g_timing_level;
+struct KernelTimer {
+  int slot = -1;
+  cudaStream_t stream;
+  KernelTimer(const char* family, cudaStream_t s, double flops, double bytes, int level = 2) : stream(s) {
+    if (g_timing_level >= level) begin(family, flops, bytes);
+  }
+  ~KernelTimer() { if (slot >= 0) end(); }
+  void begin(const char* family, double flops, double bytes);
+  void end();
+};
+
 // ---- streams ------------------------------------------------------------------
 // The caller's cell holds a cudaStream_t.  A null cell means the legacy default stream.
 inline cudaStream_t stream_of(void** cell) { return cell ? (cudaStream_t)(*cell) : (cudaStream_t)0; }

@@ -161,6 +161,7 @@ static int launch_contract(AV A, BV B, OV O, int64_t M, int64_t N, int64_t K, fl
   splits = (int)((K + kps - 1) / kps);
   if (K == 0) { splits = 1; kps = BK; }
   note_compute_stream(s);
+  KernelTimer kt("contract_cudacore", s, 2.0 * (double)M * (double)N * (double)K, 0, 1);
   dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)splits);
   if (splits > 1) {
     TF_CUDA(cudaMemsetAsync(out_base, 0, out_bytes, s));

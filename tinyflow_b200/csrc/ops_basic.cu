@@ -88,6 +88,7 @@ template <class F> __global__ void __launch_bounds__(kBlock) map3_scalar_kernel(
 template <class F> static int run_map1(const float* a, float* o, int64_t n, cudaStream_t s, const char* what, F f) {
   if (n <= 0) return 0;
   note_compute_stream(s);
+  KernelTimer kt(what, s, 0, 8.0 * n);
   if (aligned16(a) && aligned16(o)) map1_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, o, n, f);
   else map1_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, o, n, f);
   TF_AFTER(s, what);
@@ -96,6 +97,7 @@ template <class F> static int run_map1(const float* a, float* o, int64_t n, cuda
 template <class F> static int run_map2(const float* a, const float* b, float* o, int64_t n, cudaStream_t s, const char* what, F f) {
   if (n <= 0) return 0;
   note_compute_stream(s);
+  KernelTimer kt(what, s, 0, 12.0 * n);
   if (aligned16(a) && aligned16(b) && aligned16(o)) map2_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, o, n, f);
   else map2_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, b, o, n, f);
   TF_AFTER(s, what);
@@ -104,6 +106,7 @@ template <class F> static int run_map2(const float* a, const float* b, float* o,
 template <class F> static int run_map3(const float* a, const float* b, const float* c, float* o, int64_t n, cudaStream_t s, const char* what, F f) {
   if (n <= 0) return 0;
   note_compute_stream(s);
+  KernelTimer kt(what, s, 0, 16.0 * n);
   if (aligned16(a) && aligned16(b) && aligned16(c) && aligned16(o)) map3_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, c, o, n, f);
   else map3_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, b, c, o, n, f);
   TF_AFTER(s, what);
@@ -756,6 +759,7 @@ int DLGpuDropoutForward(const DLArrayHandle input, DLArrayHandle output, int dat
   if (reserveSpace_p) *reserveSpace_p = st;
   cudaStream_t s = stream_of(cudaStream);
   note_compute_stream(s);
+  KernelTimer kt("DLGpuDropoutForward", s, 0, 8.0 * st->count);
   dropout_kernel<<<grid_for(st->count, kBlock), kBlock, 0, s>>>(F(input), FM(output), st->count, dropout, 1.f / (1.f - dropout), st->seed);
   TF_AFTER(s, "DLGpuDropoutForward");
   return 0;
@@ -769,6 +773,7 @@ int DLGpuDropoutBackward(const DLArrayHandle doutput, DLArrayHandle dinput, void
   TF_REQUIRE(st && st->count == numel(doutput), "DLGpuDropoutBackward: no matching forward state");
   cudaStream_t s = stream_of(cudaStream);
   note_compute_stream(s);
+  KernelTimer kt("DLGpuDropoutBackward", s, 0, 8.0 * st->count);
   dropout_kernel<<<grid_for(st->count, kBlock), kBlock, 0, s>>>(F(doutput), FM(dinput), st->count, st->p, 1.f / (1.f - st->p), st->seed);
   st->kind = 0;
   free(st);

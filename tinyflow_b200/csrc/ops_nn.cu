@@ -309,6 +309,7 @@ int DLGpuPooling2DForward(const DLArrayHandle input, DLArrayHandle output, void*
   cudaStream_t s = stream_of(cudaStream);
   int64_t total = numel(output);
   note_compute_stream(s);
+  KernelTimer kt("DLGpuPooling2DForward", s, 0, 4.0 * (numel(input) + numel(output)));
   if (p->mode == 0) maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (float*)output->data, nullptr, total, geom_of(p));
   else avgpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (float*)output->data, total, geom_of(p));
   TF_AFTER(s, "DLGpuPooling2DForward");
@@ -324,6 +325,7 @@ int DLGpuPooling2DBackward(const DLArrayHandle input, const DLArrayHandle output
   cudaStream_t s = stream_of(cudaStream);
   int64_t total = numel(dinput);
   note_compute_stream(s);
+  KernelTimer kt("DLGpuPooling2DBackward", s, 0, 4.0 * ((p->mode == 0 ? 2 : 1) * numel(input) + numel(output)));
   if (p->mode == 0) maxpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (const float*)doutput->data, (float*)dinput->data, total, geom_of(p));
   else avgpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)doutput->data, (float*)dinput->data, total, geom_of(p));
   TF_AFTER(s, "DLGpuPooling2DBackward");
@@ -386,6 +388,7 @@ int DLGpuBatchNormalizationForward(const DLArrayHandle input, DLArrayHandle outp
   const float* x = (const float*)input->data;
   float* y = (float*)output->data;
   note_compute_stream(s);
+  KernelTimer kt("DLGpuBatchNormalizationForward", s, 0, 8.0 * numel(input) + 8.0 * p->nstat);
   if (p->mode == 0) {
     int64_t F = p->nstat;
     int N = (int)p->N;
@@ -412,6 +415,7 @@ int DLGpuBatchNormalizationBackward(const DLArrayHandle input, const DLArrayHand
   const float* dy = (const float*)doutput->data;
   float* dx = (float*)dinput->data;
   note_compute_stream(s);
+  KernelTimer kt("DLGpuBatchNormalizationBackward", s, 0, 12.0 * numel(input) + 8.0 * p->nstat);
   if (p->mode == 0) {
     int64_t F = p->nstat;
     int N = (int)p->N;

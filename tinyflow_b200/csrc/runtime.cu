@@ -7,6 +7,7 @@
 #include <unordered_map>
 #include <vector>
 #include <chrono>
+#include <string>
 
 namespace tf {
 
@@ -49,6 +50,48 @@ int after_launch(cudaStream_t s, const char* what, int nkernels) {
     if (e != cudaSuccess) { set_error("%s: %s", what, cudaGetErrorString(e)); return -1; }
   }
   return 0;
+}
+
+// ---- per-kernel timing registry ---------------------------------------------------------------
+int g_timing_level = 0;
+namespace {
+struct Family { std::string name; double flops = 0, bytes = 0, ms = 0; long long launches = 0; };
+struct PendingSpan { int family; cudaEvent_t a, b; };
+std::mutex g_kt_mu;
+std::vector<Family> g_families;
+std::vector<PendingSpan> g_pending;
+std::vector<cudaEvent_t> g_event_pool;
+cudaEvent_t take_event() {
+  if (!g_event_pool.empty()) { cudaEvent_t e = g_event_pool.back(); g_event_pool.pop_back(); return e; }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+void resolve_pending_locked() {
+  for (auto& p : g_pending) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(p.b) == cudaSuccess && cudaEventElapsedTime(&ms, p.a, p.b) == cudaSuccess) g_families[p.family].ms += ms;
+    g_event_pool.push_back(p.a);
+    g_event_pool.push_back(p.b);
+  }
+  g_pending.clear();
+}
+}  // namespace
+void KernelTimer::begin(const char* family, double flops, double bytes) {
+  std::lock_guard<std::mutex> lk(g_kt_mu);
+  int f = -1;
+  for (size_t i = 0; i < g_families.size(); ++i) if (g_families[i].name == family) { f = (int)i; break; }
+  if (f < 0) { g_families.push_back(Family{family}); f = (int)g_families.size() - 1; }
+  g_families[f].flops += flops; g_families[f].bytes += bytes; g_families[f].launches += 1;
+  PendingSpan p{f, take_event(), take_event()};
+  cudaEventRecord(p.a, stream);
+  g_pending.push_back(p);
+  slot = (int)g_pending.size() - 1;
+  if (g_pending.size() > 200000) { slot = -1; cudaEventRecord(p.b, stream); resolve_pending_locked(); }
+}
+void KernelTimer::end() {
+  std::lock_guard<std::mutex> lk(g_kt_mu);
+  if (slot >= 0 && slot < (int)g_pending.size()) cudaEventRecord(g_pending[slot].b, stream);
 }
 
 static std::atomic<cudaStream_t> g_compute_stream{(cudaStream_t)0};
@@ -299,6 +342,31 @@ int testPcie(void) {
   double c = run(dev, pinned, cudaMemcpyHostToDevice), d = run(pinned, dev, cudaMemcpyDeviceToHost);
   printf("host link GB/s: pageable H2D %.2f D2H %.2f | pinned H2D %.2f D2H %.2f\n", a, b, c, d);
   cudaFree(dev); cudaFreeHost(pinned); free(pageable);
+  return 0;
+}
+
+// Per-kernel timing: enable (level 1 = contractions, 2 = all instrumented kernels; resets the table),
+// then read a JSON array of {name, launches, ms, flops, bytes} rows.
+int TfKernelTimingEnable(int level) {
+  std::lock_guard<std::mutex> lk(g_kt_mu);
+  resolve_pending_locked();
+  if (level > 0) g_families.clear();
+  g_timing_level = level;
+  return 0;
+}
+int TfKernelTimingReport(char* buf, int buflen) {
+  std::lock_guard<std::mutex> lk(g_kt_mu);
+  resolve_pending_locked();
+  std::string out = "[";
+  char row[512];
+  for (size_t i = 0; i < g_families.size(); ++i) {
+    const Family& f = g_families[i];
+    snprintf(row, sizeof(row), "%s{\"name\": \"%s\", \"launches\": %lld, \"ms\": %.6f, \"flops\": %.6e, \"bytes\": %.6e}", i ? ", " : "", f.name.c_str(), f.launches, f.ms, f.flops, f.bytes);
+    out += row;
+  }
+  out += "]";
+  if (!buf || buflen <= (int)out.size()) TF_FAIL("TfKernelTimingReport: buffer too small (%zu bytes needed)", out.size() + 1);
+  memcpy(buf, out.c_str(), out.size() + 1);
   return 0;
 }
 
