@@ -48,6 +48,13 @@ inline cudaStream_t stream_of(void** cell) { return cell ? (cudaStream_t)(*cell)
 void note_compute_stream(cudaStream_t s);   // remembered so side-stream copies can order after compute
 cudaStream_t last_compute_stream();
 
+// ---- write versions -------------------------------------------------------------
+// Every entry point that writes a device array bumps the version of its data pointer; cached
+// derived data (packed tensor-core operands) is valid only while the version is unchanged.
+void note_write(const void* p);
+uint64_t version_of(const void* p);
+inline float* out_f32(DLArray* a) { note_write(a->data); return (float*)a->data; }
+
 // ---- shapes -------------------------------------------------------------------
 inline int64_t numel(const DLArray* a) {
   int64_t n = 1;

@@ -43,7 +43,7 @@ int DLGpuMatrixMultiply(const DLArrayHandle matA, bool transposeA, const DLArray
   cudaStream_t s = stream_of(cudaStream);
   const float* A = (const float*)matA->data;
   const float* B = (const float*)matB->data;
-  float* C = (float*)matC->data;
+  float* C = out_f32(matC);
   if (g_path != 1) {
     int oom = 0;
     int r = tc_matmul(A, transposeA, B, transposeB, C, M, N, K, s, &oom);
@@ -101,13 +101,13 @@ int DLGpuConvolution2DForward(const DLArrayHandle input, const DLArrayHandle fil
   cudaStream_t s = stream_of(cudaStream);
   if (g_path != 1) {
     int oom = 0;
-    int r = tc_conv_fwd(p, (const float*)input->data, (const float*)filter->data, (float*)output->data, s, &oom);
+    int r = tc_conv_fwd(p, (const float*)input->data, (const float*)filter->data, out_f32(output), s, &oom);
     if (r < 0) return -1;
     if (oom) { if (memorytoSaving) *memorytoSaving = oom; return 0; }
     if (r == 1) return 0;
     TF_REQUIRE(g_path != 2, "DLGpuConvolution2DForward: shape not taken by the tensor-core path (forced)");
   }
-  return cudacore_conv_fwd(p, (const float*)input->data, (const float*)filter->data, (float*)output->data, s);
+  return cudacore_conv_fwd(p, (const float*)input->data, (const float*)filter->data, out_f32(output), s);
 }
 
 int DLGpuConvolutionBackwardData(const DLArrayHandle input, const DLArrayHandle doutput, const DLArrayHandle filter, DLArrayHandle dinput,
@@ -119,13 +119,13 @@ int DLGpuConvolutionBackwardData(const DLArrayHandle input, const DLArrayHandle 
   cudaStream_t s = stream_of(cudaStream);
   if (g_path != 1) {
     int oom = 0;
-    int r = tc_conv_dgrad(p, (const float*)doutput->data, (const float*)filter->data, (float*)dinput->data, s, &oom);
+    int r = tc_conv_dgrad(p, (const float*)doutput->data, (const float*)filter->data, out_f32(dinput), s, &oom);
     if (r < 0) return -1;
     if (oom) { if (memorytoSaving) *memorytoSaving = oom; return 0; }
     if (r == 1) return 0;
     TF_REQUIRE(g_path != 2, "DLGpuConvolutionBackwardData: shape not taken by the tensor-core path (forced)");
   }
-  return cudacore_conv_dgrad(p, (const float*)doutput->data, (const float*)filter->data, (float*)dinput->data, s);
+  return cudacore_conv_dgrad(p, (const float*)doutput->data, (const float*)filter->data, out_f32(dinput), s);
 }
 
 int DLGpuConvolutionBackwardFilter(const DLArrayHandle input, const DLArrayHandle doutput, const DLArrayHandle filter, DLArrayHandle dfilter,
@@ -137,13 +137,13 @@ int DLGpuConvolutionBackwardFilter(const DLArrayHandle input, const DLArrayHandl
   cudaStream_t s = stream_of(cudaStream);
   if (g_path != 1) {
     int oom = 0;
-    int r = tc_conv_wgrad(p, (const float*)input->data, (const float*)doutput->data, (float*)dfilter->data, s, &oom);
+    int r = tc_conv_wgrad(p, (const float*)input->data, (const float*)doutput->data, out_f32(dfilter), s, &oom);
     if (r < 0) return -1;
     if (oom) { if (memorytoSaving) *memorytoSaving = oom; return 0; }
     if (r == 1) return 0;
     TF_REQUIRE(g_path != 2, "DLGpuConvolutionBackwardFilter: shape not taken by the tensor-core path (forced)");
   }
-  return cudacore_conv_wgrad(p, (const float*)input->data, (const float*)doutput->data, (float*)dfilter->data, s);
+  return cudacore_conv_wgrad(p, (const float*)input->data, (const float*)doutput->data, out_f32(dfilter), s);
 }
 
 // 1-D / 3-D convolution: symbols only.

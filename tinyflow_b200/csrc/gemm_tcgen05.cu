@@ -1,8 +1,760 @@
-// placeholder, replaced below in this session
+// Tensor-core path of the dense contractions: a persistent, warp-specialised 3xTF32 GEMM on the
+// Blackwell tcgen05 pipeline (TMA -> shared memory -> tcgen05.mma -> TMEM -> registers -> HBM).
+//
+// 3xTF32.  Every fp32 operand element a is split once into hi = tf32(a) and lo = tf32(a - hi) by a
+// packing kernel; the GEMM accumulates hi*hi + lo*hi + hi*lo in fp32 TMEM, which restores fp32-level
+// accuracy (the dropped lo*lo term is below 2^-22 relative).  Packed operands are plain 2-D row-major
+// matrices [rows][cols] (cols contiguous) so that one kernel serves every contraction:
+//
+//   matmul            A, B packed as they lie; the operand's "major" (K contiguous or M/N contiguous)
+//                     is a run-time flag that only changes the TMA box shape and the UMMA descriptor.
+//   conv forward      activations packed pixel-major [N * frame_h * frame_w][C] with the zero halo
+//                     materialised, filters packed [Cout][tap][C]; a filter tap is then a constant
+//                     row shift of the activation matrix, so the K loop is (tap, 32-channel chunk)
+//                     and each step is two plain 2-D TMA boxes.  Outputs computed for halo anchors
+//                     are discarded by the epilogue.
+//   conv backward-data  same kernel on the packed output gradient with the flipped filter
+//                     [Cin][tap'][Cout]; a strided 1x1 scatters into a zeroed dx.
+//   conv backward-filter  dW[k][c][tap] = sum_rows dy[row][k] * x[row + shift(tap)][c]: both operands
+//                     are M/N-major, the reduction runs over pixel rows, split over CTAs and combined
+//                     with fp32 atomics.
+//
+// Kernel roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-5 =
+// epilogue (one TMEM lane quarter each).  Shared memory holds a ring of stages {A_hi, A_lo, B_hi, B_lo}
+// (128-byte swizzle, 32 fp32 of K per stage); TMEM holds two accumulators so the epilogue of tile i
+// overlaps the main loop of tile i+1.  Every mbarrier wait is bounded: on time-out the CTA raises an
+// error flag the host reads, drains its outstanding copies, frees its TMEM and returns.
 #include "common.h"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
 namespace tf {
-int tc_matmul(const float*, bool, const float*, bool, float*, int64_t, int64_t, int64_t, cudaStream_t, int*) { return 0; }
-int tc_conv_fwd(ConvPlan*, const float*, const float*, float*, cudaStream_t, int*) { return 0; }
-int tc_conv_dgrad(ConvPlan*, const float*, const float*, float*, cudaStream_t, int*) { return 0; }
-int tc_conv_wgrad(ConvPlan*, const float*, const float*, float*, cudaStream_t, int*) { return 0; }
+
+// ------------------------------------------------------------------------------------------------
+// write versions: lets cached packs detect that their source tensor changed
+// ------------------------------------------------------------------------------------------------
+static std::mutex g_ver_mu;
+static std::unordered_map<const void*, uint64_t> g_versions;
+static uint64_t g_ver_counter = 1;
+void note_write(const void* p) {
+  std::lock_guard<std::mutex> lk(g_ver_mu);
+  g_versions[p] = ++g_ver_counter;
 }
+uint64_t version_of(const void* p) {
+  std::lock_guard<std::mutex> lk(g_ver_mu);
+  auto it = g_versions.find(p);
+  if (it == g_versions.end()) { g_versions[p] = ++g_ver_counter; return g_ver_counter; }
+  return it->second;
+}
+
+// ------------------------------------------------------------------------------------------------
+// device-side primitives (inline PTX)
+// ------------------------------------------------------------------------------------------------
+constexpr int BM = 128;            // UMMA M (TMEM lanes)
+constexpr int BK = 32;             // fp32 elements of K per stage = one 128-byte swizzle row
+constexpr int kThreads = 192;
+constexpr int kGroupIters = 4;     // stages accumulated in TMEM before the epilogue promotes them to registers
+constexpr long long kWaitCycles = 3000000000ll;   // ~1.5 s at 2 GHz: far beyond any legitimate wait
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and raises *abort_flag) if the barrier does not flip in time or another
+// role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  long long t0 = clock64();
+  for (;;) {
+    for (int i = 0; i < 64; ++i) if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, descriptor version 1 (Blackwell).
+//   K-major operand : 128-byte swizzle with 16-byte atoms (layout type 2): rows of 128 B (32 fp32 of K),
+//                     8-row groups 1024 B apart (SBO); LBO unused (= 16 B).
+//   MN-major operand: tf32 allows only the 128-byte swizzle with 32-byte atoms (layout type 1): tiles of
+//                     [32 K-rows][32 fp32 of M/N] = 4096 B; 4-row K groups 512 B apart (SBO), tiles 4096 B
+//                     apart along M/N (LBO).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+         (1ull << 46) | ((uint64_t)layout_type << 61);
+}
+
+// ------------------------------------------------------------------------------------------------
+// kernel parameters
+// ------------------------------------------------------------------------------------------------
+enum { kModeGemm = 0, kModeConv = 1, kModeWgrad = 2 };
+enum { kEpiRowMajor = 0, kEpiNchw = 1, kEpiWgrad = 2 };
+constexpr int kMaxTaps = 49;
+
+struct alignas(64) GemmParams {
+  CUtensorMap a_hi, a_lo, b_hi, b_lo;
+  int mode, a_mn, b_mn, epi;
+  int M, N;                       // valid extents of the output tile grid
+  int m_tiles, n_tiles, tap_tiles, splits;
+  int k_iters;                    // stages per (tile, split)
+  int chunks_per_tap;             // kModeConv: 32-channel chunks per tap
+  int b_tap_pitch;                // kModeConv: columns per tap in the packed filter
+  int ntaps;
+  int atomic;                     // epilogue adds into `out` (pre-zeroed) instead of storing
+  float* out;
+  long long ldc;                  // kEpiRowMajor
+  // kEpiNchw: row m -> (image, i, j) in a frame of frame_h x frame_w; valid if i < valid_h and j < valid_w;
+  // element (image, channel c, i, j) lives at ((image*out_c + c)*out_h + i*out_sh)*out_w + j*out_sw
+  int frame_h, frame_w, valid_h, valid_w, out_c, out_h, out_w, out_sh, out_sw;
+  int* err;                       // device-visible error word (mapped host memory)
+  int tap_off[kMaxTaps];          // row shift per tap (A rows for kModeConv, B rows for kModeWgrad)
+};
+
+template <int BN> struct SmemLayout {
+  static constexpr int kStages = BN <= 64 ? 4 : 3;
+  static constexpr int kABytes = BM * BK * 4;           // 16 KiB
+  static constexpr int kBBytes = BN * BK * 4;
+  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;   // + slack to align to 1024
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_constant__ GemmParams p) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);
+  uint64_t* empty = full + L::kStages;
+  uint64_t* acc_full = empty + L::kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles * p.n_tiles * p.tap_tiles * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // TMEM: two accumulators of BN fp32 columns each
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // tile index -> coordinates; n fastest so consecutive CTAs share the A tile through L2
+  auto decode = [&](int tile, int& mt, int& nt, int& tap, int& split) {
+    split = tile % p.splits; tile /= p.splits;
+    nt = tile % p.n_tiles; tile /= p.n_tiles;
+    tap = tile % p.tap_tiles; tile /= p.tap_tiles;
+    mt = tile;
+  };
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool armed[L::kStages]; uint32_t armed_phase[L::kStages];
+      for (int s = 0; s < L::kStages; ++s) { armed[s] = false; armed_phase[s] = 0; }
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int mt, nt, tap, split;
+        decode(tile, mt, nt, tap, split);
+        const int m0 = mt * BM, n0 = nt * BN;
+        for (int it = 0; it < p.k_iters; ++it) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* st = smem + stage * L::kStageBytes;
+          uint8_t *a_hi = st, *a_lo = st + L::kABytes, *b_hi = st + 2 * L::kABytes, *b_lo = b_hi + L::kBBytes;
+          mbar_expect_tx(&full[stage], L::kStageBytes);
+          armed[stage] = true; armed_phase[stage] = phase;
+          int a_col, a_row, b_col, b_row;
+          if (p.mode == kModeConv) {
+            int t = it / p.chunks_per_tap, ch = it - t * p.chunks_per_tap;
+            a_col = ch * BK; a_row = m0 + p.tap_off[t];
+            b_col = t * p.b_tap_pitch + ch * BK; b_row = n0;
+          } else if (p.mode == kModeWgrad) {
+            int krow = (split * p.k_iters + it) * BK;
+            a_col = m0; a_row = krow;
+            b_col = n0; b_row = krow + p.tap_off[tap];
+          } else {
+            int kk = (split * p.k_iters + it) * BK;
+            if (p.a_mn) { a_col = m0; a_row = kk; } else { a_col = kk; a_row = m0; }
+            if (p.b_mn) { b_col = n0; b_row = kk; } else { b_col = kk; b_row = n0; }
+          }
+          if (p.a_mn) {
+#pragma unroll
+            for (int i = 0; i < BM / 32; ++i) {
+              tma_load_2d(a_hi + i * 4096, &p.a_hi, a_col + 32 * i, a_row, &full[stage]);
+              tma_load_2d(a_lo + i * 4096, &p.a_lo, a_col + 32 * i, a_row, &full[stage]);
+            }
+          } else {
+            tma_load_2d(a_hi, &p.a_hi, a_col, a_row, &full[stage]);
+            tma_load_2d(a_lo, &p.a_lo, a_col, a_row, &full[stage]);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int i = 0; i < BN / 32; ++i) {
+              tma_load_2d(b_hi + i * 4096, &p.b_hi, b_col + 32 * i, b_row, &full[stage]);
+              tma_load_2d(b_lo + i * 4096, &p.b_lo, b_col + 32 * i, b_row, &full[stage]);
+            }
+          } else {
+            tma_load_2d(b_hi, &p.b_hi, b_col, b_row, &full[stage]);
+            tma_load_2d(b_lo, &p.b_lo, b_col, b_row, &full[stage]);
+          }
+          if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (*abort_flag) {
+        // let copies that are still in flight land before the CTA gives its shared memory back
+        for (int s = 0; s < L::kStages; ++s) {
+          if (!armed[s]) continue;
+          long long t0 = clock64();
+          while (!mbar_try_wait(&full[s], armed_phase[s]) && clock64() - t0 < 100000000ll) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn ? 4096u : 16u, b_lbo = p.b_mn ? 4096u : 16u;
+      const uint32_t a_kstep = p.a_mn ? 1024u : 32u, b_kstep = p.b_mn ? 1024u : 32u;
+      const uint32_t a_sbo = p.a_mn ? 512u : 1024u, b_sbo = p.b_mn ? 512u : 1024u;
+      const uint32_t a_lt = p.a_mn ? 1u : 2u, b_lt = p.b_mn ? 1u : 2u;
+      int stage = 0; uint32_t phase = 0;
+      int group = 0;            // accumulator groups issued so far (alternating TMEM buffers)
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        for (int it0 = 0; it0 < p.k_iters && ok; it0 += kGroupIters, ++group) {
+          const int acc = group & 1;
+          if (!mbar_wait(&acc_empty[acc], ((group >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          const int it1 = min(it0 + kGroupIters, p.k_iters);
+          for (int it = it0; it < it1; ++it) {
+            if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+            tcgen05_fence_after();
+            const uint32_t st = smem_u32(smem + stage * L::kStageBytes);
+            const uint32_t a_hi = st, a_lo = st + L::kABytes, b_hi = st + 2 * L::kABytes, b_lo = b_hi + L::kBBytes;
+#pragma unroll
+            for (int k = 0; k < BK / 8; ++k) {
+              const uint64_t ah = umma_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lt), al = umma_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lt);
+              const uint64_t bh = umma_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lt), bl = umma_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lt);
+              umma_tf32(d_tmem, al, bh, idesc, (it > it0 || k > 0) ? 1u : 0u);     // small terms first
+              umma_tf32(d_tmem, ah, bl, idesc, 1u);
+              umma_tf32(d_tmem, ah, bh, idesc, 1u);
+            }
+            tcgen05_commit(&empty[stage]);       // frees the stage once the MMAs above have read it
+            if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+          }
+          if (ok) tcgen05_commit(&acc_full[acc]);
+        }
+      }
+    }
+  } else {
+    // ===================== epilogue: warps 2..5, TMEM lane quarter = warp % 4 =====================
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    int group = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      int mt, nt, tap, split;
+      decode(tile, mt, nt, tap, split);
+      // The tensor core accumulates with truncation, so a long chain of MMAs into one TMEM accumulator
+      // drifts; each group of kGroupIters stages is therefore accumulated in TMEM on its own and promoted
+      // here into fp32 registers with round-to-nearest adds.
+      float accv[BN];
+#pragma unroll
+      for (int q = 0; q < BN; ++q) accv[q] = 0.f;
+      for (int it0 = 0; it0 < p.k_iters && ok; it0 += kGroupIters, ++group) {
+        const int acc = group & 1;
+        {   // lane 0 polls, the warp follows: keeps the warp converged for the .sync.aligned TMEM loads
+          int got = lane == 0 ? (int)mbar_wait(&acc_full[acc], (group >> 1) & 1, abort_flag) : 1;
+          got = __shfl_sync(0xffffffffu, got, 0);
+          if (!got) { ok = false; break; }
+        }
+        tcgen05_fence_after();
+        const uint32_t t_base = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          float v[32];
+          tmem_ld32(t_base + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) accv[c0 + q] += v[q];
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      }
+      if (!ok) break;
+      const long long m = (long long)mt * BM + row_in_tile;
+      const int n0 = nt * BN;
+      // per-row output address (everything but the column term)
+      bool row_ok = m < p.M;
+      long long base = 0, col_stride = 1;
+      if (p.epi == kEpiRowMajor) {
+        base = m * p.ldc;
+      } else if (p.epi == kEpiNchw) {
+        int per_img = p.frame_h * p.frame_w;
+        long long img = m / per_img;
+        int rem = (int)(m - img * per_img), i = rem / p.frame_w, j = rem - i * p.frame_w;
+        row_ok = row_ok && i < p.valid_h && j < p.valid_w;
+        col_stride = (long long)p.out_h * p.out_w;
+        base = (img * p.out_c) * col_stride + (long long)(i * p.out_sh) * p.out_w + j * p.out_sw;
+      } else {   // kEpiWgrad: out[(m * N_total + n) * ntaps + tap]
+        base = (m * p.N) * p.ntaps + tap;
+        col_stride = p.ntaps;
+      }
+      if (row_ok) {
+        if (p.epi == kEpiRowMajor && !p.atomic && n0 + BN <= p.N && ((base + n0) & 3) == 0) {
+          float4* dst = reinterpret_cast<float4*>(p.out + base + n0);
+#pragma unroll
+          for (int q = 0; q < BN / 4; ++q) dst[q] = make_float4(accv[4 * q], accv[4 * q + 1], accv[4 * q + 2], accv[4 * q + 3]);
+        } else {
+#pragma unroll
+          for (int q = 0; q < BN; ++q) {
+            int n = n0 + q;
+            if (n < p.N) {
+              float* dst = p.out + base + (long long)n * col_stride;
+              if (p.atomic) atomicAdd(dst, accv[q]); else *dst = accv[q];
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ===================== teardown =====================
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
+}
+
+// ------------------------------------------------------------------------------------------------
+// packing kernels (fp32 -> hi / lo tf32 pair)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void split_tf32(float a, float& hi, float& lo) {
+  uint32_t h, l;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
+  hi = __uint_as_float(h);
+  float r = a - hi;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(r));
+  lo = __uint_as_float(l);
+}
+
+// rows x cols row-major (pitch src_ld) -> hi/lo with pitch dst_ld
+__global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restrict__ src, long long src_ld, float* __restrict__ hi, float* __restrict__ lo,
+                                                          long long dst_ld, long long rows, long long cols) {
+  long long total = rows * cols, stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    long long r = i / cols, c = i - r * cols;
+    float h, l;
+    split_tf32(src[r * src_ld + c], h, l);
+    hi[r * dst_ld + c] = h;
+    lo[r * dst_ld + c] = l;
+  }
+}
+
+// NCHW activations -> pixel-major frame [N][frame_h][frame_w][pitch]:
+//   dst(n, i, j, c) = src(n, c, (i - off_h) * sh, (j - off_w) * sw) when that sample exists, else 0.
+// 32 (frame columns) x 32 (channels) tiles transposed through shared memory: reads run along w,
+// writes along c.
+struct PackGeom { int N, C, H, W, frame_h, frame_w, off_h, off_w, sh, sw, cnt_h, cnt_w, pitch; };
+__global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, PackGeom g) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
+  const int j0 = blockIdx.x * 32, i = blockIdx.y;
+  const int cblocks = (g.C + 31) / 32;
+  const int n = blockIdx.z / cblocks, c0 = (blockIdx.z % cblocks) * 32;
+  const int si = i - g.off_h;
+  const bool row_ok = si >= 0 && si < g.cnt_h;
+  {
+    int j = j0 + tx, sj = j - g.off_w;
+    bool ok = row_ok && sj >= 0 && sj < g.cnt_w && j < g.frame_w;
+    const float* s = src + ((long long)n * g.C * g.H + (long long)(si * g.sh)) * g.W + (long long)sj * g.sw;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      int c = c0 + ty + 8 * k;
+      tile[ty + 8 * k][tx] = (ok && c < g.C) ? s[(long long)c * g.H * g.W] : 0.f;
+    }
+  }
+  __syncthreads();
+  {
+    int c = c0 + tx;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      int j = j0 + ty + 8 * k;
+      if (j < g.frame_w && c < g.C) {
+        float h, l;
+        split_tf32(tile[tx][ty + 8 * k], h, l);
+        long long o = (((long long)n * g.frame_h + i) * g.frame_w + j) * g.pitch + c;
+        hi[o] = h; lo[o] = l;
+      }
+    }
+  }
+}
+
+// filters [K][C][R][S] -> forward pack [K][tap][cpad] (flip = 0) or backward-data pack [C][tap'][kpad] (flip = 1,
+// tap' = (R-1-r)*S + (S-1-s)), zero in the channel padding.
+__global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
+                                                          int K, int C, int R, int S, int flip, int inner_pad) {
+  int taps = R * S;
+  long long rows = flip ? C : K, total = rows * taps * inner_pad, stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    int in = (int)(idx % inner_pad);
+    long long t2 = idx / inner_pad;
+    int tap = (int)(t2 % taps), row = (int)(t2 / taps);
+    int inner_n = flip ? K : C;
+    float a = 0.f;
+    if (in < inner_n) {
+      int k = flip ? in : row, c = flip ? row : in;
+      int src_tap = flip ? (taps - 1 - tap) : tap;
+      a = w[((long long)k * C + c) * taps + src_tap];
+    }
+    float h, l;
+    split_tf32(a, h, l);
+    hi[idx] = h; lo[idx] = l;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+// 2-D fp32 row-major [rows][cols] with `pitch` floats per row; box = 32 cols x box_rows rows; 128-byte swizzle with
+// 16-byte atoms for K-major operands, with 32-byte atoms for the M/N-major ones (the only form tf32 takes there).
+static int make_map(CUtensorMap* m, const float* base, long long rows, long long cols, long long pitch, int box_rows, bool mn_major = false) {
+  EncodeTiledFn fn = encode_fn();
+  TF_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch * 4};
+  cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld pitch %lld)", (int)r, rows, cols, pitch);
+  return 0;
+}
+
+static int* error_word() {      // mapped pinned word: the kernels raise it, the host polls it for free
+  static int* host = nullptr;
+  static int* dev = nullptr;
+  if (!host) {
+    if (cudaHostAlloc((void**)&host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    *host = 0;
+    if (cudaHostGetDevicePointer((void**)&dev, host, 0) != cudaSuccess) { cudaGetLastError(); dev = nullptr; }
+  }
+  return dev;
+}
+static int* error_word_host() {
+  static int* host = nullptr;
+  if (!host) {
+    int* dev = error_word();
+    if (!dev) return nullptr;
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, dev) == cudaSuccess) host = (int*)at.hostPointer;
+  }
+  return host;
+}
+int tensor_path_error() { int* h = error_word_host(); return h ? *h : 0; }
+
+static bool g_attr_done[3] = {false, false, false};
+template <int BN> static int launch_gemm(const GemmParams& p, cudaStream_t s, double flops, const char* what) {
+  using L = SmemLayout<BN>;
+  constexpr int slot = BN == 64 ? 0 : (BN == 128 ? 1 : 2);
+  if (!g_attr_done[slot]) {
+    TF_CUDA(cudaFuncSetAttribute(gemm3xtf32_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    g_attr_done[slot] = true;
+  }
+  TF_REQUIRE(tensor_path_error() == 0, "%s: an earlier tensor-core kernel timed out on a barrier; refusing to launch", what);
+  int tiles = p.m_tiles * p.n_tiles * p.tap_tiles * p.splits;
+  int grid = tiles < device_sm_count() ? tiles : device_sm_count();
+  note_compute_stream(s);
+  KernelTimer kt("gemm3xtf32_tcgen05", s, flops, 0, 1);
+  gemm3xtf32_kernel<BN><<<grid, kThreads, L::kTotal, s>>>(p);
+  TF_AFTER(s, what);
+  return 0;
+}
+static int launch_gemm_bn(int bn, const GemmParams& p, cudaStream_t s, double flops, const char* what) {
+  return bn == 64 ? launch_gemm<64>(p, s, flops, what) : launch_gemm<128>(p, s, flops, what);
+}
+static inline int pick_bn(long long n) { return n <= 64 ? 64 : 128; }
+static inline long long round_up(long long a, long long b) { return (a + b - 1) / b * b; }
+
+struct Pack {           // a packed operand living in pooled device memory
+  float* hi = nullptr; float* lo = nullptr;
+  long long rows = 0, cols = 0, pitch = 0;
+  const void* src = nullptr; uint64_t version = 0; int tag = 0;   // cache key
+  size_t bytes() const { return (size_t)rows * pitch * 4; }
+};
+static int pack_alloc(Pack& pk, long long rows, long long cols, int* oom) {
+  long long pitch = round_up(cols, 4);
+  if (pk.hi && pk.rows == rows && pk.pitch == pitch) { pk.cols = cols; return 0; }
+  if (pk.hi) { pool_free(pk.hi); pool_free(pk.lo); pk.hi = pk.lo = nullptr; }
+  pk.rows = rows; pk.cols = cols; pk.pitch = pitch; pk.src = nullptr;
+  pk.hi = (float*)pool_alloc(pk.bytes());
+  pk.lo = pk.hi ? (float*)pool_alloc(pk.bytes()) : nullptr;
+  if (!pk.lo) {
+    if (pk.hi) pool_free(pk.hi);
+    pk.hi = nullptr;
+    if (oom) *oom = pk.bytes() > 0x7fffffffu ? 0x7fffffff : (int)pk.bytes();
+    return 1;
+  }
+  return 0;
+}
+static void pack_release(Pack& pk) { if (pk.hi) { pool_free(pk.hi); pool_free(pk.lo); pk.hi = pk.lo = nullptr; } }
+
+static int run_pack_matrix(const float* src, long long ld, Pack& pk, cudaStream_t s) {
+  long long total = pk.rows * pk.cols;
+  KernelTimer kt("pack_matrix", s, 0, 12.0 * total);
+  pack_matrix_kernel<<<grid_for(total, 256, 4), 256, 0, s>>>(src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols);
+  TF_AFTER(s, "pack_matrix");
+  return 0;
+}
+
+// ---- matmul ---------------------------------------------------------------------------------------
+int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_t M, int64_t N, int64_t K, cudaStream_t s, int* oom) {
+  if (M < 16 || N < 16 || K < 32 || (double)M * N * K < 4e6) return 0;      // launch-bound sizes stay on the CUDA cores
+  if (!encode_fn()) return 0;
+  // A is stored [M][K] (K-major) or, transposed, [K][M] (M-major); B is stored [K][N] (N-major) or [N][K] (K-major)
+  Pack pa, pb;
+  long long a_rows = tA ? K : M, a_cols = tA ? M : K, b_rows = tB ? N : K, b_cols = tB ? K : N;
+  if (pack_alloc(pa, a_rows, a_cols, oom)) return 0;
+  if (pack_alloc(pb, b_rows, b_cols, oom)) { pack_release(pa); return 0; }
+  int rc = run_pack_matrix(A, a_cols, pa, s);
+  if (!rc) rc = run_pack_matrix(B, b_cols, pb, s);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int bn = pick_bn(N);
+  p.mode = kModeGemm; p.a_mn = tA ? 1 : 0; p.b_mn = tB ? 0 : 1; p.epi = kEpiRowMajor;
+  if (!rc) rc = make_map(&p.a_hi, pa.hi, pa.rows, pa.cols, pa.pitch, p.a_mn ? 32 : BM, p.a_mn);
+  if (!rc) rc = make_map(&p.a_lo, pa.lo, pa.rows, pa.cols, pa.pitch, p.a_mn ? 32 : BM, p.a_mn);
+  if (!rc) rc = make_map(&p.b_hi, pb.hi, pb.rows, pb.cols, pb.pitch, p.b_mn ? 32 : bn, p.b_mn);
+  if (!rc) rc = make_map(&p.b_lo, pb.lo, pb.rows, pb.cols, pb.pitch, p.b_mn ? 32 : bn, p.b_mn);
+  if (!rc) {
+    p.M = (int)M; p.N = (int)N;
+    p.m_tiles = (int)((M + BM - 1) / BM); p.n_tiles = (int)((N + bn - 1) / bn); p.tap_tiles = 1;
+    int kit = (int)((K + BK - 1) / BK);
+    int tiles = p.m_tiles * p.n_tiles, sms = device_sm_count();
+    int splits = 1;
+    if (tiles * 2 <= sms && kit >= 16) { splits = sms / tiles; if (splits > kit / 8) splits = kit / 8; if (splits < 1) splits = 1; }
+    p.k_iters = (kit + splits - 1) / splits;
+    p.splits = (kit + p.k_iters - 1) / p.k_iters;
+    p.atomic = p.splits > 1;
+    p.out = C; p.ldc = N; p.err = error_word();
+    if (p.atomic) { if (cudaMemsetAsync(C, 0, sizeof(float) * M * N, s) != cudaSuccess) rc = -1; }
+    if (!rc) rc = launch_gemm_bn(bn, p, s, 2.0 * M * N * K, "DLGpuMatrixMultiply");
+  }
+  pack_release(pa); pack_release(pb);       // stream order keeps the blocks valid until the kernel is done
+  return rc ? -1 : 1;
+}
+
+// ---- convolution -------------------------------------------------------------------------------------
+// Shapes the tensor path takes (everything else returns 0 and runs on the CUDA cores):
+//   class A: 1x1 window, no padding, any stride;
+//   class B: stride 1 with symmetric "same" padding (2*pad = window - 1 on both axes), any window.
+struct ConvTc {
+  int cls = 0;                 // 0 unsupported, 1 class A, 2 class B
+  int frame_h = 0, frame_w = 0, off_h = 0, off_w = 0;   // frame geometry shared by the x and dy packs
+  Pack x, dy, wf, wd;
+  std::mutex mu;
+};
+static ConvTc* conv_state(ConvPlan* p) {
+  if (!p->tc_state) {
+    ConvTc* st = new ConvTc;
+    bool ok = p->dataformat == 0 && p->C >= 16 && p->K >= 16 && p->C % 4 == 0 && p->K % 4 == 0 && p->R * p->S <= kMaxTaps;
+    if (ok && p->R == 1 && p->S == 1 && p->pad_h == 0 && p->pad_w == 0) {
+      st->cls = 1; st->frame_h = p->P; st->frame_w = p->Q;
+    } else if (ok && p->stride_h == 1 && p->stride_w == 1 && 2 * p->pad_h == p->R - 1 && 2 * p->pad_w == p->S - 1) {
+      st->cls = 2; st->frame_h = p->H + 2 * p->pad_h; st->frame_w = p->W + 2 * p->pad_w; st->off_h = p->pad_h; st->off_w = p->pad_w;
+    }
+    // small problems are launch-bound: leave them to the CUDA-core kernel
+    double flops = 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S;
+    if (flops < 2e7) st->cls = 0;
+    p->tc_state = st;
+  }
+  return (ConvTc*)p->tc_state;
+}
+
+// packs an NCHW tensor with `chans` channels into the plan's frame; spatial source dims (H, W), sampling stride (sh, sw)
+static int pack_activation(Pack& pk, const float* src, int N, int chans, int H, int W, const ConvTc* st, int sh, int sw, int cnt_h, int cnt_w,
+                           int tag, cudaStream_t s, int* oom) {
+  uint64_t ver = version_of(src);
+  long long rows = (long long)N * st->frame_h * st->frame_w;
+  if (pk.hi && pk.src == src && pk.version == ver && pk.tag == tag && pk.rows == rows && pk.cols == chans) return 0;   // still valid
+  if (pack_alloc(pk, rows, chans, oom)) return 1;
+  PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, st->off_h, st->off_w, sh, sw, cnt_h, cnt_w, (int)pk.pitch};
+  dim3 grid((st->frame_w + 31) / 32, st->frame_h, N * ((chans + 31) / 32));
+  KernelTimer kt("pack_nchw", s, 0, 12.0 * rows * chans);
+  pack_nchw_kernel<<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
+  TF_AFTER(s, "pack_nchw");
+  pk.src = src; pk.version = ver; pk.tag = tag;
+  return 0;
+}
+static int pack_filter(Pack& pk, const float* w, const ConvPlan* p, int flip, cudaStream_t s, int* oom) {
+  int taps = p->R * p->S, rows = flip ? p->C : p->K, inner = flip ? p->K : p->C, inner_pad = (int)round_up(inner, 32);
+  if (pack_alloc(pk, rows, (long long)taps * inner_pad, oom)) return 1;
+  long long total = (long long)rows * taps * inner_pad;
+  pack_filter_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, pk.hi, pk.lo, p->K, p->C, p->R, p->S, flip, inner_pad);
+  TF_AFTER(s, "pack_filter");
+  return 0;
+}
+
+// forward and backward-data share one launcher: out[pixel][ch_out] = sum_{tap, ch_in} act[pixel + shift(tap)][ch_in] * filt[ch_out][tap][ch_in]
+static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, const ConvPlan* p, const ConvTc* st, float* out,
+                     int valid_h, int valid_w, int out_h, int out_w, int out_sh, int out_sw, cudaStream_t s, const char* what) {
+  GemmParams g;
+  memset(&g, 0, sizeof(g));
+  const int bn = pick_bn(ch_out);
+  g.mode = kModeConv; g.epi = kEpiNchw;
+  int rc = make_map(&g.a_hi, act.hi, act.rows, act.cols, act.pitch, BM);
+  if (!rc) rc = make_map(&g.a_lo, act.lo, act.rows, act.cols, act.pitch, BM);
+  if (!rc) rc = make_map(&g.b_hi, filt.hi, filt.rows, filt.cols, filt.pitch, bn);
+  if (!rc) rc = make_map(&g.b_lo, filt.lo, filt.rows, filt.cols, filt.pitch, bn);
+  if (rc) return -1;
+  g.M = (int)act.rows; g.N = ch_out;
+  g.m_tiles = (int)((act.rows + BM - 1) / BM); g.n_tiles = (ch_out + bn - 1) / bn; g.tap_tiles = 1; g.splits = 1;
+  g.ntaps = p->R * p->S;
+  g.chunks_per_tap = (ch_in + BK - 1) / BK;
+  g.b_tap_pitch = (int)round_up(ch_in, 32);
+  g.k_iters = g.ntaps * g.chunks_per_tap;
+  for (int r = 0; r < p->R; ++r) for (int q = 0; q < p->S; ++q) g.tap_off[r * p->S + q] = r * st->frame_w + q;
+  g.out = out; g.err = error_word();
+  g.frame_h = st->frame_h; g.frame_w = st->frame_w; g.valid_h = valid_h; g.valid_w = valid_w;
+  g.out_c = ch_out; g.out_h = out_h; g.out_w = out_w; g.out_sh = out_sh; g.out_sw = out_sw;
+  double flops = 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S;
+  return launch_gemm_bn(bn, g, s, flops, what);
+}
+
+int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStream_t s, int* oom) {
+  ConvTc* st = conv_state(p);
+  if (!st->cls || !encode_fn()) return 0;
+  std::lock_guard<std::mutex> lk(st->mu);
+  if (pack_activation(st->x, x, p->N, p->C, p->H, p->W, st, p->stride_h, p->stride_w, st->cls == 1 ? p->P : p->H, st->cls == 1 ? p->Q : p->W, 1, s, oom)) return *oom ? 1 : -1;
+  if (pack_filter(st->wf, w, p, 0, s, oom)) return *oom ? 1 : -1;
+  int rc = conv_like(st->x, st->wf, p->C, p->K, p, st, y, p->P, p->Q, p->P, p->Q, 1, 1, s, "DLGpuConvolution2DForward");
+  return rc ? -1 : 1;
+}
+
+int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaStream_t s, int* oom) {
+  ConvTc* st = conv_state(p);
+  if (!st->cls || !encode_fn()) return 0;
+  std::lock_guard<std::mutex> lk(st->mu);
+  // dy sits in the same frame as x (class B: at the padding offset; class A: dense P x Q)
+  if (pack_activation(st->dy, dy, p->N, p->K, p->P, p->Q, st, 1, 1, p->P, p->Q, 2, s, oom)) return *oom ? 1 : -1;
+  if (pack_filter(st->wd, w, p, 1, s, oom)) return *oom ? 1 : -1;
+  int rc = 0;
+  if (st->cls == 1) {
+    bool strided = p->stride_h > 1 || p->stride_w > 1;
+    if (strided && cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)p->N * p->C * p->H * p->W, s) != cudaSuccess) return -1;
+    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, p->P, p->Q, p->H, p->W, p->stride_h, p->stride_w, s, "DLGpuConvolutionBackwardData");
+  } else {
+    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, p->H, p->W, p->H, p->W, 1, 1, s, "DLGpuConvolutionBackwardData");
+  }
+  return rc ? -1 : 1;
+}
+
+int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaStream_t s, int* oom) {
+  ConvTc* st = conv_state(p);
+  if (!st->cls || !encode_fn()) return 0;
+  std::lock_guard<std::mutex> lk(st->mu);
+  if (pack_activation(st->x, x, p->N, p->C, p->H, p->W, st, p->stride_h, p->stride_w, st->cls == 1 ? p->P : p->H, st->cls == 1 ? p->Q : p->W, 1, s, oom)) return *oom ? 1 : -1;
+  if (pack_activation(st->dy, dy, p->N, p->K, p->P, p->Q, st, 1, 1, p->P, p->Q, 2, s, oom)) return *oom ? 1 : -1;
+  GemmParams g;
+  memset(&g, 0, sizeof(g));
+  const int bn = pick_bn(p->C);
+  g.mode = kModeWgrad; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiWgrad; g.atomic = 1;
+  int rc = make_map(&g.a_hi, st->dy.hi, st->dy.rows, st->dy.cols, st->dy.pitch, 32, true);
+  if (!rc) rc = make_map(&g.a_lo, st->dy.lo, st->dy.rows, st->dy.cols, st->dy.pitch, 32, true);
+  if (!rc) rc = make_map(&g.b_hi, st->x.hi, st->x.rows, st->x.cols, st->x.pitch, 32, true);
+  if (!rc) rc = make_map(&g.b_lo, st->x.lo, st->x.rows, st->x.cols, st->x.pitch, 32, true);
+  if (rc) return -1;
+  g.M = p->K; g.N = p->C;
+  g.m_tiles = (p->K + BM - 1) / BM; g.n_tiles = (p->C + bn - 1) / bn; g.tap_tiles = p->R * p->S; g.ntaps = p->R * p->S;
+  // dy row m' holds output pixel (p, q) at frame position (p + off_h, q + off_w); tap (r, s) needs the input at
+  // padded position (p + r, q + s), i.e. row m' + (r - off_h) * frame_w + (s - off_w)
+  for (int r = 0; r < p->R; ++r) for (int q = 0; q < p->S; ++q) g.tap_off[r * p->S + q] = (r - st->off_h) * st->frame_w + (q - st->off_w);
+  long long rows = st->dy.rows;
+  int kit = (int)((rows + BK - 1) / BK);
+  int tiles = g.m_tiles * g.n_tiles * g.tap_tiles, sms = device_sm_count();
+  int splits = (2 * sms + tiles - 1) / tiles;
+  if (splits > kit / 4) splits = kit / 4;
+  if (splits < 1) splits = 1;
+  g.k_iters = (kit + splits - 1) / splits;
+  g.splits = (kit + g.k_iters - 1) / g.k_iters;
+  g.out = dw; g.err = error_word();
+  if (cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)p->K * p->C * p->R * p->S, s) != cudaSuccess) return -1;
+  double flops = 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S;
+  rc = launch_gemm_bn(bn, g, s, flops, "DLGpuConvolutionBackwardFilter");
+  return rc ? -1 : 1;
+}
+
+}  // namespace tf

@@ -367,7 +367,7 @@ using namespace tf;
 namespace tf { int dp_sgd_update(float* w, const float* g, int64_t n, float lr, cudaStream_t s); }
 
 static inline const float* F(const DLArrayHandle a) { return (const float*)a->data; }
-static inline float* FM(DLArrayHandle a) { return (float*)a->data; }
+static inline float* FM(DLArrayHandle a) { return out_f32(a); }
 
 extern "C" {
 

@@ -310,8 +310,8 @@ int DLGpuPooling2DForward(const DLArrayHandle input, DLArrayHandle output, void*
   int64_t total = numel(output);
   note_compute_stream(s);
   KernelTimer kt("DLGpuPooling2DForward", s, 0, 4.0 * (numel(input) + numel(output)));
-  if (p->mode == 0) maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (float*)output->data, nullptr, total, geom_of(p));
-  else avgpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (float*)output->data, total, geom_of(p));
+  if (p->mode == 0) maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), nullptr, total, geom_of(p));
+  else avgpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), total, geom_of(p));
   TF_AFTER(s, "DLGpuPooling2DForward");
   return 0;
 }
@@ -326,8 +326,8 @@ int DLGpuPooling2DBackward(const DLArrayHandle input, const DLArrayHandle output
   int64_t total = numel(dinput);
   note_compute_stream(s);
   KernelTimer kt("DLGpuPooling2DBackward", s, 0, 4.0 * ((p->mode == 0 ? 2 : 1) * numel(input) + numel(output)));
-  if (p->mode == 0) maxpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (const float*)doutput->data, (float*)dinput->data, total, geom_of(p));
-  else avgpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)doutput->data, (float*)dinput->data, total, geom_of(p));
+  if (p->mode == 0) maxpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (const float*)doutput->data, out_f32(dinput), total, geom_of(p));
+  else avgpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)doutput->data, out_f32(dinput), total, geom_of(p));
   TF_AFTER(s, "DLGpuPooling2DBackward");
   return 0;
 }
@@ -386,7 +386,7 @@ int DLGpuBatchNormalizationForward(const DLArrayHandle input, DLArrayHandle outp
   if (Variance_p) *Variance_p = p->save_inv;
   cudaStream_t s = stream_of(cudaStream);
   const float* x = (const float*)input->data;
-  float* y = (float*)output->data;
+  float* y = out_f32(output);
   note_compute_stream(s);
   KernelTimer kt("DLGpuBatchNormalizationForward", s, 0, 8.0 * numel(input) + 8.0 * p->nstat);
   if (p->mode == 0) {
@@ -413,7 +413,7 @@ int DLGpuBatchNormalizationBackward(const DLArrayHandle input, const DLArrayHand
   cudaStream_t s = stream_of(cudaStream);
   const float* x = (const float*)input->data;
   const float* dy = (const float*)doutput->data;
-  float* dx = (float*)dinput->data;
+  float* dx = out_f32(dinput);
   note_compute_stream(s);
   KernelTimer kt("DLGpuBatchNormalizationBackward", s, 0, 12.0 * numel(input) + 8.0 * p->nstat);
   if (p->mode == 0) {

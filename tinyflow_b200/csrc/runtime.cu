@@ -193,6 +193,7 @@ static inline size_t data_bytes(const DLArray* a) { return (size_t)numel(a) * 4;
 
 }  // namespace tf
 
+namespace tf { int tensor_path_error(); }
 using namespace tf;
 
 extern "C" {
@@ -236,6 +237,7 @@ int DLArrayAlloc(const index_t* shape, index_t ndim_in, DLContext ctx, DLArrayHa
 int DLArrayFree(DLArrayHandle handle) {
   if (!handle) return 0;
   if (handle->data) {
+    if (handle->ctx.device_type == kGPU) note_write(handle->data);   // a recycled block is new data
     bool ok = (handle->ctx.device_type == kGPU) ? device_pool().free(handle->data)
                                                 : host_pool().free(handle->data);
     if (!ok) TF_FAIL("DLArrayFree: array was not allocated by DLArrayAlloc");
@@ -256,6 +258,7 @@ int DLArrayCopyFromTo(DLArrayHandle from, DLArrayHandle to, DLStreamHandle strea
   TF_CUDA(cudaSetDevice(fg ? from->ctx.device_id : to->ctx.device_id));
   cudaMemcpyKind kind = fg && tg ? cudaMemcpyDeviceToDevice : (fg ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice);
   if (bytes == 0) return 0;
+  if (tg) note_write(to->data);
   if (stream == nullptr) {
     // Blocking copy on the legacy default stream: ordered after everything already
     // enqueued on the (blocking) compute streams, and complete on return.
@@ -370,7 +373,11 @@ int TfKernelTimingReport(char* buf, int buflen) {
   return 0;
 }
 
-int TfDeviceSynchronize(void) { TF_CUDA(cudaDeviceSynchronize()); return 0; }
+int TfDeviceSynchronize(void) {
+  TF_CUDA(cudaDeviceSynchronize());
+  TF_REQUIRE(tensor_path_error() == 0, "a tensor-core kernel timed out waiting on a barrier (results of that launch are invalid)");
+  return 0;
+}
 int TfLaunchCount(long long* count) { if (count) *count = g_launches.load(); return 0; }
 int TfLastError(char* buf, int buflen) {
   if (buf && buflen > 0) { strncpy(buf, t_err, buflen - 1); buf[buflen - 1] = 0; }
