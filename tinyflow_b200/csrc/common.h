@@ -107,6 +107,11 @@ struct PoolPlan {
   int mode;              // 0 max, 1 average (divisor includes padding)
   int pad_h, pad_w, stride_h, stride_w, win_h, win_w;
   int dataformat;
+  // max pooling: first-maximum index per output, written by forward and reused by backward while the
+  // input tensor (pointer + write version) is unchanged
+  int32_t* argmax;
+  const void* argmax_src;
+  uint64_t argmax_version;
 };
 struct TensorPlan {      // activation / dropout input descriptor
   int kind;

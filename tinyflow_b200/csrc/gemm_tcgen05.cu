@@ -538,7 +538,10 @@ template <int BN> static int launch_gemm(const GemmParams& p, cudaStream_t s, do
   int tiles = p.m_tiles * p.n_tiles * p.tap_tiles * p.splits;
   int grid = tiles < device_sm_count() ? tiles : device_sm_count();
   note_compute_stream(s);
-  KernelTimer kt("gemm3xtf32_tcgen05", s, flops, 0, 1);
+  static const bool detail = getenv("TINYFLOW_TIMING_DETAIL") != nullptr;    // one timing row per distinct problem shape
+  char name[160];
+  if (detail) snprintf(name, sizeof(name), "gemm3xtf32 mode%d M%d N%d kiters%d taps%d splits%d bn%d tiles%d %s", p.mode, p.M, p.N, p.k_iters, p.tap_tiles, p.splits, BN, tiles, what + 5);
+  KernelTimer kt(detail ? name : "gemm3xtf32_tcgen05", s, flops, 0, 1);
   gemm3xtf32_kernel<BN><<<grid, kThreads, L::kTotal, s>>>(p);
   TF_AFTER(s, what);
   return 0;

@@ -68,6 +68,27 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restric
     dx[i] = acc;
   }
 }
+// Same gather, but with the forward pass's saved first-maximum indices: one index load per covering window
+// instead of a window scan.
+__global__ void __launch_bounds__(256) maxpool_bwd_idx_kernel(const int32_t* __restrict__ idx, const float* __restrict__ dy, float* __restrict__ dx, int64_t total, PoolGeom g) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int HW = g.H * g.W, PQ = g.P * g.Q;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t plane = i / HW;
+    int hw = (int)(i % HW), h = hw / g.W, w = hw % g.W;
+    const int32_t* ip = idx + plane * PQ;
+    const float* dp = dy + plane * PQ;
+    int p_lo = (h + g.ph - g.kh + g.sh) / g.sh; if (h + g.ph - g.kh + 1 <= 0) p_lo = 0;
+    int p_hi = min(g.P - 1, (h + g.ph) / g.sh);
+    int q_lo = (w + g.pw - g.kw + g.sw) / g.sw; if (w + g.pw - g.kw + 1 <= 0) q_lo = 0;
+    int q_hi = min(g.Q - 1, (w + g.pw) / g.sw);
+    float acc = 0.f;
+    for (int p = p_lo; p <= p_hi; ++p)
+      for (int q = q_lo; q <= q_hi; ++q)
+        if (__ldg(ip + p * g.Q + q) == hw) acc += __ldg(dp + p * g.Q + q);
+    dx[i] = acc;
+  }
+}
 __global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t total, PoolGeom g) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   int PQ = g.P * g.Q;
@@ -120,86 +141,150 @@ static PoolGeom geom_of(const PoolPlan* p) {
 // (src/gpu_op.cu:4224-4460).  Forward saves the mean and 1/sqrt(var+eps) it used; backward
 // computes  dx = inv * (dy - mean(dy) - xhat * mean(dy * xhat))  with xhat = (x - mean) * inv.
 //
-// Per-activation mode: one statistic per (c,h,w) feature, reduced over the batch only.  Threads
-// own consecutive features (coalesced across the warp for every sample) and keep their whole
-// batch column in registers, so x (and dy) cross HBM exactly once.
+// Per-activation mode: one statistic per (c,h,w) feature, reduced over the batch only.  A warp
+// owns 32 consecutive 128-bit feature vectors (coalesced for every sample), the batch is split over the
+// eight warps of the block, and every value stays in registers between the reduction and the apply
+// pass, so x (and dy) cross HBM exactly once.
 // =====================================================================================
 constexpr float kBnEps = 1e-5f;
-constexpr int kBnMaxBatchInRegs = 64;
+constexpr int kBnMaxBatchInRegs = 64;     // = kBnGroups * kBnPerThread
 
 template <int VEC> struct VecT;
 template <> struct VecT<1> { using type = float; };
 template <> struct VecT<2> { using type = float2; };
 template <> struct VecT<4> { using type = float4; };
 
-template <int NB, int VEC>
-__global__ void __launch_bounds__(128) bn_pa_fwd_regs_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ save_mean, float* __restrict__ save_inv, int N, int64_t F) {
+// Block = 32 feature vectors x kBnGroups sample groups.  Thread (tx, ty) owns feature vector fv0 + tx and the
+// samples ty, ty + kBnGroups, ...: each warp reads 32 consecutive feature vectors of one sample (coalesced),
+// every thread keeps only N / kBnGroups values per tensor in registers, and the per-feature sums are combined
+// across the sample groups through shared memory.
+constexpr int kBnGroups = 8;
+constexpr int kBnPerThread = 8;          // covers batches up to 64
+
+template <int VEC>
+__device__ __forceinline__ void bn_group_sum(float (&part)[VEC], float (*red)[32][VEC], int tx, int ty) {
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) red[ty][tx][k] = part[k];
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    float t = 0.f;
+#pragma unroll
+    for (int g = 0; g < kBnGroups; ++g) t += red[g][tx][k];
+    part[k] = t;
+  }
+  __syncthreads();
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(32 * kBnGroups) bn_pa_fwd_regs_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ save_mean, float* __restrict__ save_inv, int N, int64_t F) {
   using V = typename VecT<VEC>::type;
-  int64_t fv = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;       // vector index over features
-  int64_t FV = F / VEC;
-  if (fv >= FV) return;
+  __shared__ float red[kBnGroups][32][VEC];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t FV = F / VEC;
+  const int64_t fv = (int64_t)blockIdx.x * 32 + tx;
+  const bool live = fv < FV;
   const V* xv = reinterpret_cast<const V*>(x);
   V* yv = reinterpret_cast<V*>(y);
-  float v[NB][VEC];
+  float v[kBnPerThread][VEC];
 #pragma unroll
-  for (int n = 0; n < NB; ++n) {
-    if (n < N) {
-      V t = xv[(int64_t)n * FV + fv];
-      const float* tp = reinterpret_cast<const float*>(&t);
+  for (int i = 0; i < kBnPerThread; ++i) {
+    int n = ty + i * kBnGroups;
+    V t = {};
+    if (live && n < N) t = xv[(int64_t)n * FV + fv];
+    const float* tp = reinterpret_cast<const float*>(&t);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) v[n][k] = tp[k];
-    }
+    for (int k = 0; k < VEC; ++k) v[i][k] = tp[k];
   }
+  const float rn = 1.f / (float)N;
   float mean[VEC], inv[VEC];
-  float rn = 1.f / (float)N;
 #pragma unroll
   for (int k = 0; k < VEC; ++k) {
     float s = 0.f;
 #pragma unroll
-    for (int n = 0; n < NB; ++n) if (n < N) s += v[n][k];
-    float m = s * rn, q = 0.f;
+    for (int i = 0; i < kBnPerThread; ++i) s += v[i][k];       // missing samples were loaded as 0
+    mean[k] = s;
+  }
+  bn_group_sum<VEC>(mean, red, tx, ty);
 #pragma unroll
-    for (int n = 0; n < NB; ++n) if (n < N) { float d = v[n][k] - m; q += d * d; }
-    mean[k] = m;
-    inv[k] = rsqrtf(q * rn + kBnEps);
-    // one Newton step brings rsqrtf to full fp32 accuracy
-    float a = q * rn + kBnEps;
-    inv[k] = inv[k] * (1.5f - 0.5f * a * inv[k] * inv[k]);
+  for (int k = 0; k < VEC; ++k) {
+    mean[k] *= rn;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < kBnPerThread; ++i) { float d = v[i][k] - mean[k]; if (ty + i * kBnGroups < N) q += d * d; }
+    inv[k] = q;
+  }
+  bn_group_sum<VEC>(inv, red, tx, ty);
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    float a = inv[k] * rn + kBnEps;
+    float r = rsqrtf(a);
+    inv[k] = r * (1.5f - 0.5f * a * r * r);       // one Newton step: full fp32 accuracy
   }
 #pragma unroll
-  for (int n = 0; n < NB; ++n) {
-    if (n < N) {
+  for (int i = 0; i < kBnPerThread; ++i) {
+    int n = ty + i * kBnGroups;
+    if (live && n < N) {
       V t;
       float* tp = reinterpret_cast<float*>(&t);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) tp[k] = (v[n][k] - mean[k]) * inv[k];
+      for (int k = 0; k < VEC; ++k) tp[k] = (v[i][k] - mean[k]) * inv[k];
       yv[(int64_t)n * FV + fv] = t;
     }
   }
+  if (live && ty == 0) {
 #pragma unroll
-  for (int k = 0; k < VEC; ++k) { save_mean[fv * VEC + k] = mean[k]; save_inv[fv * VEC + k] = inv[k]; }
+    for (int k = 0; k < VEC; ++k) { save_mean[fv * VEC + k] = mean[k]; save_inv[fv * VEC + k] = inv[k]; }
+  }
 }
 
-template <int NB>
-__global__ void __launch_bounds__(128) bn_pa_bwd_regs_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, const float* __restrict__ save_mean, const float* __restrict__ save_inv, int N, int64_t F) {
-  int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (f >= F) return;
-  float m = save_mean[f], inv = save_inv[f];
-  float xh[NB], g[NB];
-  float s1 = 0.f, s2 = 0.f;
+template <int VEC>
+__global__ void __launch_bounds__(32 * kBnGroups) bn_pa_bwd_regs_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, const float* __restrict__ save_mean, const float* __restrict__ save_inv, int N, int64_t F) {
+  using V = typename VecT<VEC>::type;
+  __shared__ float red[kBnGroups][32][VEC];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t FV = F / VEC;
+  const int64_t fv = (int64_t)blockIdx.x * 32 + tx;
+  const bool live = fv < FV;
+  const V* xv = reinterpret_cast<const V*>(x);
+  const V* gv = reinterpret_cast<const V*>(dy);
+  V* ov = reinterpret_cast<V*>(dx);
+  float m[VEC], inv[VEC];
 #pragma unroll
-  for (int n = 0; n < NB; ++n) {
-    if (n < N) {
-      xh[n] = (x[(int64_t)n * F + f] - m) * inv;
-      g[n] = dy[(int64_t)n * F + f];
-      s1 += g[n];
-      s2 += g[n] * xh[n];
+  for (int k = 0; k < VEC; ++k) { m[k] = live ? save_mean[fv * VEC + k] : 0.f; inv[k] = live ? save_inv[fv * VEC + k] : 0.f; }
+  float xh[kBnPerThread][VEC], g[kBnPerThread][VEC];
+#pragma unroll
+  for (int i = 0; i < kBnPerThread; ++i) {
+    int n = ty + i * kBnGroups;
+    V a = {}, b = {};
+    if (live && n < N) { a = xv[(int64_t)n * FV + fv]; b = gv[(int64_t)n * FV + fv]; }
+    const float* ap = reinterpret_cast<const float*>(&a);
+    const float* bp = reinterpret_cast<const float*>(&b);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) { xh[i][k] = (live && n < N) ? (ap[k] - m[k]) * inv[k] : 0.f; g[i][k] = bp[k]; }
+  }
+  float s1[VEC], s2[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int i = 0; i < kBnPerThread; ++i) { a += g[i][k]; b += g[i][k] * xh[i][k]; }
+    s1[k] = a; s2[k] = b;
+  }
+  bn_group_sum<VEC>(s1, red, tx, ty);
+  bn_group_sum<VEC>(s2, red, tx, ty);
+  const float rn = 1.f / (float)N;
+#pragma unroll
+  for (int i = 0; i < kBnPerThread; ++i) {
+    int n = ty + i * kBnGroups;
+    if (live && n < N) {
+      V t;
+      float* tp = reinterpret_cast<float*>(&t);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) tp[k] = inv[k] * (g[i][k] - s1[k] * rn - xh[i][k] * s2[k] * rn);
+      ov[(int64_t)n * FV + fv] = t;
     }
   }
-  float rn = 1.f / (float)N;
-  s1 *= rn; s2 *= rn;
-#pragma unroll
-  for (int n = 0; n < NB; ++n) if (n < N) dx[(int64_t)n * F + f] = inv * (g[n] - s1 - xh[n] * s2);
 }
 
 // Any batch size: three passes over the batch column (the re-reads are served by L2).
@@ -261,10 +346,13 @@ __global__ void __launch_bounds__(512) bn_sp_bwd_kernel(const float* __restrict_
   for (int64_t i = threadIdx.x; i < cnt; i += blockDim.x) { int64_t o = ((i / HW) * C + c) * HW + i % HW; dx[o] = inv * (dy[o] - s1 - (x[o] - m) * inv * s2); }
 }
 
-template <int NB> static void launch_bn_fwd_regs(const float* x, float* y, float* sm, float* si, int N, int64_t F, cudaStream_t s) {
-  bool v2 = (F % 2 == 0) && aligned16(x) && aligned16(y) && NB <= 64;
-  if (v2) { int64_t FV = F / 2; bn_pa_fwd_regs_kernel<NB, 2><<<(unsigned)((FV + 127) / 128), 128, 0, s>>>(x, y, sm, si, N, F); }
-  else bn_pa_fwd_regs_kernel<NB, 1><<<(unsigned)((F + 127) / 128), 128, 0, s>>>(x, y, sm, si, N, F);
+static void launch_bn_fwd_regs(const float* x, float* y, float* sm, float* si, int N, int64_t F, cudaStream_t s) {
+  if (F % 4 == 0 && aligned16(x) && aligned16(y)) bn_pa_fwd_regs_kernel<4><<<(unsigned)((F / 4 + 31) / 32), 32 * kBnGroups, 0, s>>>(x, y, sm, si, N, F);
+  else bn_pa_fwd_regs_kernel<1><<<(unsigned)((F + 31) / 32), 32 * kBnGroups, 0, s>>>(x, y, sm, si, N, F);
+}
+static void launch_bn_bwd_regs(const float* x, const float* dy, float* dx, const float* sm, const float* si, int N, int64_t F, cudaStream_t s) {
+  if (F % 4 == 0 && aligned16(x) && aligned16(dy) && aligned16(dx)) bn_pa_bwd_regs_kernel<4><<<(unsigned)((F / 4 + 31) / 32), 32 * kBnGroups, 0, s>>>(x, dy, dx, sm, si, N, F);
+  else bn_pa_bwd_regs_kernel<1><<<(unsigned)((F + 31) / 32), 32 * kBnGroups, 0, s>>>(x, dy, dx, sm, si, N, F);
 }
 
 }  // namespace tf
@@ -309,8 +397,13 @@ int DLGpuPooling2DForward(const DLArrayHandle input, DLArrayHandle output, void*
   cudaStream_t s = stream_of(cudaStream);
   int64_t total = numel(output);
   note_compute_stream(s);
+  if (p->mode == 0 && !p->argmax) p->argmax = (int32_t*)pool_alloc(sizeof(int32_t) * (size_t)total);   // optional: backward rescans if absent
   KernelTimer kt("DLGpuPooling2DForward", s, 0, 4.0 * (numel(input) + numel(output)));
-  if (p->mode == 0) maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), nullptr, total, geom_of(p));
+  if (p->mode == 0) {
+    maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), p->argmax, total, geom_of(p));
+    p->argmax_src = input->data;
+    p->argmax_version = version_of(input->data);
+  }
   else avgpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), total, geom_of(p));
   TF_AFTER(s, "DLGpuPooling2DForward");
   return 0;
@@ -326,7 +419,12 @@ int DLGpuPooling2DBackward(const DLArrayHandle input, const DLArrayHandle output
   int64_t total = numel(dinput);
   note_compute_stream(s);
   KernelTimer kt("DLGpuPooling2DBackward", s, 0, 4.0 * ((p->mode == 0 ? 2 : 1) * numel(input) + numel(output)));
-  if (p->mode == 0) maxpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (const float*)doutput->data, out_f32(dinput), total, geom_of(p));
+  if (p->mode == 0) {
+    if (p->argmax && p->argmax_src == input->data && p->argmax_version == version_of(input->data))
+      maxpool_bwd_idx_kernel<<<grid_for(total, 256), 256, 0, s>>>(p->argmax, (const float*)doutput->data, out_f32(dinput), total, geom_of(p));
+    else
+      maxpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (const float*)doutput->data, out_f32(dinput), total, geom_of(p));
+  }
   else avgpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)doutput->data, out_f32(dinput), total, geom_of(p));
   TF_AFTER(s, "DLGpuPooling2DBackward");
   return 0;
@@ -392,9 +490,7 @@ int DLGpuBatchNormalizationForward(const DLArrayHandle input, DLArrayHandle outp
   if (p->mode == 0) {
     int64_t F = p->nstat;
     int N = (int)p->N;
-    if (N <= 8) launch_bn_fwd_regs<8>(x, y, p->save_mean, p->save_inv, N, F, s);
-    else if (N <= 32) launch_bn_fwd_regs<32>(x, y, p->save_mean, p->save_inv, N, F, s);
-    else if (N <= kBnMaxBatchInRegs) launch_bn_fwd_regs<64>(x, y, p->save_mean, p->save_inv, N, F, s);
+    if (N <= kBnMaxBatchInRegs) launch_bn_fwd_regs(x, y, p->save_mean, p->save_inv, N, F, s);
     else bn_pa_fwd_loop_kernel<<<(unsigned)((F + 127) / 128), 128, 0, s>>>(x, y, p->save_mean, p->save_inv, N, F);
   } else {
     bn_sp_fwd_kernel<<<(unsigned)p->C, 512, 0, s>>>(x, y, p->save_mean, p->save_inv, p->N, p->C, p->HW);
@@ -420,9 +516,7 @@ int DLGpuBatchNormalizationBackward(const DLArrayHandle input, const DLArrayHand
     int64_t F = p->nstat;
     int N = (int)p->N;
     unsigned grid = (unsigned)((F + 127) / 128);
-    if (N <= 8) bn_pa_bwd_regs_kernel<8><<<grid, 128, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, N, F);
-    else if (N <= 32) bn_pa_bwd_regs_kernel<32><<<grid, 128, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, N, F);
-    else if (N <= kBnMaxBatchInRegs) bn_pa_bwd_regs_kernel<64><<<grid, 128, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, N, F);
+    if (N <= kBnMaxBatchInRegs) launch_bn_bwd_regs(x, dy, dx, p->save_mean, p->save_inv, N, F, s);
     else bn_pa_bwd_loop_kernel<<<grid, 128, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, N, F);
   } else {
     bn_sp_bwd_kernel<<<(unsigned)p->C, 512, 0, s>>>(x, dy, dx, p->save_mean, p->save_inv, p->N, p->C, p->HW);
