@@ -21,8 +21,8 @@
 //
 // Kernel roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-5 =
 // epilogue (one TMEM lane quarter each).  Shared memory holds a ring of stages {A_hi, A_lo, B_hi, B_lo}
-// (128-byte swizzle, 32 fp32 of K per stage); TMEM holds two accumulators so the epilogue of tile i
-// overlaps the main loop of tile i+1.  Every mbarrier wait is bounded: on time-out the CTA raises an
+// (128-byte swizzle, 32 fp32 of K per stage); TMEM holds two accumulators so that promoting one group of
+// stages to registers overlaps the MMAs of the next.  Every mbarrier wait is bounded: on time-out the CTA raises an
 // error flag the host reads, drains its outstanding copies, frees its TMEM and returns.
 #include "common.h"
 #include <cuda.h>
@@ -115,6 +115,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, descriptor version 1 (Blackwell).
@@ -151,6 +159,7 @@ struct alignas(64) GemmParams {
   // element (image, channel c, i, j) lives at ((image*out_c + c)*out_h + i*out_sh)*out_w + j*out_sw
   int frame_h, frame_w, valid_h, valid_w, out_c, out_h, out_w, out_sh, out_sw;
   int* err;                       // device-visible error word (mapped host memory)
+  int group_iters;                // stages accumulated in TMEM before the epilogue promotes them to registers
   int tap_off[kMaxTaps];          // row shift per tap (A rows for kModeConv, B rows for kModeWgrad)
 };
 
@@ -184,8 +193,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {   // TMEM: two accumulators of BN fp32 columns each
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+  if (warp == 1) {   // TMEM: two accumulators of 2*BN fp32 columns each
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(4 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tcgen05_fence_before();
@@ -267,8 +276,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
-                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      // The B stage holds [B_hi ; B_lo] back to back, so ONE instruction with N = 2*BN computes A_hi*B_hi (columns
+      // 0..BN-1) and A_hi*B_lo (columns BN..2BN-1); a second one with N = BN adds A_lo*B_hi.  Two instructions per
+      // K step instead of three: a tcgen05.mma of this size costs ~115 cycles to issue whatever its N.
+      const uint32_t idesc_base = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t idesc_wide = idesc_base | ((uint32_t)((2 * BN) >> 3) << 17), idesc_narrow = idesc_base | ((uint32_t)(BN >> 3) << 17);
       const uint32_t a_lbo = p.a_mn ? 4096u : 16u, b_lbo = p.b_mn ? 4096u : 16u;
       const uint32_t a_kstep = p.a_mn ? 1024u : 32u, b_kstep = p.b_mn ? 1024u : 32u;
       const uint32_t a_sbo = p.a_mn ? 512u : 1024u, b_sbo = p.b_mn ? 512u : 1024u;
@@ -277,24 +289,23 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
       int group = 0;            // accumulator groups issued so far (alternating TMEM buffers)
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        for (int it0 = 0; it0 < p.k_iters && ok; it0 += kGroupIters, ++group) {
+        for (int it0 = 0; it0 < p.k_iters && ok; it0 += p.group_iters, ++group) {
           const int acc = group & 1;
           if (!mbar_wait(&acc_empty[acc], ((group >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * BN;
-          const int it1 = min(it0 + kGroupIters, p.k_iters);
+          const uint32_t d_tmem = tmem_base + acc * 2 * BN;
+          const int it1 = min(it0 + p.group_iters, p.k_iters);
           for (int it = it0; it < it1; ++it) {
             if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
             const uint32_t st = smem_u32(smem + stage * L::kStageBytes);
-            const uint32_t a_hi = st, a_lo = st + L::kABytes, b_hi = st + 2 * L::kABytes, b_lo = b_hi + L::kBBytes;
+            const uint32_t a_hi = st, a_lo = st + L::kABytes, b_hi = st + 2 * L::kABytes;
 #pragma unroll
             for (int k = 0; k < BK / 8; ++k) {
               const uint64_t ah = umma_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lt), al = umma_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lt);
-              const uint64_t bh = umma_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lt), bl = umma_desc(b_lo + k * b_kstep, b_lbo, b_sbo, b_lt);
-              umma_tf32(d_tmem, al, bh, idesc, (it > it0 || k > 0) ? 1u : 0u);     // small terms first
-              umma_tf32(d_tmem, ah, bl, idesc, 1u);
-              umma_tf32(d_tmem, ah, bh, idesc, 1u);
+              const uint64_t bh = umma_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lt);      // N = 2*BN runs on into B_lo
+              umma_tf32(d_tmem, ah, bh, idesc_wide, (it > it0 || k > 0) ? 1u : 0u);
+              umma_tf32(d_tmem, al, bh, idesc_narrow, 1u);
             }
             tcgen05_commit(&empty[stage]);       // frees the stage once the MMAs above have read it
             if (++stage == L::kStages) { stage = 0; phase ^= 1; }
@@ -318,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
       float accv[BN];
 #pragma unroll
       for (int q = 0; q < BN; ++q) accv[q] = 0.f;
-      for (int it0 = 0; it0 < p.k_iters && ok; it0 += kGroupIters, ++group) {
+      for (int it0 = 0; it0 < p.k_iters && ok; it0 += p.group_iters, ++group) {
         const int acc = group & 1;
         {   // lane 0 polls, the warp follows: keeps the warp converged for the .sync.aligned TMEM loads
           int got = lane == 0 ? (int)mbar_wait(&acc_full[acc], (group >> 1) & 1, abort_flag) : 1;
@@ -326,14 +337,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
           if (!got) { ok = false; break; }
         }
         tcgen05_fence_after();
-        const uint32_t t_base = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t t_base = tmem_base + acc * 2 * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          float v[32];
-          tmem_ld32(t_base + c0, v);
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v1[16], v2[16];
+          tmem_ld16(t_base + c0, v1);              // A_hi*B_hi + A_lo*B_hi
+          tmem_ld16(t_base + BN + c0, v2);         // A_hi*B_lo
           tmem_ld_wait();
 #pragma unroll
-          for (int q = 0; q < 32; ++q) accv[c0 + q] += v[q];
+          for (int q = 0; q < 16; ++q) accv[c0 + q] += v1[q] + v2[q];
         }
         tcgen05_fence_before();
         __syncwarp();
@@ -382,7 +394,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(4 * BN) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
 }
@@ -535,6 +547,8 @@ template <int BN> static int launch_gemm(const GemmParams& p, cudaStream_t s, do
     g_attr_done[slot] = true;
   }
   TF_REQUIRE(tensor_path_error() == 0, "%s: an earlier tensor-core kernel timed out on a barrier; refusing to launch", what);
+  static const int group_iters = getenv("TINYFLOW_GROUP_ITERS") ? atoi(getenv("TINYFLOW_GROUP_ITERS")) : kGroupIters;
+  const_cast<GemmParams&>(p).group_iters = group_iters > 0 ? group_iters : kGroupIters;
   int tiles = p.m_tiles * p.n_tiles * p.tap_tiles * p.splits;
   int grid = tiles < device_sm_count() ? tiles : device_sm_count();
   note_compute_stream(s);

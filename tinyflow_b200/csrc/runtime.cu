@@ -112,6 +112,7 @@ struct Pool {
   std::unordered_map<void*, size_t> size_of;   // every block we own, in use or cached
   long long in_use = 0, cached = 0;
   bool host;
+  bool failed_hard = false;      // an allocation failed for a reason other than running out of memory
   explicit Pool(bool h) : host(h) {}
 
   static size_t round(size_t b) {
@@ -144,6 +145,12 @@ struct Pool {
     }
     void* p = nullptr;
     cudaError_t e = raw_alloc(&p, b);
+    if (e != cudaSuccess && e != cudaErrorMemoryAllocation) {
+      // not an out-of-memory condition: the context is unusable (an earlier kernel faulted)
+      failed_hard = true;
+      set_error("device allocation failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
     if (e != cudaSuccess) {
       cudaGetLastError();
       // Give cached blocks back to the driver and try once more before reporting OOM.
@@ -219,6 +226,7 @@ int DLArrayAlloc(const index_t* shape, index_t ndim_in, DLContext ctx, DLArrayHa
   } else {
     TF_FAIL("DLArrayAlloc: unknown device type %d", (int)ctx.device_type);
   }
+  if (!data && (device_pool().failed_hard || host_pool().failed_hard)) return -1;   // message already set
   if (!data) {
     if (memorytoSaving) *memorytoSaving = bytes > 0x7fffffffu ? 0x7fffffff : (int)bytes;
     return 0;
