@@ -267,6 +267,13 @@ int TfDpInit(int rank, int world_size, const char *nccl_id_path);
 int TfDpFlush(void **cudaStream);
 int TfDpShutdown(void);
 
+/* Allocation-free twin of DLGpuReduceSumAll (no counterpart in the reference): output[0] = sum of all
+ * elements of input, with the per-block partial sums kept in a fixed 16 KiB array inside the library
+ * instead of pooled memory, for callers that must not allocate while they run.  At most 33,554,432 input
+ * elements (-1 beyond that).  All calls share the array, so calls that overlap on the GPU race.  The first
+ * call on a device resolves the array's address and should precede any stream capture. */
+int DLGpuReduceSumAllStatic(const DLArrayHandle input, DLArrayHandle output, void **cudaStream);
+
 /* Test / profiling hooks. */
 int TfPoolingArgmax(const DLArrayHandle input, int32_t *indices_dev, void ***cudnnlist,
                     void **cudaStream);   /* first-maximum index (h*W+w in the input plane) per output */

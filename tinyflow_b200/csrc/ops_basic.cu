@@ -535,6 +535,63 @@ int DLGpuReduceSumAll(const DLArrayHandle input, DLArrayHandle output) {
   TF_REQUIRE(input && output && numel(output) == 1, "DLGpuReduceSumAll: output must hold one element");
   return reduce_to_scalar(F(input), FM(output), numel(input), 1.f, 0, "DLGpuReduceSumAll");
 }
+}  // extern "C" (reopened below)
+
+// ---- sum of all elements without any allocation ------------------------------------------------
+// Some callers must not allocate while they run: code that replays a fixed sequence of launches and may
+// not touch the allocator in between, code running inside a memory-planned region where every byte of the
+// device is already assigned (the swap / recompute scheduler sizes its plan to the last byte), or a host
+// thread that must not take the allocator's lock.  DLGpuReduceSumAll needs a scratch buffer for its
+// per-block partial sums and gets it from the pool; this variant keeps that scratch in a fixed array that
+// is part of the library image instead, so it calls no cudaMalloc / cudaFree / pool routine at all.
+//
+// The price is a size limit and shared state: the array holds kStaticPartials floats (16 KiB, resident on
+// every GPU that loads the library until the process exits), one per block of kStaticElemsPerBlock inputs,
+// so inputs above kStaticMaxElems elements are refused.  All calls use the same array: two calls that
+// overlap on the GPU (different streams, or different host threads) race on it; calls on one stream are
+// safe.  Nothing has to start at zero (each call overwrites exactly the partials it then reads).
+constexpr int kStaticPartials = 4096;
+constexpr int kStaticElemsPerBlock = kBlock * 32;                                   // 8192 inputs per block
+constexpr long long kStaticMaxElems = (long long)kStaticPartials * kStaticElemsPerBlock;   // 33,554,432 floats (128 MiB)
+static __device__ __align__(256) float g_static_partials[kStaticPartials];
+
+// In host code `g_static_partials` is only a handle for the symbol, not a device address; the address a
+// kernel can use comes from cudaGetSymbolAddress, once per device, with that device current.
+static float* static_partials_ptr() {
+  static float* ptr[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); set_error("DLGpuReduceSumAllStatic: no current device"); return nullptr; }
+  if (!ptr[dev]) {
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_partials);
+    if (e != cudaSuccess) { cudaGetLastError(); set_error("DLGpuReduceSumAllStatic: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); return nullptr; }
+    ptr[dev] = p;
+  }
+  return ptr[dev];
+}
+
+extern "C" {
+
+// output[0] = sum of every element of input, computed on *cudaStream (NULL: the legacy default stream).
+// Allocation-free twin of DLGpuReduceSumAll; see the notes above.  The first call on a device looks up the
+// scratch array's device address (a host-side runtime query, no allocation) and should therefore be made
+// before any stream capture begins on that device; later calls only launch two kernels.
+int DLGpuReduceSumAllStatic(const DLArrayHandle input, DLArrayHandle output, void** cudaStream) {
+  TF_REQUIRE(input && output && numel(output) == 1, "DLGpuReduceSumAllStatic: output must hold one element");
+  const int64_t n = numel(input);
+  TF_REQUIRE(n <= kStaticMaxElems, "DLGpuReduceSumAllStatic: %lld elements exceed the fixed scratch capacity of %lld elements; use DLGpuReduceSumAll", (long long)n, kStaticMaxElems);
+  float* part = static_partials_ptr();
+  if (!part) return -1;
+  cudaStream_t s = stream_of(cudaStream);
+  int blocks = (int)((n + kStaticElemsPerBlock - 1) / kStaticElemsPerBlock);
+  if (blocks < 1) blocks = 1;
+  note_compute_stream(s);
+  partial_sum_kernel<<<blocks, kBlock, 0, s>>>(F(input), part, n);
+  final_sum_kernel<<<1, kBlock, 0, s>>>(part, FM(output), blocks, 1.f);
+  if (after_launch(s, "DLGpuReduceSumAllStatic", 2) != 0) return -1;
+  return 0;
+}
+
 int DLGpuReduceSumAllBackward(const DLArrayHandle input, DLArrayHandle output) {
   TF_REQUIRE(input && output && numel(input) >= 1, "null array");
   int64_t total = numel(output);

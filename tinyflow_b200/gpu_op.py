@@ -408,6 +408,13 @@ def testPcie():
 
 
 # ---- additions with no counterpart in the reference -------------------------------------------
+def reduce_sum_all_static(in_arr, out_arr, cudaStream):
+    """Sum of all elements into out_arr (one element) without any device allocation: the twin of
+    ``reduce_sum(in_arr, out_arr, -1)`` for callers that must not allocate while they run.  Refuses inputs
+    above 33,554,432 elements; calls share one fixed scratch array, so keep them on a single stream."""
+    check_call(_LIB.DLGpuReduceSumAllStatic(_h(in_arr), _h(out_arr), cudaStream))
+
+
 def device_synchronize():
     check_call(_LIB.TfDeviceSynchronize())
 
