@@ -266,6 +266,10 @@ int TfDpInit(int rank, int world_size, const char *nccl_id_path);
  * end of a step, before parameters are read back). */
 int TfDpFlush(void **cudaStream);
 int TfDpShutdown(void);
+int TfDpStats(long long *bytes_reduced, long long *allreduces);   /* totals since TfDpInit */
+/* Host-only: the bucket each gradient tensor lands in, given tensor sizes (floats) in arrival order and the
+ * bucket capacity; a tensor larger than the capacity gets -(id+1).  Returns the number of buckets. */
+int TfDpPlanBuckets(const long long *counts, int n, long long capacity_floats, int *bucket_of);
 
 /* Allocation-free twin of DLGpuReduceSumAll (no counterpart in the reference): output[0] = sum of all
  * elements of input, with the per-block partial sums kept in a fixed 16 KiB array inside the library
