@@ -19,14 +19,15 @@
 //                     are M/N-major, the reduction runs over pixel rows, split over CTAs and combined
 //                     with fp32 atomics.
 //
-// Kernel roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-5 =
-// epilogue (one TMEM lane quarter each).  Shared memory holds a ring of stages {A_hi, A_lo, B_hi, B_lo}
+// Kernel roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-9 =
+// epilogue (two per TMEM lane quarter, half the columns each).  Shared memory holds a ring of stages {A_hi, A_lo, B_hi, B_lo}
 // (128-byte swizzle, 32 fp32 of K per stage); TMEM holds two accumulators so that promoting one group of
 // stages to registers overlaps the MMAs of the next.  Every mbarrier wait is bounded: on time-out the CTA raises an
 // error flag the host reads, drains its outstanding copies, frees its TMEM and returns.
 #include "common.h"
 #include <cuda.h>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 namespace tf {
@@ -53,7 +54,7 @@ uint64_t version_of(const void* p) {
 // ------------------------------------------------------------------------------------------------
 constexpr int BM = 128;            // UMMA M (TMEM lanes)
 constexpr int BK = 32;             // fp32 elements of K per stage = one 128-byte swizzle row
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
 constexpr int kGroupIters = 4;     // stages accumulated in TMEM before the epilogue promotes them to registers
 constexpr long long kWaitCycles = 3000000000ll;   // ~1.5 s at 2 GHz: far beyond any legitimate wait
 
@@ -149,6 +150,7 @@ struct alignas(64) GemmParams {
   int M, N;                       // valid extents of the output tile grid
   int m_tiles, n_tiles, tap_tiles, splits;
   int k_iters;                    // stages per (tile, split)
+  int k_total;                    // stages of the whole reduction; the last split may be shorter
   int chunks_per_tap;             // kModeConv: 32-channel chunks per tap
   int b_tap_pitch;                // kModeConv: columns per tap in the packed filter
   int ntaps;
@@ -189,7 +191,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -203,6 +205,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
   const uint32_t tmem_base = *tmem_slot;
 
   // tile index -> coordinates; n fastest so consecutive CTAs share the A tile through L2
+  auto kcount_of = [&](int split) { return min(p.k_iters, p.k_total - split * p.k_iters); };
   auto decode = [&](int tile, int& mt, int& nt, int& tap, int& split) {
     split = tile % p.splits; tile /= p.splits;
     nt = tile % p.n_tiles; tile /= p.n_tiles;
@@ -221,7 +224,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
         int mt, nt, tap, split;
         decode(tile, mt, nt, tap, split);
         const int m0 = mt * BM, n0 = nt * BN;
-        for (int it = 0; it < p.k_iters; ++it) {
+        const int kcount = kcount_of(split);
+        for (int it = 0; it < kcount; ++it) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* st = smem + stage * L::kStageBytes;
           uint8_t *a_hi = st, *a_lo = st + L::kABytes, *b_hi = st + 2 * L::kABytes, *b_lo = b_hi + L::kBBytes;
@@ -229,7 +233,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
           armed[stage] = true; armed_phase[stage] = phase;
           int a_col, a_row, b_col, b_row;
           if (p.mode == kModeConv) {
-            int t = it / p.chunks_per_tap, ch = it - t * p.chunks_per_tap;
+            int git = split * p.k_iters + it;
+            int t = git / p.chunks_per_tap, ch = git - t * p.chunks_per_tap;
             a_col = ch * BK; a_row = m0 + p.tap_off[t];
             b_col = t * p.b_tap_pitch + ch * BK; b_row = n0;
           } else if (p.mode == kModeWgrad) {
@@ -289,12 +294,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
       int group = 0;            // accumulator groups issued so far (alternating TMEM buffers)
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        for (int it0 = 0; it0 < p.k_iters && ok; it0 += p.group_iters, ++group) {
+        const int kcount = kcount_of(tile % p.splits);
+        for (int it0 = 0; it0 < kcount && ok; it0 += p.group_iters, ++group) {
           const int acc = group & 1;
           if (!mbar_wait(&acc_empty[acc], ((group >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + acc * 2 * BN;
-          const int it1 = min(it0 + p.group_iters, p.k_iters);
+          const int it1 = min(it0 + p.group_iters, kcount);
           for (int it = it0; it < it1; ++it) {
             if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
@@ -315,31 +321,110 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
       }
     }
   } else {
-    // ===================== epilogue: warps 2..5, TMEM lane quarter = warp % 4 =====================
+    // ===================== epilogue: warps 2..9 =====================
+    // A warp may only read the TMEM lane quarter (warp % 4); two warps share each quarter and take one half of
+    // the tile's columns each, so that every scheduler has two epilogue warps to alternate between (the
+    // epilogue is a chain of dependent address/convert/store instructions and is issue-latency bound).
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int HC = BN / 2;                  // columns per epilogue warp
     const int row_in_tile = quarter * 32 + lane;
     int group = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       int mt, nt, tap, split;
       decode(tile, mt, nt, tap, split);
+      const int kcount = kcount_of(split);
+      const long long m = (long long)mt * BM + row_in_tile;
+      const int n0 = nt * BN + half * HC;
+      // per-row output address (everything but the column term)
+      bool row_ok = m < p.M;
+      long long base = 0;
+      uint32_t col_stride = 1;
+      if (p.epi == kEpiRowMajor) {
+        base = m * p.ldc;
+      } else if (p.epi == kEpiNchw) {
+        int per_img = p.frame_h * p.frame_w;
+        int img = (int)(m / per_img);
+        int rem = (int)(m - (long long)img * per_img), i = rem / p.frame_w, j = rem - i * p.frame_w;
+        row_ok = row_ok && i < p.valid_h && j < p.valid_w;
+        col_stride = (uint32_t)(p.out_h * p.out_w);
+        base = ((long long)img * p.out_c) * col_stride + (long long)(i * p.out_sh) * p.out_w + j * p.out_sw;
+      } else {   // kEpiWgrad: out[(m * N_total + n) * ntaps + tap]
+        base = (m * p.N) * p.ntaps + tap;
+        col_stride = (uint32_t)p.ntaps;
+      }
+      float* const row_out = p.out + base + (long long)n0 * col_stride;
+      const int ncols = max(0, min(HC, p.N - n0));
+      const bool vec_ok = p.epi == kEpiRowMajor && !p.atomic && ((base + n0) & 3) == 0;
+
+      auto wait_group = [&](int acc_buf, int grp) -> bool {   // lane 0 polls, the warp follows (keeps .sync.aligned loads converged)
+        int got = lane == 0 ? (int)mbar_wait(&acc_full[acc_buf], (grp >> 1) & 1, abort_flag) : 1;
+        return __shfl_sync(0xffffffffu, got, 0) != 0;
+      };
+      // NC values of this thread's row, columns c0.. of the warp's half; the offsets are independent of one
+      // another (no serial pointer chain) and fit 32 bits (BN * plane size is far below 2^32 elements).
+      auto store_cols = [&](const float* v, int c0, auto nc_tag) {
+        constexpr int NC = decltype(nc_tag)::value;
+        if (!row_ok || c0 >= ncols) return;
+        if (vec_ok && c0 + NC <= ncols) {
+          float4* dst = reinterpret_cast<float4*>(row_out + c0);
+#pragma unroll
+          for (int q = 0; q < NC / 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else if (c0 + NC <= ncols && !p.atomic) {
+          float* dst = row_out + (size_t)((uint32_t)c0 * col_stride);
+#pragma unroll
+          for (int q = 0; q < NC; ++q) dst[(size_t)((uint32_t)q * col_stride)] = v[q];
+        } else {
+          float* dst = row_out + (size_t)((uint32_t)c0 * col_stride);
+#pragma unroll
+          for (int q = 0; q < NC; ++q) {
+            if (c0 + q < ncols) {
+              float* d = dst + (size_t)((uint32_t)q * col_stride);
+              if (p.atomic) atomicAdd(d, v[q]); else *d = v[q];
+            }
+          }
+        }
+      };
+
+      if (kcount <= p.group_iters) {
+        // One accumulator group: stream TMEM straight to memory, 32 columns at a time.
+        const int acc = group & 1;
+        if (!wait_group(acc, group)) { ok = false; break; }
+        ++group;
+        tcgen05_fence_after();
+        const uint32_t t_base = tmem_base + acc * 2 * BN + half * HC + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+        for (int c0 = 0; c0 < HC; c0 += 32) {
+          float v1[32], v2[32];
+          tmem_ld32(t_base + c0, v1);
+          tmem_ld32(t_base + BN + c0, v2);
+          tmem_ld_wait();
+          if (c0 + 32 >= HC) {     // last chunk read: the accumulator can be reused while we store
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[acc]);
+          }
+#pragma unroll
+          for (int q = 0; q < 32; ++q) v1[q] += v2[q];
+          store_cols(v1, c0, std::integral_constant<int, 32>{});
+        }
+        continue;
+      }
+
       // The tensor core accumulates with truncation, so a long chain of MMAs into one TMEM accumulator
       // drifts; each group of kGroupIters stages is therefore accumulated in TMEM on its own and promoted
       // here into fp32 registers with round-to-nearest adds.
-      float accv[BN];
+      float accv[HC];
 #pragma unroll
-      for (int q = 0; q < BN; ++q) accv[q] = 0.f;
-      for (int it0 = 0; it0 < p.k_iters && ok; it0 += p.group_iters, ++group) {
+      for (int q = 0; q < HC; ++q) accv[q] = 0.f;
+      for (int it0 = 0; it0 < kcount && ok; it0 += p.group_iters, ++group) {
         const int acc = group & 1;
-        {   // lane 0 polls, the warp follows: keeps the warp converged for the .sync.aligned TMEM loads
-          int got = lane == 0 ? (int)mbar_wait(&acc_full[acc], (group >> 1) & 1, abort_flag) : 1;
-          got = __shfl_sync(0xffffffffu, got, 0);
-          if (!got) { ok = false; break; }
-        }
+        if (!wait_group(acc, group)) { ok = false; break; }
         tcgen05_fence_after();
-        const uint32_t t_base = tmem_base + acc * 2 * BN + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t t_base = tmem_base + acc * 2 * BN + half * HC + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 16) {
+        for (int c0 = 0; c0 < HC; c0 += 16) {
           float v1[16], v2[16];
           tmem_ld16(t_base + c0, v1);              // A_hi*B_hi + A_lo*B_hi
           tmem_ld16(t_base + BN + c0, v2);         // A_hi*B_lo
@@ -352,40 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
       }
       if (!ok) break;
-      const long long m = (long long)mt * BM + row_in_tile;
-      const int n0 = nt * BN;
-      // per-row output address (everything but the column term)
-      bool row_ok = m < p.M;
-      long long base = 0, col_stride = 1;
-      if (p.epi == kEpiRowMajor) {
-        base = m * p.ldc;
-      } else if (p.epi == kEpiNchw) {
-        int per_img = p.frame_h * p.frame_w;
-        long long img = m / per_img;
-        int rem = (int)(m - img * per_img), i = rem / p.frame_w, j = rem - i * p.frame_w;
-        row_ok = row_ok && i < p.valid_h && j < p.valid_w;
-        col_stride = (long long)p.out_h * p.out_w;
-        base = (img * p.out_c) * col_stride + (long long)(i * p.out_sh) * p.out_w + j * p.out_sw;
-      } else {   // kEpiWgrad: out[(m * N_total + n) * ntaps + tap]
-        base = (m * p.N) * p.ntaps + tap;
-        col_stride = p.ntaps;
-      }
-      if (row_ok) {
-        if (p.epi == kEpiRowMajor && !p.atomic && n0 + BN <= p.N && ((base + n0) & 3) == 0) {
-          float4* dst = reinterpret_cast<float4*>(p.out + base + n0);
-#pragma unroll
-          for (int q = 0; q < BN / 4; ++q) dst[q] = make_float4(accv[4 * q], accv[4 * q + 1], accv[4 * q + 2], accv[4 * q + 3]);
-        } else {
-#pragma unroll
-          for (int q = 0; q < BN; ++q) {
-            int n = n0 + q;
-            if (n < p.N) {
-              float* dst = p.out + base + (long long)n * col_stride;
-              if (p.atomic) atomicAdd(dst, accv[q]); else *dst = accv[q];
-            }
-          }
-        }
-      }
+      store_cols(accv, 0, std::integral_constant<int, HC>{});
     }
   }
 
@@ -623,6 +675,7 @@ int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_
     int tiles = p.m_tiles * p.n_tiles, sms = device_sm_count();
     int splits = 1;
     if (tiles * 2 <= sms && kit >= 16) { splits = sms / tiles; if (splits > kit / 8) splits = kit / 8; if (splits < 1) splits = 1; }
+    p.k_total = kit;
     p.k_iters = (kit + splits - 1) / splits;
     p.splits = (kit + p.k_iters - 1) / p.k_iters;
     p.atomic = p.splits > 1;
@@ -687,7 +740,7 @@ static int pack_filter(Pack& pk, const float* w, const ConvPlan* p, int flip, cu
 
 // forward and backward-data share one launcher: out[pixel][ch_out] = sum_{tap, ch_in} act[pixel + shift(tap)][ch_in] * filt[ch_out][tap][ch_in]
 static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, const ConvPlan* p, const ConvTc* st, float* out,
-                     int valid_h, int valid_w, int out_h, int out_w, int out_sh, int out_sw, cudaStream_t s, const char* what) {
+                     int valid_h, int valid_w, int out_h, int out_w, int out_sh, int out_sw, bool out_is_zero, cudaStream_t s, const char* what) {
   GemmParams g;
   memset(&g, 0, sizeof(g));
   const int bn = pick_bn(ch_out);
@@ -702,11 +755,26 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, c
   g.ntaps = p->R * p->S;
   g.chunks_per_tap = (ch_in + BK - 1) / BK;
   g.b_tap_pitch = (int)round_up(ch_in, 32);
-  g.k_iters = g.ntaps * g.chunks_per_tap;
+  g.k_total = g.ntaps * g.chunks_per_tap;
+  g.k_iters = g.k_total;
+  {   // Split the reduction when the tile count quantises badly onto the SMs and the reduction is long enough.
+    int tiles = g.m_tiles * g.n_tiles, sms = device_sm_count();
+    auto eff = [&](int sp) { long long w = (long long)tiles * sp; return (double)w / (double)(((w + sms - 1) / sms) * sms); };
+    int best = 1;
+    if (g.k_total >= 32 && eff(1) < 0.85) {
+      for (int sp = 2; sp <= 8 && g.k_total / sp >= 12; ++sp) if (eff(sp) > eff(best) + 0.03) best = sp;
+    }
+    if (best > 1) {
+      g.k_iters = (g.k_total + best - 1) / best;
+      g.splits = (g.k_total + g.k_iters - 1) / g.k_iters;
+      g.atomic = g.splits > 1;
+    }
+  }
   for (int r = 0; r < p->R; ++r) for (int q = 0; q < p->S; ++q) g.tap_off[r * p->S + q] = r * st->frame_w + q;
   g.out = out; g.err = error_word();
   g.frame_h = st->frame_h; g.frame_w = st->frame_w; g.valid_h = valid_h; g.valid_w = valid_w;
   g.out_c = ch_out; g.out_h = out_h; g.out_w = out_w; g.out_sh = out_sh; g.out_sw = out_sw;
+  if (g.atomic && !out_is_zero) TF_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)p->N * ch_out * out_h * out_w, s));
   double flops = 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S;
   return launch_gemm_bn(bn, g, s, flops, what);
 }
@@ -717,7 +785,7 @@ int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStrea
   std::lock_guard<std::mutex> lk(st->mu);
   if (pack_activation(st->x, x, p->N, p->C, p->H, p->W, st, p->stride_h, p->stride_w, st->cls == 1 ? p->P : p->H, st->cls == 1 ? p->Q : p->W, 1, s, oom)) return *oom ? 1 : -1;
   if (pack_filter(st->wf, w, p, 0, s, oom)) return *oom ? 1 : -1;
-  int rc = conv_like(st->x, st->wf, p->C, p->K, p, st, y, p->P, p->Q, p->P, p->Q, 1, 1, s, "DLGpuConvolution2DForward");
+  int rc = conv_like(st->x, st->wf, p->C, p->K, p, st, y, p->P, p->Q, p->P, p->Q, 1, 1, false, s, "DLGpuConvolution2DForward");
   return rc ? -1 : 1;
 }
 
@@ -732,9 +800,9 @@ int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaS
   if (st->cls == 1) {
     bool strided = p->stride_h > 1 || p->stride_w > 1;
     if (strided && cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)p->N * p->C * p->H * p->W, s) != cudaSuccess) return -1;
-    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, p->P, p->Q, p->H, p->W, p->stride_h, p->stride_w, s, "DLGpuConvolutionBackwardData");
+    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, p->P, p->Q, p->H, p->W, p->stride_h, p->stride_w, strided, s, "DLGpuConvolutionBackwardData");
   } else {
-    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, p->H, p->W, p->H, p->W, 1, 1, s, "DLGpuConvolutionBackwardData");
+    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, p->H, p->W, p->H, p->W, 1, 1, false, s, "DLGpuConvolutionBackwardData");
   }
   return rc ? -1 : 1;
 }
@@ -765,6 +833,7 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
   int splits = (2 * sms + tiles - 1) / tiles;
   if (splits > kit / 4) splits = kit / 4;
   if (splits < 1) splits = 1;
+  g.k_total = kit;
   g.k_iters = (kit + splits - 1) / splits;
   g.splits = (kit + g.k_iters - 1) / g.k_iters;
   g.out = dw; g.err = error_word();

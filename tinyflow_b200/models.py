@@ -184,7 +184,108 @@ def resnet50(batch=64, classes=1000, image=224, dropout=0.5):
     return Model("resnet50", X, y_, loss, y, params, (batch, 3, image, image), (batch, classes), [drop6])
 
 
-BUILDERS = {"mlp": mlp, "lenet5": lenet5, "vgg16": vgg16, "resnet50": resnet50}
+def inceptionv3(batch=32, classes=1000, image=299, dropout=0.8):
+    """Inception-v3 without batch norm, wired like Inceptionv3_test_leo.py:558-1020 (conv+ReLU units, chained
+    two-input channel concats, the 8x8 grid-reduction module reading the second 17x17 module's output)."""
+    X, y_ = ad.Placeholder("X"), ad.Placeholder("y_")
+    params = {}
+
+    def unit(x, name, shape, padding="SAME", stride=1):
+        w = ad.Variable(name)
+        params[w] = shape
+        return _conv_relu(x, w, padding, stride, stride)
+
+    def cat(*xs):
+        out = xs[0]
+        for x in xs[1:]:
+            out = ad.concat_forward_op(out, x)
+        return out
+
+    def avg3(x):
+        return ad.pooling_2d_forward_op(x, "NCHW", "mean", 1, 1, 1, 1, 3, 3)
+
+    # stem: 299 -> 35x35x192
+    h = unit(X, "filterb_1", (32, 3, 3, 3), "VALID", 2)
+    h = unit(h, "filterb_2", (32, 32, 3, 3), "VALID")
+    h = unit(h, "filterb_3", (64, 32, 3, 3))
+    h = ad.pooling_2d_forward_op(h, "NCHW", "max", 0, 0, 2, 2, 3, 3)
+    h = unit(h, "filterb_4", (80, 64, 1, 1), "VALID")
+    h = unit(h, "filterb_5", (192, 80, 3, 3), "VALID")
+    h = ad.pooling_2d_forward_op(h, "NCHW", "max", 0, 0, 2, 2, 3, 3)
+
+    # three 35x35 modules (1x1 | 1x1-5x5 | 1x1-3x3-3x3 | avgpool-1x1)
+    cin = 192
+    for i, proj in enumerate((32, 64, 64), start=1):
+        f = "filter1_%d_" % i
+        b0 = unit(h, f + "0", (64, cin, 1, 1))
+        b1 = unit(unit(h, f + "1a", (48, cin, 1, 1)), f + "1b", (64, 48, 5, 5))
+        b2 = unit(unit(unit(h, f + "2a", (64, cin, 1, 1)), f + "2b", (96, 64, 3, 3)), f + "2c", (96, 96, 3, 3))
+        b3 = unit(avg3(h), f + ("3" if i == 3 else "3a"), (proj, cin, 1, 1))
+        h = cat(b0, b1, b2, b3)
+        cin = 64 + 64 + 96 + proj
+
+    # grid reduction 35 -> 17
+    b0 = unit(h, "filter2_1_0", (384, cin, 3, 3), "VALID", 2)
+    b1 = unit(unit(unit(h, "filter2_1_1a", (64, cin, 1, 1)), "filter2_1_1b", (96, 64, 3, 3)), "filter2_1_1c", (96, 96, 3, 3), "VALID", 2)
+    b2 = ad.pooling_2d_forward_op(h, "NCHW", "mean", 0, 0, 2, 2, 3, 3)
+    h = cat(b0, b1, b2)
+    cin = 384 + 96 + cin     # 768
+
+    # four 17x17 modules with factorised 7x7 convolutions
+    outs17 = []
+    for i, mid in zip(range(2, 6), (128, 160, 160, 160)):
+        f = "filter2_%d_" % i
+        b0 = unit(h, f + "0", (192, cin, 1, 1))
+        b1 = unit(h, f + "1a", (mid, cin, 1, 1))
+        b1 = unit(b1, f + "1b", (mid, mid, 1, 7))
+        b1 = unit(b1, f + "1c", (192, mid, 7, 1))
+        b2 = unit(h, f + "2a", (mid, cin, 1, 1))
+        b2 = unit(b2, f + "2b", (mid, mid, 7, 1))
+        b2 = unit(b2, f + "2c", (mid, mid, 1, 7))
+        b2 = unit(b2, f + "2d", (mid, mid, 7, 1))
+        b2 = unit(b2, f + "2e", (192, mid, 1, 7))
+        b3 = unit(avg3(h), f + "3a", (192, cin, 1, 1))
+        h = cat(b0, b1, b2, b3)
+        outs17.append(h)
+
+    # grid reduction 17 -> 8; its second branch and its pooling branch read the output of the FIRST 17x17 module
+    # (Inceptionv3_test_leo.py:893-898), which is kept here so that the node sequence matches.
+    early = outs17[0]
+    b0 = unit(unit(h, "filter3_1_0a", (192, cin, 1, 1)), "filter3_1_0b", (320, 192, 3, 3), "VALID", 2)
+    b1 = unit(early, "filter3_1_1a", (192, cin, 1, 1))
+    b1 = unit(b1, "filter3_1_1b", (192, 192, 1, 7))
+    b1 = unit(b1, "filter3_1_1c", (192, 192, 7, 1))
+    b1 = unit(b1, "filter3_1_1d", (192, 192, 3, 3), "VALID", 2)
+    b2 = ad.pooling_2d_forward_op(early, "NCHW", "mean", 0, 0, 2, 2, 3, 3)
+    h = cat(b0, b1, b2)
+    cin = 320 + 192 + cin    # 1280
+
+    # two 8x8 modules with split 1x3 / 3x1 branches
+    for i in (2, 3):
+        f = "filter3_%d_" % i
+        b0 = unit(h, f + "0", (320, cin, 1, 1))
+        b1a = unit(h, f + "1a", (384, cin, 1, 1))
+        b1 = ad.concat_forward_op(unit(b1a, f + "1b", (384, 384, 1, 3)), unit(b1a, f + "1c", (384, 384, 3, 1)))
+        b2b = unit(unit(h, f + "2a", (448, cin, 1, 1)), f + "2b", (384, 448, 3, 3))
+        b2 = ad.concat_forward_op(unit(b2b, f + "2c", (384, 384, 1, 3)), unit(b2b, f + "2d", (384, 384, 3, 1)))
+        b3 = unit(avg3(h), f + "3a", (192, cin, 1, 1))
+        h = cat(b0, b1, b2, b3)
+        cin = 320 + 768 + 768 + 192    # 2048
+
+    final = (((image - 3) // 2 + 1 - 2 - 3) // 2 + 1 - 2 - 3) // 2 + 1     # 35 for 299
+    final = ((final - 3) // 2 + 1 - 3) // 2 + 1                              # 8
+    h = ad.pooling_2d_forward_op(h, "NCHW", "mean", 0, 0, 1, 1, final, final)
+    drop = ad.dropout_forward_op(h, "NCHW", dropout)
+    h = unit(drop, "filtera1", (classes, cin, 1, 1))
+    W, b = ad.Variable("filtersmul"), ad.Variable("biases")
+    dense = ad.dense(ad.squeeze_op(h), W, b)
+    y = ad.fullyactivation_forward_op(dense, "NCHW", "softmax")
+    loss = ad.crossEntropy_loss(y, y_)
+    params[W], params[b] = (classes, classes), (classes,)
+    return Model("inceptionv3", X, y_, loss, y, params, (batch, 3, image, image), (batch, classes), [drop])
+
+
+BUILDERS = {"mlp": mlp, "lenet5": lenet5, "vgg16": vgg16, "resnet50": resnet50, "inceptionv3": inceptionv3}
 
 
 def synthetic_batch(model: Model, seed=1234, rank=0, input_dist="normal"):
