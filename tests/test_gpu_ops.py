@@ -263,6 +263,15 @@ CONV = [
     (4, 512, 7, 7, 2048, 1, 1, "VALID", 1, 1),
     (3, 96, 14, 14, 160, 3, 3, "SAME", 1, 1),
     (2, 40, 9, 9, 72, 1, 1, "SAME", 1, 1),
+    # stride-1 windows without padding (frame wider than the input on both sides of dy)
+    (2, 32, 37, 37, 32, 3, 3, "VALID", 1, 1),
+    (2, 80, 21, 21, 192, 3, 3, "VALID", 1, 1),
+    # few input channels: several taps share one tile of the filter-gradient GEMM
+    (2, 16, 28, 28, 64, 3, 3, "SAME", 1, 1),
+    (2, 48, 35, 35, 64, 5, 5, "SAME", 1, 1),
+    # three input channels: patch-matrix path
+    (4, 3, 64, 64, 64, 7, 7, "VALID", 2, 2),
+    (16, 3, 75, 75, 32, 3, 3, "VALID", 2, 2),
 ]
 
 

@@ -93,6 +93,10 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
@@ -161,8 +165,9 @@ struct alignas(64) GemmParams {
   // element (image, channel c, i, j) lives at ((image*out_c + c)*out_h + i*out_sh)*out_w + j*out_sw
   int frame_h, frame_w, valid_h, valid_w, out_c, out_h, out_w, out_sh, out_sw;
   int* err;                       // device-visible error word (mapped host memory)
+  int slot, taps_per_tile;        // kModeWgrad: M-tile rows are taps_per_tile slots of `slot` input channels, one filter tap per slot
   int group_iters;                // stages accumulated in TMEM before the epilogue promotes them to registers
-  int tap_off[kMaxTaps];          // row shift per tap (A rows for kModeConv, B rows for kModeWgrad)
+  int tap_off[kMaxTaps];          // row shift per tap (applied to the activation operand A)
 };
 
 template <int BN> struct SmemLayout {
@@ -239,29 +244,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
             b_col = t * p.b_tap_pitch + ch * BK; b_row = n0;
           } else if (p.mode == kModeWgrad) {
             int krow = (split * p.k_iters + it) * BK;
-            a_col = m0; a_row = krow;
-            b_col = n0; b_row = krow + p.tap_off[tap];
+            a_col = mt * p.slot; a_row = krow;      // per-box tap shift applied below
+            b_col = n0; b_row = krow;
           } else {
             int kk = (split * p.k_iters + it) * BK;
             if (p.a_mn) { a_col = m0; a_row = kk; } else { a_col = kk; a_row = m0; }
             if (p.b_mn) { b_col = n0; b_row = kk; } else { b_col = kk; b_row = n0; }
           }
-          if (p.a_mn) {
-#pragma unroll
-            for (int i = 0; i < BM / 32; ++i) {
-              tma_load_2d(a_hi + i * 4096, &p.a_hi, a_col + 32 * i, a_row, &full[stage]);
-              tma_load_2d(a_lo + i * 4096, &p.a_lo, a_col + 32 * i, a_row, &full[stage]);
+          // M/N-major operands come through a 3-D view {32 columns, rows, column groups}: one copy lands
+          // [groups][32 rows][128 B], the layout the 32-byte-atom swizzle descriptor expects.
+          if (p.mode == kModeWgrad) {
+            // One copy per tap slot; a slot past the last tap reads rows beyond the pack (the copy still completes
+            // with its full byte count and fills zeros).
+            const int gps = p.slot >> 5;
+            for (int sl = 0; sl < p.taps_per_tile; ++sl) {
+              int t = tap * p.taps_per_tile + sl;
+              int row = t < p.ntaps ? a_row + p.tap_off[t] : 0x40000000;
+              tma_load_3d(a_hi + sl * gps * 4096, &p.a_hi, 0, row, a_col >> 5, &full[stage]);
+              tma_load_3d(a_lo + sl * gps * 4096, &p.a_lo, 0, row, a_col >> 5, &full[stage]);
             }
+          } else if (p.a_mn) {
+            tma_load_3d(a_hi, &p.a_hi, 0, a_row, a_col >> 5, &full[stage]);
+            tma_load_3d(a_lo, &p.a_lo, 0, a_row, a_col >> 5, &full[stage]);
           } else {
             tma_load_2d(a_hi, &p.a_hi, a_col, a_row, &full[stage]);
             tma_load_2d(a_lo, &p.a_lo, a_col, a_row, &full[stage]);
           }
           if (p.b_mn) {
-#pragma unroll
-            for (int i = 0; i < BN / 32; ++i) {
-              tma_load_2d(b_hi + i * 4096, &p.b_hi, b_col + 32 * i, b_row, &full[stage]);
-              tma_load_2d(b_lo + i * 4096, &p.b_lo, b_col + 32 * i, b_row, &full[stage]);
-            }
+            tma_load_3d(b_hi, &p.b_hi, 0, b_row, b_col >> 5, &full[stage]);
+            tma_load_3d(b_lo, &p.b_lo, 0, b_row, b_col >> 5, &full[stage]);
           } else {
             tma_load_2d(b_hi, &p.b_hi, b_col, b_row, &full[stage]);
             tma_load_2d(b_lo, &p.b_lo, b_col, b_row, &full[stage]);
@@ -350,9 +361,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
         row_ok = row_ok && i < p.valid_h && j < p.valid_w;
         col_stride = (uint32_t)(p.out_h * p.out_w);
         base = ((long long)img * p.out_c) * col_stride + (long long)(i * p.out_sh) * p.out_w + j * p.out_sw;
-      } else {   // kEpiWgrad: out[(m * N_total + n) * ntaps + tap]
-        base = (m * p.N) * p.ntaps + tap;
-        col_stride = (uint32_t)p.ntaps;
+      } else {   // kEpiWgrad: tile row -> (tap slot, input channel c), column n = output channel: out[(n * C + c) * ntaps + tap]
+        int sl = row_in_tile / p.slot, c = mt * p.slot + row_in_tile - sl * p.slot, t = tap * p.taps_per_tile + sl;
+        row_ok = t < p.ntaps && c < p.M;
+        base = (long long)c * p.ntaps + t;
+        col_stride = (uint32_t)(p.M * p.ntaps);
       }
       float* const row_out = p.out + base + (long long)n0 * col_stride;
       const int ncols = max(0, min(HC, p.N - n0));
@@ -515,6 +528,29 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
   }
 }
 
+// NCHW activations -> explicit patch matrix [N*P*Q][pitch], column (c*R + r)*S + s = the filter's own flat index
+// within one output channel, so the convolution becomes a 1x1 one over C*R*S "channels".  Used where the
+// channel count is too small to fill a 32-wide reduction chunk per tap (first layers, C = 3).
+struct PatchGeom { int N, C, H, W, R, S, P, Q, sh, sw, pad_h, pad_w, cols, pitch; };
+__global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, PatchGeom g) {
+  const long long rows = (long long)g.N * g.P * g.Q, total = rows * g.pitch, stride = (long long)gridDim.x * blockDim.x;
+  const int rs = g.R * g.S;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const long long row = idx / g.pitch;
+    const int col = (int)(idx - row * g.pitch);
+    float a = 0.f;
+    if (col < g.cols) {
+      const int c = col / rs, t = col - c * rs, r = t / g.S, q2 = t - r * g.S;
+      const int n = (int)(row / (g.P * g.Q)), rem = (int)(row - (long long)n * g.P * g.Q), pp = rem / g.Q, qq = rem - pp * g.Q;
+      const int i = pp * g.sh - g.pad_h + r, j = qq * g.sw - g.pad_w + q2;
+      if (i >= 0 && i < g.H && j >= 0 && j < g.W) a = src[(((long long)n * g.C + c) * g.H + i) * g.W + j];
+    }
+    float h, l;
+    split_tf32(a, h, l);
+    hi[idx] = h; lo[idx] = l;
+  }
+}
+
 // filters [K][C][R][S] -> forward pack [K][tap][cpad] (flip = 0) or backward-data pack [C][tap'][kpad] (flip = 1,
 // tap' = (R-1-r)*S + (S-1-s)), zero in the channel padding.
 __global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
@@ -555,7 +591,7 @@ static EncodeTiledFn encode_fn() {
 
 // 2-D fp32 row-major [rows][cols] with `pitch` floats per row; box = 32 cols x box_rows rows; 128-byte swizzle with
 // 16-byte atoms for K-major operands, with 32-byte atoms for the M/N-major ones (the only form tf32 takes there).
-static int make_map(CUtensorMap* m, const float* base, long long rows, long long cols, long long pitch, int box_rows, bool mn_major = false) {
+static int make_map(CUtensorMap* m, const float* base, long long rows, long long cols, long long pitch, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   TF_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -563,8 +599,24 @@ static int make_map(CUtensorMap* m, const float* base, long long rows, long long
   cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld pitch %lld)", (int)r, rows, cols, pitch);
+  return 0;
+}
+// M/N-major operand: 3-D view {32 columns, rows, pitch / 32 column groups} with a box of `groups` groups x 32 rows.
+// The pack's pitch is a multiple of 32, so every group lies inside the allocation; columns past the logical
+// width hold whatever the pack left there and only reach output rows / columns that the epilogue masks.
+static int make_map_mn(CUtensorMap* m, const float* base, long long rows, long long pitch, int groups) {
+  EncodeTiledFn fn = encode_fn();
+  TF_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from this driver");
+  TF_REQUIRE(pitch % 32 == 0, "M/N-major operand pitch %lld is not a multiple of 32", pitch);
+  cuuint64_t dims[3] = {32, (cuuint64_t)rows, (cuuint64_t)(pitch / 32)};
+  cuuint64_t strides[2] = {(cuuint64_t)pitch * 4, 128};
+  cuuint32_t box[3] = {32, 32, (cuuint32_t)groups};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (3-D) failed with %d (rows %lld pitch %lld groups %d)", (int)r, rows, pitch, groups);
   return 0;
 }
 
@@ -625,7 +677,7 @@ struct Pack {           // a packed operand living in pooled device memory
   size_t bytes() const { return (size_t)rows * pitch * 4; }
 };
 static int pack_alloc(Pack& pk, long long rows, long long cols, int* oom) {
-  long long pitch = round_up(cols, 4);
+  long long pitch = round_up(cols, 32);
   if (pk.hi && pk.rows == rows && pk.pitch == pitch) { pk.cols = cols; return 0; }
   if (pk.hi) { pool_free(pk.hi); pool_free(pk.lo); pk.hi = pk.lo = nullptr; }
   pk.rows = rows; pk.cols = cols; pk.pitch = pitch; pk.src = nullptr;
@@ -664,10 +716,10 @@ int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_
   memset(&p, 0, sizeof(p));
   const int bn = pick_bn(N);
   p.mode = kModeGemm; p.a_mn = tA ? 1 : 0; p.b_mn = tB ? 0 : 1; p.epi = kEpiRowMajor;
-  if (!rc) rc = make_map(&p.a_hi, pa.hi, pa.rows, pa.cols, pa.pitch, p.a_mn ? 32 : BM, p.a_mn);
-  if (!rc) rc = make_map(&p.a_lo, pa.lo, pa.rows, pa.cols, pa.pitch, p.a_mn ? 32 : BM, p.a_mn);
-  if (!rc) rc = make_map(&p.b_hi, pb.hi, pb.rows, pb.cols, pb.pitch, p.b_mn ? 32 : bn, p.b_mn);
-  if (!rc) rc = make_map(&p.b_lo, pb.lo, pb.rows, pb.cols, pb.pitch, p.b_mn ? 32 : bn, p.b_mn);
+  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_hi, pa.hi, pa.rows, pa.pitch, BM / 32) : make_map(&p.a_hi, pa.hi, pa.rows, pa.cols, pa.pitch, BM);
+  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_lo, pa.lo, pa.rows, pa.pitch, BM / 32) : make_map(&p.a_lo, pa.lo, pa.rows, pa.cols, pa.pitch, BM);
+  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_hi, pb.hi, pb.rows, pb.pitch, bn / 32) : make_map(&p.b_hi, pb.hi, pb.rows, pb.cols, pb.pitch, bn);
+  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_lo, pb.lo, pb.rows, pb.pitch, bn / 32) : make_map(&p.b_lo, pb.lo, pb.rows, pb.cols, pb.pitch, bn);
   if (!rc) {
     p.M = (int)M; p.N = (int)N;
     p.m_tiles = (int)((M + BM - 1) / BM); p.n_tiles = (int)((N + bn - 1) / bn); p.tap_tiles = 1;
@@ -689,22 +741,34 @@ int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_
 
 // ---- convolution -------------------------------------------------------------------------------------
 // Shapes the tensor path takes (everything else returns 0 and runs on the CUDA cores):
-//   class A: 1x1 window, no padding, any stride;
-//   class B: stride 1 with symmetric "same" padding (2*pad = window - 1 on both axes), any window.
+//   class A: 1x1 window, no padding, any stride (frame = the P x Q output grid, x sampled with the stride);
+//   class B: stride 1, padding <= window - 1 on each axis, any window: frame = (H + R - 1) x (W + S - 1); x sits at
+//            offset (pad_h, pad_w), dy at (R - 1 - pad_h, S - 1 - pad_w), which gives each the zero halo its role
+//            needs (forward padding for x, "full" correlation for dy);
+//   class C: too few input channels for a per-tap reduction chunk: x is expanded into patches (C*R*S columns) and
+//            the problem runs as class A over C*R*S channels; forward and filter gradient only.
 struct ConvTc {
-  int cls = 0;                 // 0 unsupported, 1 class A, 2 class B
-  int frame_h = 0, frame_w = 0, off_h = 0, off_w = 0;   // frame geometry shared by the x and dy packs
+  int cls = 0;                 // 0 unsupported, 1 class A, 2 class B, 3 class C
+  int frame_h = 0, frame_w = 0;                          // frame geometry shared by the x and dy packs
+  int x_off_h = 0, x_off_w = 0, dy_off_h = 0, dy_off_w = 0;
+  int eC = 0, eR = 1, eS = 1;                            // reduction channels and window of the problem as the GEMM sees it
   Pack x, dy, wf, wd;
   std::mutex mu;
 };
 static ConvTc* conv_state(ConvPlan* p) {
   if (!p->tc_state) {
     ConvTc* st = new ConvTc;
-    bool ok = p->dataformat == 0 && p->C >= 16 && p->K >= 16 && p->C % 4 == 0 && p->K % 4 == 0 && p->R * p->S <= kMaxTaps;
+    st->eC = p->C; st->eR = p->R; st->eS = p->S;
+    bool base = p->dataformat == 0 && p->K >= 16 && p->K % 4 == 0 && p->R * p->S <= kMaxTaps;
+    bool ok = base && p->C >= 16 && p->C % 4 == 0;
     if (ok && p->R == 1 && p->S == 1 && p->pad_h == 0 && p->pad_w == 0) {
       st->cls = 1; st->frame_h = p->P; st->frame_w = p->Q;
-    } else if (ok && p->stride_h == 1 && p->stride_w == 1 && 2 * p->pad_h == p->R - 1 && 2 * p->pad_w == p->S - 1) {
-      st->cls = 2; st->frame_h = p->H + 2 * p->pad_h; st->frame_w = p->W + 2 * p->pad_w; st->off_h = p->pad_h; st->off_w = p->pad_w;
+    } else if (ok && p->stride_h == 1 && p->stride_w == 1 && p->pad_h <= p->R - 1 && p->pad_w <= p->S - 1) {
+      st->cls = 2; st->frame_h = p->H + p->R - 1; st->frame_w = p->W + p->S - 1;
+      st->x_off_h = p->pad_h; st->x_off_w = p->pad_w; st->dy_off_h = p->R - 1 - p->pad_h; st->dy_off_w = p->S - 1 - p->pad_w;
+    } else if (base && p->C < 16 && p->C * p->R * p->S <= 1024) {
+      st->cls = 3; st->frame_h = p->P; st->frame_w = p->Q;
+      st->eC = p->C * p->R * p->S; st->eR = st->eS = 1;
     }
     // small problems are launch-bound: leave them to the CUDA-core kernel
     double flops = 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S;
@@ -714,14 +778,15 @@ static ConvTc* conv_state(ConvPlan* p) {
   return (ConvTc*)p->tc_state;
 }
 
-// packs an NCHW tensor with `chans` channels into the plan's frame; spatial source dims (H, W), sampling stride (sh, sw)
-static int pack_activation(Pack& pk, const float* src, int N, int chans, int H, int W, const ConvTc* st, int sh, int sw, int cnt_h, int cnt_w,
-                           int tag, cudaStream_t s, int* oom) {
+// packs an NCHW tensor with `chans` channels into the plan's frame at offset (off_h, off_w); spatial source dims (H, W),
+// sampling stride (sh, sw)
+static int pack_activation(Pack& pk, const float* src, int N, int chans, int H, int W, const ConvTc* st, int off_h, int off_w, int sh, int sw,
+                           int cnt_h, int cnt_w, int tag, cudaStream_t s, int* oom) {
   uint64_t ver = version_of(src);
   long long rows = (long long)N * st->frame_h * st->frame_w;
   if (pk.hi && pk.src == src && pk.version == ver && pk.tag == tag && pk.rows == rows && pk.cols == chans) return 0;   // still valid
   if (pack_alloc(pk, rows, chans, oom)) return 1;
-  PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, st->off_h, st->off_w, sh, sw, cnt_h, cnt_w, (int)pk.pitch};
+  PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, off_h, off_w, sh, sw, cnt_h, cnt_w, (int)pk.pitch};
   dim3 grid((st->frame_w + 31) / 32, st->frame_h, N * ((chans + 31) / 32));
   KernelTimer kt("pack_nchw", s, 0, 12.0 * rows * chans);
   pack_nchw_kernel<<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
@@ -729,13 +794,51 @@ static int pack_activation(Pack& pk, const float* src, int N, int chans, int H, 
   pk.src = src; pk.version = ver; pk.tag = tag;
   return 0;
 }
-static int pack_filter(Pack& pk, const float* w, const ConvPlan* p, int flip, cudaStream_t s, int* oom) {
-  int taps = p->R * p->S, rows = flip ? p->C : p->K, inner = flip ? p->K : p->C, inner_pad = (int)round_up(inner, 32);
+// the x operand of a plan: frame pack (classes A, B) or patch matrix (class C)
+static int pack_x(ConvTc* st, const ConvPlan* p, const float* x, cudaStream_t s, int* oom) {
+  if (st->cls != 3)
+    return pack_activation(st->x, x, p->N, p->C, p->H, p->W, st, st->x_off_h, st->x_off_w, p->stride_h, p->stride_w,
+                           st->cls == 1 ? p->P : p->H, st->cls == 1 ? p->Q : p->W, 1, s, oom);
+  Pack& pk = st->x;
+  uint64_t ver = version_of(x);
+  long long rows = (long long)p->N * p->P * p->Q;
+  if (pk.hi && pk.src == x && pk.version == ver && pk.tag == 3 && pk.rows == rows && pk.cols == st->eC) return 0;
+  if (pack_alloc(pk, rows, st->eC, oom)) return 1;
+  PatchGeom g{p->N, p->C, p->H, p->W, p->R, p->S, p->P, p->Q, p->stride_h, p->stride_w, p->pad_h, p->pad_w, st->eC, (int)pk.pitch};
+  KernelTimer kt("pack_patches", s, 0, 8.0 * rows * pk.pitch);
+  pack_patches_kernel<<<grid_for(rows * pk.pitch, 256, 8), 256, 0, s>>>(x, pk.hi, pk.lo, g);
+  TF_AFTER(s, "pack_patches");
+  pk.src = x; pk.version = ver; pk.tag = 3;
+  return 0;
+}
+static int pack_dy(ConvTc* st, const ConvPlan* p, const float* dy, cudaStream_t s, int* oom) {
+  return pack_activation(st->dy, dy, p->N, p->K, p->P, p->Q, st, st->dy_off_h, st->dy_off_w, 1, 1, p->P, p->Q, 2, s, oom);
+}
+static int pack_filter(Pack& pk, const float* w, const ConvPlan* p, const ConvTc* st, int flip, cudaStream_t s, int* oom) {
+  int taps = st->eR * st->eS, rows = flip ? st->eC : p->K, inner = flip ? p->K : st->eC, inner_pad = (int)round_up(inner, 32);
   if (pack_alloc(pk, rows, (long long)taps * inner_pad, oom)) return 1;
   long long total = (long long)rows * taps * inner_pad;
-  pack_filter_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, pk.hi, pk.lo, p->K, p->C, p->R, p->S, flip, inner_pad);
+  pack_filter_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, pk.hi, pk.lo, p->K, st->eC, st->eR, st->eS, flip, inner_pad);
   TF_AFTER(s, "pack_filter");
   return 0;
+}
+
+// Picks how many ways to split a reduction of k_total stages over `tiles` output tiles: minimises
+// waves * (stages per tile + fixed per-tile cost), everything in units of one stage; a split costs extra
+// (pre-zeroed output and atomic adds) so ties go to fewer splits.
+static int choose_splits(int tiles, int k_total, int min_iters, int max_splits, bool free_split) {
+  const int sms = device_sm_count();
+  double best_cost = 1e30; int best = 1;
+  for (int sp = 1; sp <= max_splits; ++sp) {
+    int it = (k_total + sp - 1) / sp;
+    if (sp > 1 && it < min_iters) break;
+    int real = (k_total + it - 1) / it;
+    long long total = (long long)tiles * real;
+    long long waves = (total + sms - 1) / sms;
+    double cost = (double)waves * (it + 8.0 + ((real > 1 && !free_split) ? 4.0 : 0.0));
+    if (cost < best_cost * 0.97) { best_cost = cost; best = real; }
+  }
+  return best;
 }
 
 // forward and backward-data share one launcher: out[pixel][ch_out] = sum_{tap, ch_in} act[pixel + shift(tap)][ch_in] * filt[ch_out][tap][ch_in]
@@ -752,25 +855,20 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, c
   if (rc) return -1;
   g.M = (int)act.rows; g.N = ch_out;
   g.m_tiles = (int)((act.rows + BM - 1) / BM); g.n_tiles = (ch_out + bn - 1) / bn; g.tap_tiles = 1; g.splits = 1;
-  g.ntaps = p->R * p->S;
+  g.ntaps = st->eR * st->eS;
   g.chunks_per_tap = (ch_in + BK - 1) / BK;
   g.b_tap_pitch = (int)round_up(ch_in, 32);
   g.k_total = g.ntaps * g.chunks_per_tap;
   g.k_iters = g.k_total;
   {   // Split the reduction when the tile count quantises badly onto the SMs and the reduction is long enough.
-    int tiles = g.m_tiles * g.n_tiles, sms = device_sm_count();
-    auto eff = [&](int sp) { long long w = (long long)tiles * sp; return (double)w / (double)(((w + sms - 1) / sms) * sms); };
-    int best = 1;
-    if (g.k_total >= 32 && eff(1) < 0.85) {
-      for (int sp = 2; sp <= 8 && g.k_total / sp >= 12; ++sp) if (eff(sp) > eff(best) + 0.03) best = sp;
-    }
+    int best = g.k_total >= 24 ? choose_splits(g.m_tiles * g.n_tiles, g.k_total, 8, 16, false) : 1;
     if (best > 1) {
       g.k_iters = (g.k_total + best - 1) / best;
       g.splits = (g.k_total + g.k_iters - 1) / g.k_iters;
       g.atomic = g.splits > 1;
     }
   }
-  for (int r = 0; r < p->R; ++r) for (int q = 0; q < p->S; ++q) g.tap_off[r * p->S + q] = r * st->frame_w + q;
+  for (int r = 0; r < st->eR; ++r) for (int q = 0; q < st->eS; ++q) g.tap_off[r * st->eS + q] = r * st->frame_w + q;
   g.out = out; g.err = error_word();
   g.frame_h = st->frame_h; g.frame_w = st->frame_w; g.valid_h = valid_h; g.valid_w = valid_w;
   g.out_c = ch_out; g.out_h = out_h; g.out_w = out_w; g.out_sh = out_sh; g.out_sw = out_sw;
@@ -783,19 +881,18 @@ int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStrea
   ConvTc* st = conv_state(p);
   if (!st->cls || !encode_fn()) return 0;
   std::lock_guard<std::mutex> lk(st->mu);
-  if (pack_activation(st->x, x, p->N, p->C, p->H, p->W, st, p->stride_h, p->stride_w, st->cls == 1 ? p->P : p->H, st->cls == 1 ? p->Q : p->W, 1, s, oom)) return *oom ? 1 : -1;
-  if (pack_filter(st->wf, w, p, 0, s, oom)) return *oom ? 1 : -1;
-  int rc = conv_like(st->x, st->wf, p->C, p->K, p, st, y, p->P, p->Q, p->P, p->Q, 1, 1, false, s, "DLGpuConvolution2DForward");
+  if (pack_x(st, p, x, s, oom)) return *oom ? 1 : -1;
+  if (pack_filter(st->wf, w, p, st, 0, s, oom)) return *oom ? 1 : -1;
+  int rc = conv_like(st->x, st->wf, st->eC, p->K, p, st, y, p->P, p->Q, p->P, p->Q, 1, 1, false, s, "DLGpuConvolution2DForward");
   return rc ? -1 : 1;
 }
 
 int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaStream_t s, int* oom) {
   ConvTc* st = conv_state(p);
-  if (!st->cls || !encode_fn()) return 0;
+  if (!st->cls || st->cls == 3 || !encode_fn()) return 0;
   std::lock_guard<std::mutex> lk(st->mu);
-  // dy sits in the same frame as x (class B: at the padding offset; class A: dense P x Q)
-  if (pack_activation(st->dy, dy, p->N, p->K, p->P, p->Q, st, 1, 1, p->P, p->Q, 2, s, oom)) return *oom ? 1 : -1;
-  if (pack_filter(st->wd, w, p, 1, s, oom)) return *oom ? 1 : -1;
+  if (pack_dy(st, p, dy, s, oom)) return *oom ? 1 : -1;
+  if (pack_filter(st->wd, w, p, st, 1, s, oom)) return *oom ? 1 : -1;
   int rc = 0;
   if (st->cls == 1) {
     bool strided = p->stride_h > 1 || p->stride_w > 1;
@@ -811,28 +908,32 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
   ConvTc* st = conv_state(p);
   if (!st->cls || !encode_fn()) return 0;
   std::lock_guard<std::mutex> lk(st->mu);
-  if (pack_activation(st->x, x, p->N, p->C, p->H, p->W, st, p->stride_h, p->stride_w, st->cls == 1 ? p->P : p->H, st->cls == 1 ? p->Q : p->W, 1, s, oom)) return *oom ? 1 : -1;
-  if (pack_activation(st->dy, dy, p->N, p->K, p->P, p->Q, st, 1, 1, p->P, p->Q, 2, s, oom)) return *oom ? 1 : -1;
+  if (pack_x(st, p, x, s, oom)) return *oom ? 1 : -1;
+  if (pack_dy(st, p, dy, s, oom)) return *oom ? 1 : -1;
   GemmParams g;
   memset(&g, 0, sizeof(g));
-  const int bn = pick_bn(p->C);
+  // A = x (M = tap slots x input channels), B = dy (N = output channels); both M/N-major, reduction over pixel rows.
+  const int bn = pick_bn(p->K);
   g.mode = kModeWgrad; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiWgrad; g.atomic = 1;
-  int rc = make_map(&g.a_hi, st->dy.hi, st->dy.rows, st->dy.cols, st->dy.pitch, 32, true);
-  if (!rc) rc = make_map(&g.a_lo, st->dy.lo, st->dy.rows, st->dy.cols, st->dy.pitch, 32, true);
-  if (!rc) rc = make_map(&g.b_hi, st->x.hi, st->x.rows, st->x.cols, st->x.pitch, 32, true);
-  if (!rc) rc = make_map(&g.b_lo, st->x.lo, st->x.rows, st->x.cols, st->x.pitch, 32, true);
+  g.M = st->eC; g.N = p->K; g.ntaps = st->eR * st->eS;
+  // Few input channels: several filter taps share one 128-row tile (slots of 32, 64 or 128 channels), so that the
+  // tensor core's M dimension is full and dy is read once for all of them.
+  g.slot = st->eC >= 128 ? BM : (int)round_up(st->eC, 32) == 96 ? BM : (int)round_up(st->eC, 32);
+  g.taps_per_tile = BM / g.slot;
+  int rc = make_map_mn(&g.a_hi, st->x.hi, st->x.rows, st->x.pitch, g.slot / 32);
+  if (!rc) rc = make_map_mn(&g.a_lo, st->x.lo, st->x.rows, st->x.pitch, g.slot / 32);
+  if (!rc) rc = make_map_mn(&g.b_hi, st->dy.hi, st->dy.rows, st->dy.pitch, bn / 32);
+  if (!rc) rc = make_map_mn(&g.b_lo, st->dy.lo, st->dy.rows, st->dy.pitch, bn / 32);
   if (rc) return -1;
-  g.M = p->K; g.N = p->C;
-  g.m_tiles = (p->K + BM - 1) / BM; g.n_tiles = (p->C + bn - 1) / bn; g.tap_tiles = p->R * p->S; g.ntaps = p->R * p->S;
-  // dy row m' holds output pixel (p, q) at frame position (p + off_h, q + off_w); tap (r, s) needs the input at
-  // padded position (p + r, q + s), i.e. row m' + (r - off_h) * frame_w + (s - off_w)
-  for (int r = 0; r < p->R; ++r) for (int q = 0; q < p->S; ++q) g.tap_off[r * p->S + q] = (r - st->off_h) * st->frame_w + (q - st->off_w);
+  g.m_tiles = (st->eC + g.slot - 1) / g.slot;
+  g.tap_tiles = (g.ntaps + g.taps_per_tile - 1) / g.taps_per_tile;
+  g.n_tiles = (p->K + bn - 1) / bn;
+  // dy row m' holds output pixel (p, q) at frame position (p + dy_off_h, q + dy_off_w); tap (r, s) needs the padded
+  // input at (p + r, q + s), which sits at frame row m' + (r - dy_off_h) * frame_w + (s - dy_off_w)
+  for (int r = 0; r < st->eR; ++r) for (int q = 0; q < st->eS; ++q) g.tap_off[r * st->eS + q] = (r - st->dy_off_h) * st->frame_w + (q - st->dy_off_w);
   long long rows = st->dy.rows;
   int kit = (int)((rows + BK - 1) / BK);
-  int tiles = g.m_tiles * g.n_tiles * g.tap_tiles, sms = device_sm_count();
-  int splits = (2 * sms + tiles - 1) / tiles;
-  if (splits > kit / 4) splits = kit / 4;
-  if (splits < 1) splits = 1;
+  int splits = choose_splits(g.m_tiles * g.n_tiles * g.tap_tiles, kit, 4, 1024, true);
   g.k_total = kit;
   g.k_iters = (kit + splits - 1) / splits;
   g.splits = (kit + g.k_iters - 1) / g.k_iters;
