@@ -491,38 +491,49 @@ __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restric
 
 // NCHW activations -> pixel-major frame [N][frame_h][frame_w][pitch]:
 //   dst(n, i, j, c) = src(n, c, (i - off_h) * sh, (j - off_w) * sw) when that sample exists, else 0.
-// 32 (frame columns) x 32 (channels) tiles transposed through shared memory: reads run along w,
-// writes along c.
+// One block moves 32 frame columns x TC channels of one frame row through shared memory: reads run along w
+// (TC/8 independent loads per thread in flight), writes along c as 16-byte vectors of hi and of lo.
 struct PackGeom { int N, C, H, W, frame_h, frame_w, off_h, off_w, sh, sw, cnt_h, cnt_w, pitch; };
+template <int TC>
 __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, PackGeom g) {
-  __shared__ float tile[32][33];
+  __shared__ float tile[TC][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
   const int j0 = blockIdx.x * 32, i = blockIdx.y;
-  const int cblocks = (g.C + 31) / 32;
-  const int n = blockIdx.z / cblocks, c0 = (blockIdx.z % cblocks) * 32;
+  const int cblocks = (g.C + TC - 1) / TC;
+  const int n = blockIdx.z / cblocks, c0 = (blockIdx.z % cblocks) * TC;
   const int si = i - g.off_h;
   const bool row_ok = si >= 0 && si < g.cnt_h;
   {
-    int j = j0 + tx, sj = j - g.off_w;
-    bool ok = row_ok && sj >= 0 && sj < g.cnt_w && j < g.frame_w;
+    const int j = j0 + tx, sj = j - g.off_w;
+    const bool ok = row_ok && sj >= 0 && sj < g.cnt_w && j < g.frame_w;
     const float* s = src + ((long long)n * g.C * g.H + (long long)(si * g.sh)) * g.W + (long long)sj * g.sw;
+    const long long plane = (long long)g.H * g.W;
+    float v[TC / 8];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      int c = c0 + ty + 8 * k;
-      tile[ty + 8 * k][tx] = (ok && c < g.C) ? s[(long long)c * g.H * g.W] : 0.f;
+    for (int k = 0; k < TC / 8; ++k) {
+      const int c = c0 + ty + 8 * k;
+      v[k] = (ok && c < g.C) ? __ldg(s + c * plane) : 0.f;
     }
+#pragma unroll
+    for (int k = 0; k < TC / 8; ++k) tile[ty + 8 * k][tx] = v[k];
   }
   __syncthreads();
   {
-    int c = c0 + tx;
+    // a warp writes whole pixels: lane -> 4 consecutive channels, TC/4 lanes per pixel, 128/TC pixels per pass
+    constexpr int LPP = TC / 4, PPW = 32 / LPP;       // lanes per pixel, pixels per warp pass
+    const int cl = (tx % LPP) * 4, c = c0 + cl;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      int j = j0 + ty + 8 * k;
-      if (j < g.frame_w && c < g.C) {
-        float h, l;
-        split_tf32(tile[tx][ty + 8 * k], h, l);
-        long long o = (((long long)n * g.frame_h + i) * g.frame_w + j) * g.pitch + c;
-        hi[o] = h; lo[o] = l;
+    for (int k = 0; k < 32 / (8 * PPW); ++k) {
+      const int jj = (k * 8 + ty) * PPW + tx / LPP, j = j0 + jj;
+      if (j < g.frame_w && c < g.pitch) {
+        float4 h, l;
+        split_tf32(tile[cl][jj], h.x, l.x);
+        split_tf32(tile[cl + 1][jj], h.y, l.y);
+        split_tf32(tile[cl + 2][jj], h.z, l.z);
+        split_tf32(tile[cl + 3][jj], h.w, l.w);
+        const long long o = (((long long)n * g.frame_h + i) * g.frame_w + j) * g.pitch + c;
+        *reinterpret_cast<float4*>(hi + o) = h;
+        *reinterpret_cast<float4*>(lo + o) = l;
       }
     }
   }
@@ -533,21 +544,35 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
 // channel count is too small to fill a 32-wide reduction chunk per tap (first layers, C = 3).
 struct PatchGeom { int N, C, H, W, R, S, P, Q, sh, sw, pad_h, pad_w, cols, pitch; };
 __global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, PatchGeom g) {
-  const long long rows = (long long)g.N * g.P * g.Q, total = rows * g.pitch, stride = (long long)gridDim.x * blockDim.x;
+  // column -> (source offset relative to the window origin, r, s), the same for every row
+  __shared__ int col_off[1024];
+  __shared__ short col_r[1024], col_s[1024];
   const int rs = g.R * g.S;
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
-    const long long row = idx / g.pitch;
-    const int col = (int)(idx - row * g.pitch);
-    float a = 0.f;
-    if (col < g.cols) {
-      const int c = col / rs, t = col - c * rs, r = t / g.S, q2 = t - r * g.S;
-      const int n = (int)(row / (g.P * g.Q)), rem = (int)(row - (long long)n * g.P * g.Q), pp = rem / g.Q, qq = rem - pp * g.Q;
-      const int i = pp * g.sh - g.pad_h + r, j = qq * g.sw - g.pad_w + q2;
-      if (i >= 0 && i < g.H && j >= 0 && j < g.W) a = src[(((long long)n * g.C + c) * g.H + i) * g.W + j];
+  for (int col = threadIdx.x; col < g.cols; col += blockDim.x) {
+    const int c = col / rs, t = col - c * rs, r = t / g.S, q = t - r * g.S;
+    col_off[col] = (c * g.H + r) * g.W + q;
+    col_r[col] = (short)r; col_s[col] = (short)q;
+  }
+  __syncthreads();
+  const long long rows = (long long)g.N * g.P * g.Q;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  const int pq = g.P * g.Q;
+  for (long long row = (long long)blockIdx.x * wpb + warp; row < rows; row += (long long)gridDim.x * wpb) {   // one warp per patch row
+    const int n = (int)(row / pq), rem = (int)(row - (long long)n * pq), pp = rem / g.Q, qq = rem - pp * g.Q;
+    const int i0 = pp * g.sh - g.pad_h, j0 = qq * g.sw - g.pad_w;
+    const float* base = src + ((long long)n * g.C * g.H + i0) * g.W + j0;
+    float* h_row = hi + row * g.pitch;
+    float* l_row = lo + row * g.pitch;
+    for (int col = lane; col < g.pitch; col += 32) {
+      float a = 0.f;
+      if (col < g.cols) {
+        const int i = i0 + col_r[col], j = j0 + col_s[col];
+        if (i >= 0 && i < g.H && j >= 0 && j < g.W) a = __ldg(base + col_off[col]);
+      }
+      float h, l;
+      split_tf32(a, h, l);
+      h_row[col] = h; l_row[col] = l;
     }
-    float h, l;
-    split_tf32(a, h, l);
-    hi[idx] = h; lo[idx] = l;
   }
 }
 
@@ -787,9 +812,12 @@ static int pack_activation(Pack& pk, const float* src, int N, int chans, int H, 
   if (pk.hi && pk.src == src && pk.version == ver && pk.tag == tag && pk.rows == rows && pk.cols == chans) return 0;   // still valid
   if (pack_alloc(pk, rows, chans, oom)) return 1;
   PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, off_h, off_w, sh, sw, cnt_h, cnt_w, (int)pk.pitch};
-  dim3 grid((st->frame_w + 31) / 32, st->frame_h, N * ((chans + 31) / 32));
+  const int tc = chans > 64 ? 128 : chans > 32 ? 64 : 32;
+  dim3 grid((st->frame_w + 31) / 32, st->frame_h, N * ((chans + tc - 1) / tc));
   KernelTimer kt("pack_nchw", s, 0, 12.0 * rows * chans);
-  pack_nchw_kernel<<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
+  if (tc == 128) pack_nchw_kernel<128><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
+  else if (tc == 64) pack_nchw_kernel<64><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
+  else pack_nchw_kernel<32><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
   TF_AFTER(s, "pack_nchw");
   pk.src = src; pk.version = ver; pk.tag = tag;
   return 0;
@@ -806,7 +834,7 @@ static int pack_x(ConvTc* st, const ConvPlan* p, const float* x, cudaStream_t s,
   if (pack_alloc(pk, rows, st->eC, oom)) return 1;
   PatchGeom g{p->N, p->C, p->H, p->W, p->R, p->S, p->P, p->Q, p->stride_h, p->stride_w, p->pad_h, p->pad_w, st->eC, (int)pk.pitch};
   KernelTimer kt("pack_patches", s, 0, 8.0 * rows * pk.pitch);
-  pack_patches_kernel<<<grid_for(rows * pk.pitch, 256, 8), 256, 0, s>>>(x, pk.hi, pk.lo, g);
+  pack_patches_kernel<<<grid_for(rows * 32, 256, 4), 256, 0, s>>>(x, pk.hi, pk.lo, g);
   TF_AFTER(s, "pack_patches");
   pk.src = x; pk.version = ver; pk.tag = 3;
   return 0;
