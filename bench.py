@@ -2,7 +2,7 @@
 """Benchmark: train images/s for one forward + backward + SGD step of ResNet-50 (batch 64 per GPU,
 3x224x224 synthetic inputs, 1000 classes) through the mirrored executor and the C-ABI library.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload resnet50|vgg16|lenet5|mlp]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload resnet50|vgg16|inceptionv3|lenet5|mlp]
 
 With N > 1 launch under torchrun (one rank per GPU); rank 0 prints one JSON line.
 `--impl reference` times the CPU arm instead: the same graph evaluated by the numpy restatement of
@@ -26,6 +26,7 @@ sys.path.insert(0, REPO)
 WORKLOADS = {
     "resnet50": dict(batch=64, image=224, classes=1000, lr=0.01, dist="normal"),
     "vgg16": dict(batch=64, image=224, classes=1000, lr=0.01, dist="normal"),
+    "inceptionv3": dict(batch=32, image=299, classes=1000, lr=0.01, dist="normal"),
     "lenet5": dict(batch=256, lr=0.05, dist="uniform"),
     "mlp": dict(batch=1000, lr=0.1, dist="uniform"),
 }
@@ -36,7 +37,7 @@ def build_model(name, batch=None):
     cfg = dict(WORKLOADS[name])
     if batch is not None:
         cfg["batch"] = batch
-    if name in ("resnet50", "vgg16"):
+    if name in ("resnet50", "vgg16", "inceptionv3"):
         return models.BUILDERS[name](batch=cfg["batch"], classes=cfg["classes"], image=cfg["image"]), cfg
     return models.BUILDERS[name](batch=cfg["batch"]), cfg
 
@@ -149,7 +150,7 @@ def run_reference_arm(args):
     import numpy as np  # noqa: F401  (loads the BLAS whose thread count is reported)
     workload = args.workload
     cfg = WORKLOADS[workload]
-    sample = {"resnet50": 4, "vgg16": 2}.get(workload, cfg["batch"])
+    sample = {"resnet50": 4, "vgg16": 2, "inceptionv3": 2}.get(workload, cfg["batch"])
     blas_threads, cores = cpu_threads()
     for _ in range(args.warmup if workload in ("mlp", "lenet5") else min(args.warmup, 1)):
         cpu_step_time(workload, sample)
@@ -217,7 +218,7 @@ def main():
         check_call(_LIB.TfDpInit(rank, world, id_path.encode()))
 
     model, cfg = build_model(args.workload, batch=args.batch)
-    model.set_dropout(0.5 if args.workload in ("resnet50", "vgg16") else 0.0)
+    model.set_dropout({"resnet50": 0.5, "vgg16": 0.5, "inceptionv3": 0.8}.get(args.workload, 0.0))
     ex = ad.Executor(model.loss, model.y, cfg["lr"], None, None, None, optimizer="sgd")
     ctx = ndarray.gpu(0)
     Xn, Yn = models.synthetic_batch(model, seed=1234, rank=rank, input_dist=cfg["dist"])
@@ -350,7 +351,7 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        sample = {"resnet50": 4, "vgg16": 2}.get(args.workload, batch)
+        sample = {"resnet50": 4, "vgg16": 2, "inceptionv3": 2}.get(args.workload, batch)
         t = cpu_step_time(args.workload, sample)
         threads, cores = cpu_threads()
         cpu_baseline = {"value": sample / t, "unit": "images/s", "cores": threads, "kind": "port",
@@ -363,7 +364,7 @@ def main():
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "%s b%d/GPU %s fp32 fwd+bwd+SGD" % (args.workload, batch, "x".join(str(d) for d in model.input_shape[1:])),
                        "global_batch": world * batch, "parallelism": "dp%d" % world, "l2": "per-step working set (GBs of activations) exceeds the 126 MB L2",
-                       "dropout": 0.5 if model.dropout_nodes else 0.0, "device_ms_per_step": dev_ms / args.steps, "host_ms_per_step": wall_ms / args.steps,
+                       "dropout": (model.dropout_nodes[0].dropout if model.dropout_nodes else 0.0), "device_ms_per_step": dev_ms / args.steps, "host_ms_per_step": wall_ms / args.steps,
                        "algorithmic_tflop_per_step": flops / 1e12, "final_loss": final_loss},
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(Xn.nbytes + Yn.nbytes), "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),

@@ -225,6 +225,18 @@ def test_resnet50_reduced_end_to_end(lib_path):
     assert gpu_err.max() <= 5 * f32_err.max() + 1e-4
 
 
+def test_inceptionv3_reduced_node_by_node(lib_path):
+    """Inception-v3 graph (all 94 convolutions, 38 channel concats, padded average pools, 4-D dropout) at batch 2 on
+    75x75 images (the smallest size every stride-2 stage still accepts: 7x7, 3x3 and 1x1 grids)."""
+    from tinyflow_b200 import models
+    model = models.inceptionv3(batch=2, image=75, classes=1000)
+    feed_np = _feed(model)
+    ex, loss, nxt = run_step(model, feed_np, 0.01, dropout=0.8)
+    worst = check_node_by_node(ex, feed_np)
+    print("worst node", worst)
+    assert np.isfinite(loss.asnumpy()).all()
+
+
 def test_two_steps_reuse_pool_and_stay_finite(lib_path):
     from tinyflow_b200 import models, ndarray
     from tinyflow_b200._base import _LIB
