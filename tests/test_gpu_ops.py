@@ -269,6 +269,13 @@ CONV = [
     # few input channels: several taps share one tile of the filter-gradient GEMM
     (2, 16, 28, 28, 64, 3, 3, "SAME", 1, 1),
     (2, 48, 35, 35, 64, 5, 5, "SAME", 1, 1),
+    # strided windows: one frame per stride phase
+    (2, 32, 35, 35, 64, 3, 3, "VALID", 2, 2),
+    (2, 96, 17, 17, 96, 3, 3, "VALID", 2, 2),
+    (2, 64, 16, 16, 32, 3, 3, "SAME", 2, 2),
+    (2, 288, 15, 15, 128, 3, 3, "VALID", 2, 2),
+    (2, 32, 23, 23, 32, 5, 5, "SAME", 3, 3),
+    (2, 64, 20, 18, 64, 1, 3, "SAME", 2, 2),
     # three input channels: patch-matrix path
     (4, 3, 64, 64, 64, 7, 7, "VALID", 2, 2),
     (16, 3, 75, 75, 32, 3, 3, "VALID", 2, 2),

@@ -161,13 +161,16 @@ struct alignas(64) GemmParams {
   int atomic;                     // epilogue adds into `out` (pre-zeroed) instead of storing
   float* out;
   long long ldc;                  // kEpiRowMajor
-  // kEpiNchw: row m -> (image, i, j) in a frame of frame_h x frame_w; valid if i < valid_h and j < valid_w;
-  // element (image, channel c, i, j) lives at ((image*out_c + c)*out_h + i*out_sh)*out_w + j*out_sw
-  int frame_h, frame_w, valid_h, valid_w, out_c, out_h, out_w, out_sh, out_sw;
+  // kEpiNchw: row m -> (image, i, j) in a frame of frame_h x frame_w, stored at output pixel
+  // (oi, oj) = (i*out_sh + out_off_h, j*out_sw + out_off_w) of channel plane c: ((image*out_c + c)*out_h + oi)*out_w + oj;
+  // rows with i >= valid_h, j >= valid_w or (oi, oj) outside the plane are dropped
+  int frame_h, frame_w, valid_h, valid_w, out_c, out_h, out_w, out_sh, out_sw, out_off_h, out_off_w;
   int* err;                       // device-visible error word (mapped host memory)
   int slot, taps_per_tile;        // kModeWgrad: M-tile rows are taps_per_tile slots of `slot` input channels, one filter tap per slot
   int group_iters;                // stages accumulated in TMEM before the epilogue promotes them to registers
   int tap_off[kMaxTaps];          // row shift per tap (applied to the activation operand A)
+  short tap_col[kMaxTaps];        // first column of the tap's channels in A (space-to-depth packs keep one phase per column block)
+  short tap_b[kMaxTaps];          // kModeConv: which tap block of the packed filter the tap multiplies
 };
 
 template <int BN> struct SmemLayout {
@@ -240,8 +243,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
           if (p.mode == kModeConv) {
             int git = split * p.k_iters + it;
             int t = git / p.chunks_per_tap, ch = git - t * p.chunks_per_tap;
-            a_col = ch * BK; a_row = m0 + p.tap_off[t];
-            b_col = t * p.b_tap_pitch + ch * BK; b_row = n0;
+            a_col = p.tap_col[t] + ch * BK; a_row = m0 + p.tap_off[t];
+            b_col = p.tap_b[t] * p.b_tap_pitch + ch * BK; b_row = n0;
           } else if (p.mode == kModeWgrad) {
             int krow = (split * p.k_iters + it) * BK;
             a_col = mt * p.slot; a_row = krow;      // per-box tap shift applied below
@@ -260,8 +263,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
             for (int sl = 0; sl < p.taps_per_tile; ++sl) {
               int t = tap * p.taps_per_tile + sl;
               int row = t < p.ntaps ? a_row + p.tap_off[t] : 0x40000000;
-              tma_load_3d(a_hi + sl * gps * 4096, &p.a_hi, 0, row, a_col >> 5, &full[stage]);
-              tma_load_3d(a_lo + sl * gps * 4096, &p.a_lo, 0, row, a_col >> 5, &full[stage]);
+              int grp = (a_col + (t < p.ntaps ? p.tap_col[t] : 0)) >> 5;
+              tma_load_3d(a_hi + sl * gps * 4096, &p.a_hi, 0, row, grp, &full[stage]);
+              tma_load_3d(a_lo + sl * gps * 4096, &p.a_lo, 0, row, grp, &full[stage]);
             }
           } else if (p.a_mn) {
             tma_load_3d(a_hi, &p.a_hi, 0, a_row, a_col >> 5, &full[stage]);
@@ -358,9 +362,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
         int per_img = p.frame_h * p.frame_w;
         int img = (int)(m / per_img);
         int rem = (int)(m - (long long)img * per_img), i = rem / p.frame_w, j = rem - i * p.frame_w;
-        row_ok = row_ok && i < p.valid_h && j < p.valid_w;
+        int oi = i * p.out_sh + p.out_off_h, oj = j * p.out_sw + p.out_off_w;
+        row_ok = row_ok && i < p.valid_h && j < p.valid_w && oi >= 0 && oi < p.out_h && oj >= 0 && oj < p.out_w;
         col_stride = (uint32_t)(p.out_h * p.out_w);
-        base = ((long long)img * p.out_c) * col_stride + (long long)(i * p.out_sh) * p.out_w + j * p.out_sw;
+        base = ((long long)img * p.out_c) * col_stride + (long long)oi * p.out_w + oj;
       } else {   // kEpiWgrad: tile row -> (tap slot, input channel c), column n = output channel: out[(n * C + c) * ntaps + tap]
         int sl = row_in_tile / p.slot, c = mt * p.slot + row_in_tile - sl * p.slot, t = tap * p.taps_per_tile + sl;
         row_ok = t < p.ntaps && c < p.M;
@@ -490,10 +495,12 @@ __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restric
 }
 
 // NCHW activations -> pixel-major frame [N][frame_h][frame_w][pitch]:
-//   dst(n, i, j, c) = src(n, c, (i - off_h) * sh, (j - off_w) * sw) when that sample exists, else 0.
-// One block moves 32 frame columns x TC channels of one frame row through shared memory: reads run along w
-// (TC/8 independent loads per thread in flight), writes along c as 16-byte vectors of hi and of lo.
-struct PackGeom { int N, C, H, W, frame_h, frame_w, off_h, off_w, sh, sw, cnt_h, cnt_w, pitch; };
+//   dst(n, i, j, dst_c0 + c) = src(n, c, i * sh - off_h, j * sw - off_w) when that sample exists, else 0
+// (off > 0 places the source behind a zero halo; off <= 0 with sh > 1 selects one phase of a strided sampling).
+// Channels c < c_limit are written (zeros past C).  One block moves 32 frame columns x TC channels of one frame
+// row through shared memory: reads run along w (TC/8 independent loads per thread in flight), writes along c as
+// 16-byte vectors of hi and of lo.
+struct PackGeom { int N, C, H, W, frame_h, frame_w, off_h, off_w, sh, sw, pitch, dst_c0, c_limit; };
 template <int TC>
 __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, PackGeom g) {
   __shared__ float tile[TC][33];
@@ -501,12 +508,12 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
   const int j0 = blockIdx.x * 32, i = blockIdx.y;
   const int cblocks = (g.C + TC - 1) / TC;
   const int n = blockIdx.z / cblocks, c0 = (blockIdx.z % cblocks) * TC;
-  const int si = i - g.off_h;
-  const bool row_ok = si >= 0 && si < g.cnt_h;
+  const int si = i * g.sh - g.off_h;
+  const bool row_ok = si >= 0 && si < g.H;
   {
-    const int j = j0 + tx, sj = j - g.off_w;
-    const bool ok = row_ok && sj >= 0 && sj < g.cnt_w && j < g.frame_w;
-    const float* s = src + ((long long)n * g.C * g.H + (long long)(si * g.sh)) * g.W + (long long)sj * g.sw;
+    const int j = j0 + tx, sj = j * g.sw - g.off_w;
+    const bool ok = row_ok && sj >= 0 && sj < g.W && j < g.frame_w;
+    const float* s = src + ((long long)n * g.C * g.H + (long long)si) * g.W + (long long)sj;
     const long long plane = (long long)g.H * g.W;
     float v[TC / 8];
 #pragma unroll
@@ -525,13 +532,13 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
 #pragma unroll
     for (int k = 0; k < 32 / (8 * PPW); ++k) {
       const int jj = (k * 8 + ty) * PPW + tx / LPP, j = j0 + jj;
-      if (j < g.frame_w && c < g.pitch) {
+      if (j < g.frame_w && c < g.c_limit) {
         float4 h, l;
         split_tf32(tile[cl][jj], h.x, l.x);
         split_tf32(tile[cl + 1][jj], h.y, l.y);
         split_tf32(tile[cl + 2][jj], h.z, l.z);
         split_tf32(tile[cl + 3][jj], h.w, l.w);
-        const long long o = (((long long)n * g.frame_h + i) * g.frame_w + j) * g.pitch + c;
+        const long long o = (((long long)n * g.frame_h + i) * g.frame_w + j) * g.pitch + g.dst_c0 + c;
         *reinterpret_cast<float4*>(hi + o) = h;
         *reinterpret_cast<float4*>(lo + o) = l;
       }
@@ -770,10 +777,11 @@ int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_
 //   class B: stride 1, padding <= window - 1 on each axis, any window: frame = (H + R - 1) x (W + S - 1); x sits at
 //            offset (pad_h, pad_w), dy at (R - 1 - pad_h, S - 1 - pad_w), which gives each the zero halo its role
 //            needs (forward padding for x, "full" correlation for dy);
+//   class D: strided windows with C a multiple of 32: space-to-depth phases (see conv_state);
 //   class C: too few input channels for a per-tap reduction chunk: x is expanded into patches (C*R*S columns) and
 //            the problem runs as class A over C*R*S channels; forward and filter gradient only.
 struct ConvTc {
-  int cls = 0;                 // 0 unsupported, 1 class A, 2 class B, 3 class C
+  int cls = 0;                 // 0 unsupported, 1 class A, 2 class B, 3 class C, 4 class D
   int frame_h = 0, frame_w = 0;                          // frame geometry shared by the x and dy packs
   int x_off_h = 0, x_off_w = 0, dy_off_h = 0, dy_off_w = 0;
   int eC = 0, eR = 1, eS = 1;                            // reduction channels and window of the problem as the GEMM sees it
@@ -791,6 +799,14 @@ static ConvTc* conv_state(ConvPlan* p) {
     } else if (ok && p->stride_h == 1 && p->stride_w == 1 && p->pad_h <= p->R - 1 && p->pad_w <= p->S - 1) {
       st->cls = 2; st->frame_h = p->H + p->R - 1; st->frame_w = p->W + p->S - 1;
       st->x_off_h = p->pad_h; st->x_off_w = p->pad_w; st->dy_off_h = p->R - 1 - p->pad_h; st->dy_off_w = p->S - 1 - p->pad_w;
+    } else if (ok && p->C % 32 == 0 && p->stride_h * p->stride_w <= 16 && p->pad_h <= p->R - 1 && p->pad_w <= p->S - 1 &&
+               (long long)p->stride_h * p->stride_w * p->C < 32768) {
+      // strided window: x is split into stride_h*stride_w phases (space to depth), each tap reads one phase at a
+      // stride-1 shift; dy sits behind a halo of (R-1)/stride_h, (S-1)/stride_w for the backward-data pass
+      st->cls = 4;
+      st->dy_off_h = (p->R - 1) / p->stride_h; st->dy_off_w = (p->S - 1) / p->stride_w;
+      int uh = (p->H - 1 + p->pad_h) / p->stride_h + 1, uw = (p->W - 1 + p->pad_w) / p->stride_w + 1;
+      st->frame_h = (uh > p->P ? uh : p->P) + st->dy_off_h; st->frame_w = (uw > p->Q ? uw : p->Q) + st->dy_off_w;
     } else if (base && p->C < 16 && p->C * p->R * p->S <= 1024) {
       st->cls = 3; st->frame_h = p->P; st->frame_w = p->Q;
       st->eC = p->C * p->R * p->S; st->eR = st->eS = 1;
@@ -803,44 +819,65 @@ static ConvTc* conv_state(ConvPlan* p) {
   return (ConvTc*)p->tc_state;
 }
 
-// packs an NCHW tensor with `chans` channels into the plan's frame at offset (off_h, off_w); spatial source dims (H, W),
-// sampling stride (sh, sw)
-static int pack_activation(Pack& pk, const float* src, int N, int chans, int H, int W, const ConvTc* st, int off_h, int off_w, int sh, int sw,
-                           int cnt_h, int cnt_w, int tag, cudaStream_t s, int* oom) {
-  uint64_t ver = version_of(src);
-  long long rows = (long long)N * st->frame_h * st->frame_w;
-  if (pk.hi && pk.src == src && pk.version == ver && pk.tag == tag && pk.rows == rows && pk.cols == chans) return 0;   // still valid
-  if (pack_alloc(pk, rows, chans, oom)) return 1;
-  PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, off_h, off_w, sh, sw, cnt_h, cnt_w, (int)pk.pitch};
+// One launch of the frame pack: `chans` channels of an NCHW tensor (spatial dims H x W) into columns dst_c0.. of pk
+static int launch_pack_nchw(Pack& pk, const float* src, int N, int chans, int H, int W, const ConvTc* st, int off_h, int off_w, int sh, int sw,
+                            int dst_c0, bool last, cudaStream_t s) {
+  PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, off_h, off_w, sh, sw, (int)pk.pitch, dst_c0, last ? (int)pk.pitch - dst_c0 : chans};
   const int tc = chans > 64 ? 128 : chans > 32 ? 64 : 32;
   dim3 grid((st->frame_w + 31) / 32, st->frame_h, N * ((chans + tc - 1) / tc));
-  KernelTimer kt("pack_nchw", s, 0, 12.0 * rows * chans);
+  KernelTimer kt("pack_nchw", s, 0, 12.0 * pk.rows * chans);
   if (tc == 128) pack_nchw_kernel<128><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
   else if (tc == 64) pack_nchw_kernel<64><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
   else pack_nchw_kernel<32><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
   TF_AFTER(s, "pack_nchw");
-  pk.src = src; pk.version = ver; pk.tag = tag;
   return 0;
 }
-// the x operand of a plan: frame pack (classes A, B) or patch matrix (class C)
+static bool pack_valid(const Pack& pk, const void* src, uint64_t ver, int tag, long long rows, long long cols) {
+  return pk.hi && pk.src == src && pk.version == ver && pk.tag == tag && pk.rows == rows && pk.cols == cols;
+}
+// the x operand of a plan: frame pack (classes A, B), patch matrix (class C) or one frame per stride phase (class D)
 static int pack_x(ConvTc* st, const ConvPlan* p, const float* x, cudaStream_t s, int* oom) {
-  if (st->cls != 3)
-    return pack_activation(st->x, x, p->N, p->C, p->H, p->W, st, st->x_off_h, st->x_off_w, p->stride_h, p->stride_w,
-                           st->cls == 1 ? p->P : p->H, st->cls == 1 ? p->Q : p->W, 1, s, oom);
   Pack& pk = st->x;
-  uint64_t ver = version_of(x);
-  long long rows = (long long)p->N * p->P * p->Q;
-  if (pk.hi && pk.src == x && pk.version == ver && pk.tag == 3 && pk.rows == rows && pk.cols == st->eC) return 0;
-  if (pack_alloc(pk, rows, st->eC, oom)) return 1;
-  PatchGeom g{p->N, p->C, p->H, p->W, p->R, p->S, p->P, p->Q, p->stride_h, p->stride_w, p->pad_h, p->pad_w, st->eC, (int)pk.pitch};
-  KernelTimer kt("pack_patches", s, 0, 8.0 * rows * pk.pitch);
-  pack_patches_kernel<<<grid_for(rows * 32, 256, 4), 256, 0, s>>>(x, pk.hi, pk.lo, g);
-  TF_AFTER(s, "pack_patches");
-  pk.src = x; pk.version = ver; pk.tag = 3;
+  const uint64_t ver = version_of(x);
+  if (st->cls == 3) {
+    long long rows = (long long)p->N * p->P * p->Q;
+    if (pack_valid(pk, x, ver, 3, rows, st->eC)) return 0;
+    if (pack_alloc(pk, rows, st->eC, oom)) return 1;
+    PatchGeom g{p->N, p->C, p->H, p->W, p->R, p->S, p->P, p->Q, p->stride_h, p->stride_w, p->pad_h, p->pad_w, st->eC, (int)pk.pitch};
+    KernelTimer kt("pack_patches", s, 0, 8.0 * rows * pk.pitch);
+    pack_patches_kernel<<<grid_for(rows * 32, 256, 4), 256, 0, s>>>(x, pk.hi, pk.lo, g);
+    TF_AFTER(s, "pack_patches");
+    pk.src = x; pk.version = ver; pk.tag = 3;
+    return 0;
+  }
+  const long long rows = (long long)p->N * st->frame_h * st->frame_w;
+  const int phases = st->cls == 4 ? p->stride_h * p->stride_w : 1;
+  if (pack_valid(pk, x, ver, st->cls, rows, (long long)phases * p->C)) return 0;
+  if (pack_alloc(pk, rows, (long long)phases * p->C, oom)) return 1;
+  int rc = 0;
+  if (st->cls == 4) {
+    // phase (a, b) holds x_padded(sh*u + a, sw*v + b) = x(sh*u + a - pad_h, sw*v + b - pad_w) at frame position (u, v)
+    for (int a = 0; a < p->stride_h && !rc; ++a)
+      for (int b = 0; b < p->stride_w && !rc; ++b) {
+        int ph = a * p->stride_w + b;
+        rc = launch_pack_nchw(pk, x, p->N, p->C, p->H, p->W, st, p->pad_h - a, p->pad_w - b, p->stride_h, p->stride_w, ph * p->C, ph == phases - 1, s);
+      }
+  } else {
+    rc = launch_pack_nchw(pk, x, p->N, p->C, p->H, p->W, st, st->x_off_h, st->x_off_w, p->stride_h, p->stride_w, 0, true, s);
+  }
+  if (rc) return -1;
+  pk.src = x; pk.version = ver; pk.tag = st->cls;
   return 0;
 }
 static int pack_dy(ConvTc* st, const ConvPlan* p, const float* dy, cudaStream_t s, int* oom) {
-  return pack_activation(st->dy, dy, p->N, p->K, p->P, p->Q, st, st->dy_off_h, st->dy_off_w, 1, 1, p->P, p->Q, 2, s, oom);
+  Pack& pk = st->dy;
+  const uint64_t ver = version_of(dy);
+  const long long rows = (long long)p->N * st->frame_h * st->frame_w;
+  if (pack_valid(pk, dy, ver, 2, rows, p->K)) return 0;
+  if (pack_alloc(pk, rows, p->K, oom)) return 1;
+  if (launch_pack_nchw(pk, dy, p->N, p->K, p->P, p->Q, st, st->dy_off_h, st->dy_off_w, 1, 1, 0, true, s)) return -1;
+  pk.src = dy; pk.version = ver; pk.tag = 2;
+  return 0;
 }
 static int pack_filter(Pack& pk, const float* w, const ConvPlan* p, const ConvTc* st, int flip, cudaStream_t s, int* oom) {
   int taps = st->eR * st->eS, rows = flip ? st->eC : p->K, inner = flip ? p->K : st->eC, inner_pad = (int)round_up(inner, 32);
@@ -869,9 +906,11 @@ static int choose_splits(int tiles, int k_total, int min_iters, int max_splits, 
   return best;
 }
 
-// forward and backward-data share one launcher: out[pixel][ch_out] = sum_{tap, ch_in} act[pixel + shift(tap)][ch_in] * filt[ch_out][tap][ch_in]
-static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, const ConvPlan* p, const ConvTc* st, float* out,
-                     int valid_h, int valid_w, int out_h, int out_w, int out_sh, int out_sw, bool out_is_zero, cudaStream_t s, const char* what) {
+// forward and backward-data share one launcher: out[pixel][ch_out] = sum_{tap, ch_in} act[pixel + off(tap)][col(tap) + ch_in] * filt[ch_out][b(tap)][ch_in]
+struct TapList { int n = 0; int off[kMaxTaps]; int col[kMaxTaps]; int b[kMaxTaps]; void add(int o, int c, int bb) { off[n] = o; col[n] = c; b[n] = bb; ++n; } };
+struct OutGeom { int valid_h, valid_w, out_h, out_w, out_sh, out_sw, out_off_h, out_off_w; };
+static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, const ConvPlan* p, const ConvTc* st, float* out, const TapList& taps,
+                     const OutGeom& og, bool out_is_zero, double flops, cudaStream_t s, const char* what) {
   GemmParams g;
   memset(&g, 0, sizeof(g));
   const int bn = pick_bn(ch_out);
@@ -883,7 +922,7 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, c
   if (rc) return -1;
   g.M = (int)act.rows; g.N = ch_out;
   g.m_tiles = (int)((act.rows + BM - 1) / BM); g.n_tiles = (ch_out + bn - 1) / bn; g.tap_tiles = 1; g.splits = 1;
-  g.ntaps = st->eR * st->eS;
+  g.ntaps = taps.n;
   g.chunks_per_tap = (ch_in + BK - 1) / BK;
   g.b_tap_pitch = (int)round_up(ch_in, 32);
   g.k_total = g.ntaps * g.chunks_per_tap;
@@ -896,14 +935,14 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, c
       g.atomic = g.splits > 1;
     }
   }
-  for (int r = 0; r < st->eR; ++r) for (int q = 0; q < st->eS; ++q) g.tap_off[r * st->eS + q] = r * st->frame_w + q;
+  for (int t = 0; t < taps.n; ++t) { g.tap_off[t] = taps.off[t]; g.tap_col[t] = (short)taps.col[t]; g.tap_b[t] = (short)taps.b[t]; }
   g.out = out; g.err = error_word();
-  g.frame_h = st->frame_h; g.frame_w = st->frame_w; g.valid_h = valid_h; g.valid_w = valid_w;
-  g.out_c = ch_out; g.out_h = out_h; g.out_w = out_w; g.out_sh = out_sh; g.out_sw = out_sw;
-  if (g.atomic && !out_is_zero) TF_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)p->N * ch_out * out_h * out_w, s));
-  double flops = 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S;
+  g.frame_h = st->frame_h; g.frame_w = st->frame_w; g.valid_h = og.valid_h; g.valid_w = og.valid_w;
+  g.out_c = ch_out; g.out_h = og.out_h; g.out_w = og.out_w; g.out_sh = og.out_sh; g.out_sw = og.out_sw; g.out_off_h = og.out_off_h; g.out_off_w = og.out_off_w;
+  if (g.atomic && !out_is_zero) TF_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)p->N * ch_out * og.out_h * og.out_w, s));
   return launch_gemm_bn(bn, g, s, flops, what);
 }
+static double conv_flops(const ConvPlan* p) { return 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S; }
 
 int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStream_t s, int* oom) {
   ConvTc* st = conv_state(p);
@@ -911,7 +950,14 @@ int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStrea
   std::lock_guard<std::mutex> lk(st->mu);
   if (pack_x(st, p, x, s, oom)) return *oom ? 1 : -1;
   if (pack_filter(st->wf, w, p, st, 0, s, oom)) return *oom ? 1 : -1;
-  int rc = conv_like(st->x, st->wf, st->eC, p->K, p, st, y, p->P, p->Q, p->P, p->Q, 1, 1, false, s, "DLGpuConvolution2DForward");
+  TapList taps;
+  for (int r = 0; r < st->eR; ++r)
+    for (int q = 0; q < st->eS; ++q) {
+      if (st->cls == 4) taps.add((r / p->stride_h) * st->frame_w + q / p->stride_w, ((r % p->stride_h) * p->stride_w + q % p->stride_w) * p->C, r * st->eS + q);
+      else taps.add(r * st->frame_w + q, 0, r * st->eS + q);
+    }
+  OutGeom og{p->P, p->Q, p->P, p->Q, 1, 1, 0, 0};
+  int rc = conv_like(st->x, st->wf, st->eC, p->K, p, st, y, taps, og, false, conv_flops(p), s, "DLGpuConvolution2DForward");
   return rc ? -1 : 1;
 }
 
@@ -920,14 +966,34 @@ int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaS
   if (!st->cls || st->cls == 3 || !encode_fn()) return 0;
   std::lock_guard<std::mutex> lk(st->mu);
   if (pack_dy(st, p, dy, s, oom)) return *oom ? 1 : -1;
-  if (pack_filter(st->wd, w, p, st, 1, s, oom)) return *oom ? 1 : -1;
+  if (pack_filter(st->wd, w, p, st, 1, s, oom)) return *oom ? 1 : -1;     // [C][flipped tap][K]
+  const int ntap = p->R * p->S;
   int rc = 0;
   if (st->cls == 1) {
     bool strided = p->stride_h > 1 || p->stride_w > 1;
     if (strided && cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)p->N * p->C * p->H * p->W, s) != cudaSuccess) return -1;
-    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, p->P, p->Q, p->H, p->W, p->stride_h, p->stride_w, strided, s, "DLGpuConvolutionBackwardData");
+    TapList taps; taps.add(0, 0, 0);
+    OutGeom og{p->P, p->Q, p->H, p->W, p->stride_h, p->stride_w, 0, 0};
+    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, taps, og, strided, conv_flops(p), s, "DLGpuConvolutionBackwardData");
+  } else if (st->cls == 2) {
+    TapList taps;
+    for (int r = 0; r < p->R; ++r) for (int q = 0; q < p->S; ++q) taps.add(r * st->frame_w + q, 0, r * p->S + q);
+    OutGeom og{p->H, p->W, p->H, p->W, 1, 1, 0, 0};
+    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, taps, og, false, conv_flops(p), s, "DLGpuConvolutionBackwardData");
   } else {
-    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, p->H, p->W, p->H, p->W, 1, 1, false, s, "DLGpuConvolutionBackwardData");
+    // One launch per stride phase (a, b): dx_padded(sh*u + a, sw*v + b) = sum over the taps r = sh*r' + a, s = sw*s' + b of
+    // dy(u - r', v - s') * w(r, s); dy sits at frame offset (hh, hw), so the shift is (hh - r') rows and (hw - s') columns.
+    if (cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)p->N * p->C * p->H * p->W, s) != cudaSuccess) return -1;
+    for (int a = 0; a < p->stride_h && !rc; ++a)
+      for (int b = 0; b < p->stride_w && !rc; ++b) {
+        TapList taps;
+        for (int r = a; r < p->R; r += p->stride_h)
+          for (int q = b; q < p->S; q += p->stride_w)
+            taps.add((st->dy_off_h - r / p->stride_h) * st->frame_w + (st->dy_off_w - q / p->stride_w), 0, ntap - 1 - (r * p->S + q));
+        if (!taps.n) continue;      // no tap lands on this phase: it stays zero
+        OutGeom og{st->frame_h, st->frame_w, p->H, p->W, p->stride_h, p->stride_w, a - p->pad_h, b - p->pad_w};
+        rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, taps, og, true, conv_flops(p) * taps.n / ntap, s, "DLGpuConvolutionBackwardData");
+      }
   }
   return rc ? -1 : 1;
 }
@@ -958,7 +1024,16 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
   g.n_tiles = (p->K + bn - 1) / bn;
   // dy row m' holds output pixel (p, q) at frame position (p + dy_off_h, q + dy_off_w); tap (r, s) needs the padded
   // input at (p + r, q + s), which sits at frame row m' + (r - dy_off_h) * frame_w + (s - dy_off_w)
-  for (int r = 0; r < st->eR; ++r) for (int q = 0; q < st->eS; ++q) g.tap_off[r * st->eS + q] = (r - st->dy_off_h) * st->frame_w + (q - st->dy_off_w);
+  for (int r = 0; r < st->eR; ++r)
+    for (int q = 0; q < st->eS; ++q) {
+      int t = r * st->eS + q;
+      if (st->cls == 4) {
+        g.tap_off[t] = (r / p->stride_h - st->dy_off_h) * st->frame_w + (q / p->stride_w - st->dy_off_w);
+        g.tap_col[t] = (short)(((r % p->stride_h) * p->stride_w + q % p->stride_w) * p->C);
+      } else {
+        g.tap_off[t] = (r - st->dy_off_h) * st->frame_w + (q - st->dy_off_w);
+      }
+    }
   long long rows = st->dy.rows;
   int kit = (int)((rows + BK - 1) / BK);
   int splits = choose_splits(g.m_tiles * g.n_tiles * g.tap_tiles, kit, 4, 1024, true);
