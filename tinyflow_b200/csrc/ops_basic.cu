@@ -299,13 +299,28 @@ template <int MODE> __global__ void __launch_bounds__(kBlock) loss_grad_kernel(c
 // ---- concat along axis 1 ---------------------------------------------------------------
 // dst[n, off + j] = src[n, j] for j < src_inner; MODE 0 copies src -> dst slice, MODE 1 the
 // slice of dst -> src (the backward split).  Rows are n, `inner` counts floats per sample.
-template <int MODE> __global__ void __launch_bounds__(kBlock) slice_copy_kernel(float* __restrict__ part, float* __restrict__ whole, int64_t nrows, int64_t part_inner, int64_t whole_inner, int64_t off) {
-  int64_t total = nrows * part_inner, stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    int64_t r = i / part_inner, j = i % part_inner;
-    if (MODE == 0) whole[r * whole_inner + off + j] = part[i];
-    else part[i] = whole[r * whole_inner + off + j];
+// One grid row (blockIdx.y) per sample, so no per-element divide; V = float4 when both inner sizes and the offset
+// are multiples of 4 floats, else float.
+template <int MODE, typename V> __global__ void __launch_bounds__(kBlock) slice_copy_kernel(V* __restrict__ part, V* __restrict__ whole, int64_t nrows, int64_t part_inner, int64_t whole_inner, int64_t off) {
+  for (int64_t r = blockIdx.y; r < nrows; r += gridDim.y) {
+    V* p = part + r * part_inner;
+    V* w = whole + r * whole_inner + off;
+    for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < part_inner; j += (int64_t)gridDim.x * blockDim.x) {
+      if (MODE == 0) w[j] = p[j];
+      else p[j] = w[j];
+    }
   }
+}
+template <int MODE> static void launch_slice_copy(float* part, float* whole, int64_t rows, int64_t part_inner, int64_t whole_inner, int64_t off, cudaStream_t s) {
+  if (rows <= 0 || part_inner <= 0) return;
+  bool vec = part_inner % 4 == 0 && whole_inner % 4 == 0 && off % 4 == 0 && ((uintptr_t)part % 16 == 0) && ((uintptr_t)whole % 16 == 0);
+  int64_t per_row = vec ? part_inner / 4 : part_inner;
+  int gy = (int)(rows < 65535 ? rows : 65535);
+  int64_t want = (per_row + kBlock - 1) / kBlock, cap = (int64_t)8 * 148 / gy + 1;
+  int gx = (int)(want < cap ? want : cap);
+  dim3 grid(gx < 1 ? 1 : gx, gy);
+  if (vec) slice_copy_kernel<MODE, float4><<<grid, kBlock, 0, s>>>((float4*)part, (float4*)whole, rows, part_inner / 4, whole_inner / 4, off / 4);
+  else slice_copy_kernel<MODE, float><<<grid, kBlock, 0, s>>>(part, whole, rows, part_inner, whole_inner, off);
 }
 
 // ---- dropout: counter-based keep mask ---------------------------------------------------
@@ -717,8 +732,9 @@ int DLGpuConcatForward(const DLArrayHandle input1, const DLArrayHandle input2, D
   TF_REQUIRE(output && numel(output) == rows * (ia + ib), "DLGpuConcatForward: output size mismatch");
   cudaStream_t s = stream_of(cudaStream);
   note_compute_stream(s);
-  slice_copy_kernel<0><<<grid_for(rows * ia, kBlock), kBlock, 0, s>>>((float*)input1->data, FM(output), rows, ia, ia + ib, 0);
-  slice_copy_kernel<0><<<grid_for(rows * ib, kBlock), kBlock, 0, s>>>((float*)input2->data, FM(output), rows, ib, ia + ib, ia);
+  KernelTimer kt("DLGpuConcatForward", s, 0, 8.0 * rows * (ia + ib), 2);
+  launch_slice_copy<0>((float*)input1->data, FM(output), rows, ia, ia + ib, 0, s);
+  launch_slice_copy<0>((float*)input2->data, FM(output), rows, ib, ia + ib, ia, s);
   if (after_launch(s, "DLGpuConcatForward", 2) != 0) return -1;
   return 0;
 }
@@ -728,7 +744,8 @@ int DLGpuConcataBackward(const DLArrayHandle input1, const DLArrayHandle input2,
   TF_REQUIRE(doutput && dinput1 && numel(doutput) == rows * (ia + ib) && numel(dinput1) == rows * ia, "DLGpuConcataBackward: size mismatch");
   cudaStream_t s = stream_of(cudaStream);
   note_compute_stream(s);
-  slice_copy_kernel<1><<<grid_for(rows * ia, kBlock), kBlock, 0, s>>>(FM(dinput1), (float*)doutput->data, rows, ia, ia + ib, 0);
+  KernelTimer kt("DLGpuConcatBackward", s, 0, 8.0 * rows * ia);
+  launch_slice_copy<1>(FM(dinput1), (float*)doutput->data, rows, ia, ia + ib, 0, s);
   TF_AFTER(s, "DLGpuConcataBackward");
   return 0;
 }
@@ -738,7 +755,8 @@ int DLGpuConcatbBackward(const DLArrayHandle input1, const DLArrayHandle input2,
   TF_REQUIRE(doutput && dinput2 && numel(doutput) == rows * (ia + ib) && numel(dinput2) == rows * ib, "DLGpuConcatbBackward: size mismatch");
   cudaStream_t s = stream_of(cudaStream);
   note_compute_stream(s);
-  slice_copy_kernel<1><<<grid_for(rows * ib, kBlock), kBlock, 0, s>>>(FM(dinput2), (float*)doutput->data, rows, ib, ia + ib, ia);
+  KernelTimer kt("DLGpuConcatBackward", s, 0, 8.0 * rows * ib);
+  launch_slice_copy<1>(FM(dinput2), (float*)doutput->data, rows, ib, ia + ib, ia, s);
   TF_AFTER(s, "DLGpuConcatbBackward");
   return 0;
 }

@@ -12,34 +12,92 @@ namespace tf {
 // cannot be observed: a max window that covers only padding yields 0, and on ties the first
 // maximum in row-major window order receives the gradient.
 // =====================================================================================
-struct PoolGeom { int C, H, W, P, Q, ph, pw, sh, sw, kh, kw; };
+// Division of a 32-bit unsigned number by a divisor fixed at launch time (multiply-high, add, two shifts: the
+// round-up method for invariant divisors): flat indices are split into (plane, row, column) per element, and
+// a hardware-emulated 64-bit divide per split made these kernels instruction-bound.
+struct FastDiv {
+  uint32_t d, m, s1, s2;
+  __host__ void init(uint32_t div) {
+    d = div ? div : 1;
+    uint32_t l = 0;
+    while ((1ull << l) < d) ++l;                         // ceil(log2 d)
+    m = (uint32_t)((((1ull << 32) * ((1ull << l) - d)) / d) + 1);
+    s1 = l < 1 ? l : 1; s2 = l > 1 ? l - 1 : 0;
+  }
+  __device__ __forceinline__ uint32_t div(uint32_t n) const {
+    uint32_t t = __umulhi(m, n);
+    return (t + ((n - t) >> s1)) >> s2;
+  }
+};
+struct PoolGeom { int C, H, W, P, Q, ph, pw, sh, sw, kh, kw; FastDiv dHW, dW, dPQ, dQ, dsh, dsw; };
 
+// flat index -> (plane, a, b) with a * width + b the offset inside a plane of `area` elements
+__device__ __forceinline__ void split_index(int64_t i, const FastDiv& area, const FastDiv& width, int64_t& plane, int& a, int& b) {
+  if (i <= 0xffffffffll) {
+    uint32_t n = (uint32_t)i, pl = area.div(n), rem = n - pl * area.d, r = width.div(rem);
+    plane = pl; a = (int)r; b = (int)(rem - r * width.d);
+  } else {
+    plane = i / area.d;
+    int rem = (int)(i - plane * area.d);
+    a = rem / (int)width.d; b = rem - a * (int)width.d;
+  }
+}
+// windows p with p*stride - pad <= h < p*stride - pad + win, clipped to [0, count)
+__device__ __forceinline__ void covering(int h, int pad, int win, int stride, const FastDiv& ds, int count, int& lo, int& hi) {
+  int t = h + pad - win + 1;                             // first window start that still covers h, times nothing yet
+  lo = t <= 0 ? 0 : (int)ds.div((uint32_t)(t + stride - 1));
+  hi = min(count - 1, (int)ds.div((uint32_t)(h + pad)));
+}
+
+// KH, KW > 0 fix the window at compile time (all loads of a window are issued before the first compare);
+// KH = 0 takes the window from the geometry.
+template <int KH, int KW>
 __device__ __forceinline__ int window_argmax(const float* __restrict__ plane, const PoolGeom& g, int p, int q, float* best_out) {
-  int h0 = p * g.sh - g.ph, w0 = q * g.sw - g.pw;
+  const int h0 = p * g.sh - g.ph, w0 = q * g.sw - g.pw;
   int best = -1;
   float bv = 0.f;
-  for (int r = 0; r < g.kh; ++r) {
-    int h = h0 + r;
-    if (h < 0 || h >= g.H) continue;
-    for (int s = 0; s < g.kw; ++s) {
-      int w = w0 + s;
-      if (w < 0 || w >= g.W) continue;
-      float v = plane[h * g.W + w];
-      if (best < 0 || v > bv) { best = h * g.W + w; bv = v; }
+  if (KH > 0) {
+    float v[KH > 0 ? KH * KW : 1];
+#pragma unroll
+    for (int r = 0; r < KH; ++r)
+#pragma unroll
+      for (int s = 0; s < KW; ++s) {
+        int h = h0 + r, w = w0 + s;
+        bool ok = h >= 0 && h < g.H && w >= 0 && w < g.W;
+        v[r * KW + s] = ok ? __ldg(plane + h * g.W + w) : 0.f;
+      }
+#pragma unroll
+    for (int r = 0; r < KH; ++r)
+#pragma unroll
+      for (int s = 0; s < KW; ++s) {
+        int h = h0 + r, w = w0 + s;
+        bool ok = h >= 0 && h < g.H && w >= 0 && w < g.W;
+        if (ok && (best < 0 || v[r * KW + s] > bv)) { best = h * g.W + w; bv = v[r * KW + s]; }
+      }
+  } else {
+    for (int r = 0; r < g.kh; ++r) {
+      int h = h0 + r;
+      if (h < 0 || h >= g.H) continue;
+      for (int s = 0; s < g.kw; ++s) {
+        int w = w0 + s;
+        if (w < 0 || w >= g.W) continue;
+        float v = __ldg(plane + h * g.W + w);
+        if (best < 0 || v > bv) { best = h * g.W + w; bv = v; }
+      }
     }
   }
   *best_out = bv;
   return best;
 }
 
+template <int KH, int KW>
 __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ idx, int64_t total, PoolGeom g) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  int PQ = g.P * g.Q;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    int64_t plane = i / PQ;
-    int pq = (int)(i % PQ), p = pq / g.Q, q = pq % g.Q;
+    int64_t plane; int p, q;
+    split_index(i, g.dPQ, g.dQ, plane, p, q);
     float v;
-    int a = window_argmax(x + plane * g.H * g.W, g, p, q, &v);
+    int a = window_argmax<KH, KW>(x + plane * g.dHW.d, g, p, q, &v);
     if (y) y[i] = a < 0 ? 0.f : v;
     if (idx) idx[i] = a;
   }
@@ -48,84 +106,98 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restric
 // first maximum it is.  No atomics, deterministic, dx fully written.
 __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, int64_t total, PoolGeom g) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  int HW = g.H * g.W, PQ = g.P * g.Q;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    int64_t plane = i / HW;
-    int hw = (int)(i % HW), h = hw / g.W, w = hw % g.W;
-    const float* xp = x + plane * HW;
-    const float* dp = dy + plane * PQ;
-    // windows (p,q) with p*sh - ph <= h < p*sh - ph + kh
-    int p_lo = (h + g.ph - g.kh + g.sh) / g.sh; if (h + g.ph - g.kh + 1 <= 0) p_lo = 0;
-    int p_hi = min(g.P - 1, (h + g.ph) / g.sh);
-    int q_lo = (w + g.pw - g.kw + g.sw) / g.sw; if (w + g.pw - g.kw + 1 <= 0) q_lo = 0;
-    int q_hi = min(g.Q - 1, (w + g.pw) / g.sw);
+    int64_t plane; int h, w;
+    split_index(i, g.dHW, g.dW, plane, h, w);
+    const int hw = h * g.W + w;
+    const float* xp = x + plane * g.dHW.d;
+    const float* dp = dy + plane * g.dPQ.d;
+    int p_lo, p_hi, q_lo, q_hi;
+    covering(h, g.ph, g.kh, g.sh, g.dsh, g.P, p_lo, p_hi);
+    covering(w, g.pw, g.kw, g.sw, g.dsw, g.Q, q_lo, q_hi);
     float acc = 0.f;
     for (int p = p_lo; p <= p_hi; ++p)
       for (int q = q_lo; q <= q_hi; ++q) {
         float v;
-        if (window_argmax(xp, g, p, q, &v) == hw) acc += dp[p * g.Q + q];
+        if (window_argmax<0, 0>(xp, g, p, q, &v) == hw) acc += dp[p * g.Q + q];
       }
     dx[i] = acc;
   }
 }
-// Same gather, but with the forward pass's saved first-maximum indices: one index load per covering window
-// instead of a window scan.
-__global__ void __launch_bounds__(256) maxpool_bwd_idx_kernel(const int32_t* __restrict__ idx, const float* __restrict__ dy, float* __restrict__ dx, int64_t total, PoolGeom g) {
+// Same gather with the forward pass's saved first-maximum indices (MAXPOOL) or plain summation (average pooling).
+// NP x NQ bounds the windows that can cover one input element (ceil(window / stride) per axis, 0 = take the bounds
+// at run time); with compile-time bounds all index and dy loads are issued before the first use.
+template <bool MAXPOOL, int NP, int NQ>
+__global__ void __launch_bounds__(256) pool_bwd_gather_kernel(const int32_t* __restrict__ idx, const float* __restrict__ dy, float* __restrict__ dx, int64_t total, float scale, PoolGeom g) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  int HW = g.H * g.W, PQ = g.P * g.Q;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    int64_t plane = i / HW;
-    int hw = (int)(i % HW), h = hw / g.W, w = hw % g.W;
-    const int32_t* ip = idx + plane * PQ;
-    const float* dp = dy + plane * PQ;
-    int p_lo = (h + g.ph - g.kh + g.sh) / g.sh; if (h + g.ph - g.kh + 1 <= 0) p_lo = 0;
-    int p_hi = min(g.P - 1, (h + g.ph) / g.sh);
-    int q_lo = (w + g.pw - g.kw + g.sw) / g.sw; if (w + g.pw - g.kw + 1 <= 0) q_lo = 0;
-    int q_hi = min(g.Q - 1, (w + g.pw) / g.sw);
+    int64_t plane; int h, w;
+    split_index(i, g.dHW, g.dW, plane, h, w);
+    const int hw = h * g.W + w;
+    const int32_t* ip = idx + plane * g.dPQ.d;
+    const float* dp = dy + plane * g.dPQ.d;
+    int p_lo, p_hi, q_lo, q_hi;
+    covering(h, g.ph, g.kh, g.sh, g.dsh, g.P, p_lo, p_hi);
+    covering(w, g.pw, g.kw, g.sw, g.dsw, g.Q, q_lo, q_hi);
     float acc = 0.f;
-    for (int p = p_lo; p <= p_hi; ++p)
-      for (int q = q_lo; q <= q_hi; ++q)
-        if (__ldg(ip + p * g.Q + q) == hw) acc += __ldg(dp + p * g.Q + q);
-    dx[i] = acc;
+    if (NP > 0) {
+      float v[NP > 0 ? NP * NQ : 1];
+      int id[NP > 0 ? NP * NQ : 1];
+#pragma unroll
+      for (int a = 0; a < NP; ++a)
+#pragma unroll
+        for (int b = 0; b < NQ; ++b) {
+          int p = p_lo + a, q = q_lo + b;
+          bool ok = p <= p_hi && q <= q_hi;
+          int o = ok ? p * g.Q + q : 0;
+          v[a * NQ + b] = ok ? __ldg(dp + o) : 0.f;
+          id[a * NQ + b] = MAXPOOL ? (ok ? __ldg(ip + o) : -1) : hw;
+        }
+#pragma unroll
+      for (int k = 0; k < NP * NQ; ++k) acc += id[k] == hw ? v[k] : 0.f;
+    } else {
+      for (int p = p_lo; p <= p_hi; ++p)
+        for (int q = q_lo; q <= q_hi; ++q) {
+          float v = __ldg(dp + p * g.Q + q);
+          int id = MAXPOOL ? __ldg(ip + p * g.Q + q) : hw;
+          acc += id == hw ? v : 0.f;
+        }
+    }
+    dx[i] = acc * scale;
   }
 }
+template <int KH, int KW>
 __global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t total, PoolGeom g) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  int PQ = g.P * g.Q;
   float inv = 1.f / (float)(g.kh * g.kw);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    int64_t plane = i / PQ;
-    int pq = (int)(i % PQ), p = pq / g.Q, q = pq % g.Q;
-    const float* xp = x + plane * g.H * g.W;
+    int64_t plane; int p, q;
+    split_index(i, g.dPQ, g.dQ, plane, p, q);
+    const float* xp = x + plane * g.dHW.d;
     int h0 = p * g.sh - g.ph, w0 = q * g.sw - g.pw;
     float acc = 0.f;
-    for (int r = 0; r < g.kh; ++r) {
-      int h = h0 + r;
-      if (h < 0 || h >= g.H) continue;
-      for (int s = 0; s < g.kw; ++s) {
-        int w = w0 + s;
-        if (w >= 0 && w < g.W) acc += xp[h * g.W + w];
+    if (KH > 0) {
+      float v[KH > 0 ? KH * KW : 1];
+#pragma unroll
+      for (int r = 0; r < KH; ++r)
+#pragma unroll
+        for (int s = 0; s < KW; ++s) {
+          int h = h0 + r, w = w0 + s;
+          v[r * KW + s] = (h >= 0 && h < g.H && w >= 0 && w < g.W) ? __ldg(xp + h * g.W + w) : 0.f;
+        }
+#pragma unroll
+      for (int k = 0; k < KH * KW; ++k) acc += v[k];
+    } else {
+      for (int r = 0; r < g.kh; ++r) {
+        int h = h0 + r;
+        if (h < 0 || h >= g.H) continue;
+        for (int s = 0; s < g.kw; ++s) {
+          int w = w0 + s;
+          if (w >= 0 && w < g.W) acc += __ldg(xp + h * g.W + w);
+        }
       }
     }
     y[i] = acc * inv;
-  }
-}
-__global__ void __launch_bounds__(256) avgpool_bwd_kernel(const float* __restrict__ dy, float* __restrict__ dx, int64_t total, PoolGeom g) {
-  int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  int HW = g.H * g.W, PQ = g.P * g.Q;
-  float inv = 1.f / (float)(g.kh * g.kw);
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    int64_t plane = i / HW;
-    int hw = (int)(i % HW), h = hw / g.W, w = hw % g.W;
-    const float* dp = dy + plane * PQ;
-    int p_lo = (h + g.ph - g.kh + g.sh) / g.sh; if (h + g.ph - g.kh + 1 <= 0) p_lo = 0;
-    int p_hi = min(g.P - 1, (h + g.ph) / g.sh);
-    int q_lo = (w + g.pw - g.kw + g.sw) / g.sw; if (w + g.pw - g.kw + 1 <= 0) q_lo = 0;
-    int q_hi = min(g.Q - 1, (w + g.pw) / g.sw);
-    float acc = 0.f;
-    for (int p = p_lo; p <= p_hi; ++p)
-      for (int q = q_lo; q <= q_hi; ++q) acc += dp[p * g.Q + q];
-    dx[i] = acc * inv;
   }
 }
 
@@ -133,7 +205,28 @@ static PoolGeom geom_of(const PoolPlan* p) {
   PoolGeom g;
   g.C = p->C; g.H = p->H; g.W = p->W; g.P = p->P; g.Q = p->Q;
   g.ph = p->pad_h; g.pw = p->pad_w; g.sh = p->stride_h; g.sw = p->stride_w; g.kh = p->win_h; g.kw = p->win_w;
+  g.dHW.init((uint32_t)(p->H * p->W)); g.dW.init((uint32_t)p->W); g.dPQ.init((uint32_t)(p->P * p->Q)); g.dQ.init((uint32_t)p->Q);
+  g.dsh.init((uint32_t)p->stride_h); g.dsw.init((uint32_t)p->stride_w);
   return g;
+}
+
+static void launch_maxpool_fwd(const PoolPlan* p, const float* x, float* y, int32_t* idx, int64_t total, cudaStream_t s) {
+  PoolGeom g = geom_of(p);
+  int grid = grid_for(total, 256);
+  if (p->win_h == 3 && p->win_w == 3) maxpool_fwd_kernel<3, 3><<<grid, 256, 0, s>>>(x, y, idx, total, g);
+  else if (p->win_h == 2 && p->win_w == 2) maxpool_fwd_kernel<2, 2><<<grid, 256, 0, s>>>(x, y, idx, total, g);
+  else if (p->win_h == 1 && p->win_w == 1) maxpool_fwd_kernel<1, 1><<<grid, 256, 0, s>>>(x, y, idx, total, g);
+  else maxpool_fwd_kernel<0, 0><<<grid, 256, 0, s>>>(x, y, idx, total, g);
+}
+template <bool MAXPOOL> static void launch_pool_gather(const PoolPlan* p, const int32_t* idx, const float* dy, float* dx, int64_t total, float scale, cudaStream_t s) {
+  PoolGeom g = geom_of(p);
+  int grid = grid_for(total, 256);
+  auto bound = [](int win, int stride, int count) { int n = (win + stride - 1) / stride; return n < count ? n : count; };
+  int np = bound(p->win_h, p->stride_h, p->P), nq = bound(p->win_w, p->stride_w, p->Q);
+  if (np == 1 && nq == 1) pool_bwd_gather_kernel<MAXPOOL, 1, 1><<<grid, 256, 0, s>>>(idx, dy, dx, total, scale, g);
+  else if (np <= 2 && nq <= 2) pool_bwd_gather_kernel<MAXPOOL, 2, 2><<<grid, 256, 0, s>>>(idx, dy, dx, total, scale, g);
+  else if (np <= 3 && nq <= 3) pool_bwd_gather_kernel<MAXPOOL, 3, 3><<<grid, 256, 0, s>>>(idx, dy, dx, total, scale, g);
+  else pool_bwd_gather_kernel<MAXPOOL, 0, 0><<<grid, 256, 0, s>>>(idx, dy, dx, total, scale, g);
 }
 
 // =====================================================================================
@@ -400,11 +493,12 @@ int DLGpuPooling2DForward(const DLArrayHandle input, DLArrayHandle output, void*
   if (p->mode == 0 && !p->argmax) p->argmax = (int32_t*)pool_alloc(sizeof(int32_t) * (size_t)total);   // optional: backward rescans if absent
   KernelTimer kt("DLGpuPooling2DForward", s, 0, 4.0 * (numel(input) + numel(output)));
   if (p->mode == 0) {
-    maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), p->argmax, total, geom_of(p));
+    launch_maxpool_fwd(p, (const float*)input->data, out_f32(output), p->argmax, total, s);
     p->argmax_src = input->data;
     p->argmax_version = version_of(input->data);
   }
-  else avgpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), total, geom_of(p));
+  else if (p->win_h == 3 && p->win_w == 3) avgpool_fwd_kernel<3, 3><<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), total, geom_of(p));
+  else avgpool_fwd_kernel<0, 0><<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), total, geom_of(p));
   TF_AFTER(s, "DLGpuPooling2DForward");
   return 0;
 }
@@ -421,11 +515,11 @@ int DLGpuPooling2DBackward(const DLArrayHandle input, const DLArrayHandle output
   KernelTimer kt("DLGpuPooling2DBackward", s, 0, 4.0 * ((p->mode == 0 ? 2 : 1) * numel(input) + numel(output)));
   if (p->mode == 0) {
     if (p->argmax && p->argmax_src == input->data && p->argmax_version == version_of(input->data))
-      maxpool_bwd_idx_kernel<<<grid_for(total, 256), 256, 0, s>>>(p->argmax, (const float*)doutput->data, out_f32(dinput), total, geom_of(p));
+      launch_pool_gather<true>(p, p->argmax, (const float*)doutput->data, out_f32(dinput), total, 1.f, s);
     else
       maxpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, (const float*)doutput->data, out_f32(dinput), total, geom_of(p));
   }
-  else avgpool_bwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)doutput->data, out_f32(dinput), total, geom_of(p));
+  else launch_pool_gather<false>(p, nullptr, (const float*)doutput->data, out_f32(dinput), total, 1.f / (float)(p->win_h * p->win_w), s);
   TF_AFTER(s, "DLGpuPooling2DBackward");
   return 0;
 }
@@ -436,7 +530,7 @@ int TfPoolingArgmax(const DLArrayHandle input, int32_t* indices_dev, void*** cud
   cudaStream_t s = stream_of(cudaStream);
   int64_t total = (int64_t)p->N * p->C * p->P * p->Q;
   note_compute_stream(s);
-  maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, nullptr, indices_dev, total, geom_of(p));
+  launch_maxpool_fwd(p, (const float*)input->data, nullptr, indices_dev, total, s);
   TF_AFTER(s, "TfPoolingArgmax");
   return 0;
 }
