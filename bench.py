@@ -334,13 +334,13 @@ def main():
         top = max(kernel_rows, key=lambda r: r["ms"])
         total_ms = sum(r["ms"] for r in kernel_rows)
         if top["flops"] > 0:
-            # 3xTF32 issues three tensor-core MMAs per algorithmic multiply-add; the denominator is the measured
-            # bf16 rate halved (TF32 runs at half the bf16 rate), sustained figure because the kernel runs inside a long step
-            peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) / 2.0
+            # 3xFP16 issues three tensor-core MMAs per algorithmic multiply-add; the denominator is the measured 16-bit
+            # tensor rate (fp16 runs at the bf16 rate), sustained figure because the kernel runs inside a long step
+            peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
             ach = top["flops"] / (top["ms"] / 1000.0) / 1e12
             roofline = {"bound": "tensor", "kernel": top["name"], "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                         "traffic": None, "launches": top["launches"], "avg_us": 1000.0 * top["ms"] / max(top["launches"], 1),
-                        "peak_source": "%s bf16 sustained / 2 (tf32); algorithmic flops, issued tensor flops are 3x" % peak_kind,
+                        "peak_source": "%s bf16 sustained (fp16 inputs run at the same rate); algorithmic flops, issued tensor flops are 3x" % peak_kind,
                         "share_of_timed_kernels": top["ms"] / total_ms if total_ms else None}
         else:
             peak = peaks["hbm_gbs"]

@@ -1,16 +1,20 @@
-// Tensor-core path of the dense contractions: a persistent, warp-specialised 3xTF32 GEMM on the
+// Tensor-core path of the dense contractions: a persistent, warp-specialised 3xFP16 GEMM on the
 // Blackwell tcgen05 pipeline (TMA -> shared memory -> tcgen05.mma -> TMEM -> registers -> HBM).
 //
-// 3xTF32.  Every fp32 operand element a is split once into hi = tf32(a) and lo = tf32(a - hi) by a
-// packing kernel; the GEMM accumulates hi*hi + lo*hi + hi*lo in fp32 TMEM, which restores fp32-level
-// accuracy (the dropped lo*lo term is below 2^-22 relative).  Packed operands are plain 2-D row-major
+// 3xFP16.  Every fp32 operand tensor is scaled by a power of two s chosen from its largest magnitude
+// (max|a|*s in [2^14, 2^15)), and every element is split once into hi = fp16(a*s) and lo = fp16(a*s - hi)
+// by a packing kernel: 22 mantissa bits, the same as a tf32 hi/lo pair, and elements down to 2^-18 of the
+// tensor's maximum keep all of them (smaller ones lose absolute precision below 2^-40 of the maximum).
+// The GEMM accumulates hi*hi + lo*hi + hi*lo in fp32 TMEM (the dropped lo*lo term is below 2^-22
+// relative) and the epilogue multiplies by 1/(s_A*s_B), exact.  fp16 inputs run the tensor pipe at twice
+// the tf32 rate and halve the operand bytes.  Packed operands are plain 2-D row-major
 // matrices [rows][cols] (cols contiguous) so that one kernel serves every contraction:
 //
 //   matmul            A, B packed as they lie; the operand's "major" (K contiguous or M/N contiguous)
 //                     is a run-time flag that only changes the TMA box shape and the UMMA descriptor.
 //   conv forward      activations packed pixel-major [N * frame_h * frame_w][C] with the zero halo
 //                     materialised, filters packed [Cout][tap][C]; a filter tap is then a constant
-//                     row shift of the activation matrix, so the K loop is (tap, 32-channel chunk)
+//                     row shift of the activation matrix, so the K loop is (tap, 64-channel chunk)
 //                     and each step is two plain 2-D TMA boxes.  Outputs computed for halo anchors
 //                     are discarded by the epilogue.
 //   conv backward-data  same kernel on the packed output gradient with the flipped filter
@@ -21,11 +25,12 @@
 //
 // Kernel roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2-9 =
 // epilogue (two per TMEM lane quarter, half the columns each).  Shared memory holds a ring of stages {A_hi, A_lo, B_hi, B_lo}
-// (128-byte swizzle, 32 fp32 of K per stage); TMEM holds two accumulators so that promoting one group of
+// (128-byte swizzle, 64 halves of K per stage); TMEM holds two accumulators so that promoting one group of
 // stages to registers overlaps the MMAs of the next.  Every mbarrier wait is bounded: on time-out the CTA raises an
 // error flag the host reads, drains its outstanding copies, frees its TMEM and returns.
 #include "common.h"
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <mutex>
 #include <type_traits>
 #include <unordered_map>
@@ -53,7 +58,7 @@ uint64_t version_of(const void* p) {
 // device-side primitives (inline PTX)
 // ------------------------------------------------------------------------------------------------
 constexpr int BM = 128;            // UMMA M (TMEM lanes)
-constexpr int BK = 32;             // fp32 elements of K per stage = one 128-byte swizzle row
+constexpr int BK = 64;             // fp16 elements of K per stage = one 128-byte swizzle row
 constexpr int kThreads = 320;
 constexpr int kGroupIters = 4;     // stages accumulated in TMEM before the epilogue promotes them to registers
 constexpr long long kWaitCycles = 3000000000ll;   // ~1.5 s at 2 GHz: far beyond any legitimate wait
@@ -102,11 +107,11 @@ __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fe
 __device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
@@ -130,12 +135,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, descriptor version 1 (Blackwell).
-//   K-major operand : 128-byte swizzle with 16-byte atoms (layout type 2): rows of 128 B (32 fp32 of K),
-//                     8-row groups 1024 B apart (SBO); LBO unused (= 16 B).
-//   MN-major operand: tf32 allows only the 128-byte swizzle with 32-byte atoms (layout type 1): tiles of
-//                     [32 K-rows][32 fp32 of M/N] = 4096 B; 4-row K groups 512 B apart (SBO), tiles 4096 B
-//                     apart along M/N (LBO).
+// Shared-memory matrix descriptor, descriptor version 1 (Blackwell), 128-byte swizzle with 16-byte atoms
+// (layout type 2) for both majors:
+//   K-major operand : rows of 128 B (64 halves of K), 8-row groups 1024 B apart (SBO); LBO unused (= 16 B);
+//                     one MMA (K = 16) advances the start address by 32 B.
+//   MN-major operand: [64 K-rows][128 B = 64 halves of M/N] per column group; 8-row K groups 1024 B apart (SBO),
+//                     column groups 8192 B apart (LBO); one MMA (K = 16) advances the start address by 2048 B.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
   return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
          (1ull << 46) | ((uint64_t)layout_type << 61);
@@ -160,6 +165,7 @@ struct alignas(64) GemmParams {
   int ntaps;
   int atomic;                     // epilogue adds into `out` (pre-zeroed) instead of storing
   float* out;
+  const float* a_scale; const float* b_scale;   // device words: the power-of-two scales the packs were made with
   long long ldc;                  // kEpiRowMajor
   // kEpiNchw: row m -> (image, i, j) in a frame of frame_h x frame_w, stored at output pixel
   // (oi, oj) = (i*out_sh + out_off_h, j*out_sw + out_off_w) of channel plane c: ((image*out_c + c)*out_h + oi)*out_w + oj;
@@ -175,15 +181,15 @@ struct alignas(64) GemmParams {
 
 template <int BN> struct SmemLayout {
   static constexpr int kStages = BN <= 64 ? 4 : 3;
-  static constexpr int kABytes = BM * BK * 4;           // 16 KiB
-  static constexpr int kBBytes = BN * BK * 4;
+  static constexpr int kABytes = BM * BK * 2;           // 16 KiB
+  static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;   // + slack to align to 1024
 };
 
 template <int BN>
-__global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_constant__ GemmParams p) {
+__global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_constant__ GemmParams p) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -254,29 +260,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
             if (p.a_mn) { a_col = m0; a_row = kk; } else { a_col = kk; a_row = m0; }
             if (p.b_mn) { b_col = n0; b_row = kk; } else { b_col = kk; b_row = n0; }
           }
-          // M/N-major operands come through a 3-D view {32 columns, rows, column groups}: one copy lands
-          // [groups][32 rows][128 B], the layout the 32-byte-atom swizzle descriptor expects.
+          // M/N-major operands come through a 3-D view {64 columns, rows, column groups}: one copy lands
+          // [groups][64 rows][128 B], the layout the M/N-major descriptor expects.
           if (p.mode == kModeWgrad) {
             // One copy per tap slot; a slot past the last tap reads rows beyond the pack (the copy still completes
             // with its full byte count and fills zeros).
-            const int gps = p.slot >> 5;
+            const int gps = p.slot >> 6;
             for (int sl = 0; sl < p.taps_per_tile; ++sl) {
               int t = tap * p.taps_per_tile + sl;
               int row = t < p.ntaps ? a_row + p.tap_off[t] : 0x40000000;
-              int grp = (a_col + (t < p.ntaps ? p.tap_col[t] : 0)) >> 5;
-              tma_load_3d(a_hi + sl * gps * 4096, &p.a_hi, 0, row, grp, &full[stage]);
-              tma_load_3d(a_lo + sl * gps * 4096, &p.a_lo, 0, row, grp, &full[stage]);
+              int grp = (a_col + (t < p.ntaps ? p.tap_col[t] : 0)) >> 6;
+              tma_load_3d(a_hi + sl * gps * 8192, &p.a_hi, 0, row, grp, &full[stage]);
+              tma_load_3d(a_lo + sl * gps * 8192, &p.a_lo, 0, row, grp, &full[stage]);
             }
           } else if (p.a_mn) {
-            tma_load_3d(a_hi, &p.a_hi, 0, a_row, a_col >> 5, &full[stage]);
-            tma_load_3d(a_lo, &p.a_lo, 0, a_row, a_col >> 5, &full[stage]);
+            tma_load_3d(a_hi, &p.a_hi, 0, a_row, a_col >> 6, &full[stage]);
+            tma_load_3d(a_lo, &p.a_lo, 0, a_row, a_col >> 6, &full[stage]);
           } else {
             tma_load_2d(a_hi, &p.a_hi, a_col, a_row, &full[stage]);
             tma_load_2d(a_lo, &p.a_lo, a_col, a_row, &full[stage]);
           }
           if (p.b_mn) {
-            tma_load_3d(b_hi, &p.b_hi, 0, b_row, b_col >> 5, &full[stage]);
-            tma_load_3d(b_lo, &p.b_lo, 0, b_row, b_col >> 5, &full[stage]);
+            tma_load_3d(b_hi, &p.b_hi, 0, b_row, b_col >> 6, &full[stage]);
+            tma_load_3d(b_lo, &p.b_lo, 0, b_row, b_col >> 6, &full[stage]);
           } else {
             tma_load_2d(b_hi, &p.b_hi, b_col, b_row, &full[stage]);
             tma_load_2d(b_lo, &p.b_lo, b_col, b_row, &full[stage]);
@@ -299,12 +305,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
       // The B stage holds [B_hi ; B_lo] back to back, so ONE instruction with N = 2*BN computes A_hi*B_hi (columns
       // 0..BN-1) and A_hi*B_lo (columns BN..2BN-1); a second one with N = BN adds A_lo*B_hi.  Two instructions per
       // K step instead of three: a tcgen05.mma of this size costs ~115 cycles to issue whatever its N.
-      const uint32_t idesc_base = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) | ((uint32_t)(BM >> 4) << 24);
+      // instruction descriptor: D = f32 (bits 4-5 = 1), A = B = f16 (format 0), majors, N >> 3 at bit 17, M >> 4 at bit 24
+      const uint32_t idesc_base = (1u << 4) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) | ((uint32_t)(BM >> 4) << 24);
       const uint32_t idesc_wide = idesc_base | ((uint32_t)((2 * BN) >> 3) << 17), idesc_narrow = idesc_base | ((uint32_t)(BN >> 3) << 17);
-      const uint32_t a_lbo = p.a_mn ? 4096u : 16u, b_lbo = p.b_mn ? 4096u : 16u;
-      const uint32_t a_kstep = p.a_mn ? 1024u : 32u, b_kstep = p.b_mn ? 1024u : 32u;
-      const uint32_t a_sbo = p.a_mn ? 512u : 1024u, b_sbo = p.b_mn ? 512u : 1024u;
-      const uint32_t a_lt = p.a_mn ? 1u : 2u, b_lt = p.b_mn ? 1u : 2u;
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u, b_kstep = p.b_mn ? 2048u : 32u;
+      const uint32_t a_sbo = 1024u, b_sbo = 1024u;
+      const uint32_t a_lt = 2u, b_lt = 2u;
       int stage = 0; uint32_t phase = 0;
       int group = 0;            // accumulator groups issued so far (alternating TMEM buffers)
       bool ok = true;
@@ -322,11 +329,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
             const uint32_t st = smem_u32(smem + stage * L::kStageBytes);
             const uint32_t a_hi = st, a_lo = st + L::kABytes, b_hi = st + 2 * L::kABytes;
 #pragma unroll
-            for (int k = 0; k < BK / 8; ++k) {
+            for (int k = 0; k < BK / 16; ++k) {
               const uint64_t ah = umma_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lt), al = umma_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lt);
               const uint64_t bh = umma_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lt);      // N = 2*BN runs on into B_lo
-              umma_tf32(d_tmem, ah, bh, idesc_wide, (it > it0 || k > 0) ? 1u : 0u);
-              umma_tf32(d_tmem, al, bh, idesc_narrow, 1u);
+              umma_f16(d_tmem, ah, bh, idesc_wide, (it > it0 || k > 0) ? 1u : 0u);
+              umma_f16(d_tmem, al, bh, idesc_narrow, 1u);
             }
             tcgen05_commit(&empty[stage]);       // frees the stage once the MMAs above have read it
             if (++stage == L::kStages) { stage = 0; phase ^= 1; }
@@ -344,6 +351,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
     const int half = (warp - 2) >> 2;
     constexpr int HC = BN / 2;                  // columns per epilogue warp
     const int row_in_tile = quarter * 32 + lane;
+    const float inv_scale = (1.f / __ldg(p.a_scale)) * (1.f / __ldg(p.b_scale));     // powers of two: exact
     int group = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -424,7 +432,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
             if (lane == 0) mbar_arrive(&acc_empty[acc]);
           }
 #pragma unroll
-          for (int q = 0; q < 32; ++q) v1[q] += v2[q];
+          for (int q = 0; q < 32; ++q) v1[q] = (v1[q] + v2[q]) * inv_scale;
           store_cols(v1, c0, std::integral_constant<int, 32>{});
         }
         continue;
@@ -455,6 +463,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
       }
       if (!ok) break;
+#pragma unroll
+      for (int q = 0; q < HC; ++q) accv[q] *= inv_scale;
       store_cols(accv, 0, std::integral_constant<int, HC>{});
     }
   }
@@ -470,25 +480,57 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xtf32_kernel(const __grid_co
 }
 
 // ------------------------------------------------------------------------------------------------
-// packing kernels (fp32 -> hi / lo tf32 pair)
+// packing kernels (fp32 -> power-of-two scale + hi / lo fp16 pair)
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void split_tf32(float a, float& hi, float& lo) {
-  uint32_t h, l;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(a));
-  hi = __uint_as_float(h);
-  float r = a - hi;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(r));
-  lo = __uint_as_float(l);
+// Largest magnitude of a tensor, as the bit pattern of a non-negative float (unsigned order = float order).
+__global__ void __launch_bounds__(256) amax_kernel(const float* __restrict__ src, long long n, uint32_t* __restrict__ amax) {
+  uint32_t m = 0;
+  const long long stride = (long long)gridDim.x * blockDim.x, tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const float4* s4 = reinterpret_cast<const float4*>(src);
+    for (long long i = tid; i < n / 4; i += stride) {
+      float4 v = __ldg(s4 + i);
+      m = max(max(m, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)), max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)))));
+    }
+    for (long long i = (n / 4) * 4 + tid; i < n; i += stride) m = max(m, __float_as_uint(fabsf(__ldg(src + i))));
+  } else {
+    for (long long i = tid; i < n; i += stride) m = max(m, __float_as_uint(fabsf(__ldg(src + i))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(amax, m);
+}
+// Scale words of one pack: amax[0..1] alternate between uses (the pack kernel of use k reads amax[k & 1] and clears
+// amax[(k + 1) & 1] for the next use, so no separate clearing launch is needed), scale = the power of two in force.
+struct ScaleRef { const uint32_t* amax_cur; uint32_t* amax_next; float* scale; };
+// s = 2^(14 - floor(log2 amax)): amax * s lies in [2^14, 2^15), below the fp16 maximum 65504 after rounding
+__device__ __forceinline__ float scale_from_amax(uint32_t bits) {
+  int e = (int)((bits >> 23) & 0xff);
+  if (bits == 0 || e == 0xff) return 1.f;             // all zero, or Inf/NaN inside (the results are meaningless then)
+  if (e == 0) e = 1;
+  int se = 14 - (e - 127);
+  se = se > 100 ? 100 : (se < -100 ? -100 : se);
+  return __uint_as_float((uint32_t)(se + 127) << 23);
+}
+__device__ __forceinline__ float pack_scale(const ScaleRef& r, bool first_thread) {
+  const float s = scale_from_amax(__ldg(r.amax_cur));
+  if (first_thread) { *r.scale = s; *r.amax_next = 0; }
+  return s;
+}
+__device__ __forceinline__ void split_f16(float a, __half& hi, __half& lo) {
+  hi = __float2half_rn(a);
+  lo = __float2half_rn(a - __half2float(hi));
 }
 
 // rows x cols row-major (pitch src_ld) -> hi/lo with pitch dst_ld
-__global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restrict__ src, long long src_ld, float* __restrict__ hi, float* __restrict__ lo,
-                                                          long long dst_ld, long long rows, long long cols) {
+__global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restrict__ src, long long src_ld, __half* __restrict__ hi, __half* __restrict__ lo,
+                                                          long long dst_ld, long long rows, long long cols, ScaleRef sr) {
+  const float sc = pack_scale(sr, blockIdx.x == 0 && threadIdx.x == 0);
   long long total = rows * cols, stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     long long r = i / cols, c = i - r * cols;
-    float h, l;
-    split_tf32(src[r * src_ld + c], h, l);
+    __half h, l;
+    split_f16(src[r * src_ld + c] * sc, h, l);
     hi[r * dst_ld + c] = h;
     lo[r * dst_ld + c] = l;
   }
@@ -499,14 +541,17 @@ __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restric
 // (off > 0 places the source behind a zero halo; off <= 0 with sh > 1 selects one phase of a strided sampling).
 // Channels c < c_limit are written (zeros past C).  One block moves 32 frame columns x TC channels of one frame
 // row through shared memory: reads run along w (TC/8 independent loads per thread in flight), writes along c as
-// 16-byte vectors of hi and of lo.
+// 16-byte vectors (8 halves) of hi and of lo.
 struct PackGeom { int N, C, H, W, frame_h, frame_w, off_h, off_w, sh, sw, pitch, dst_c0, c_limit; };
 template <int TC>
-__global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, PackGeom g) {
-  __shared__ float tile[TC][33];
+__global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, __half* __restrict__ hi, __half* __restrict__ lo, PackGeom g, ScaleRef sr) {
+  // tile[c][j ^ (c / 8)]: the XOR keeps both phases free of bank conflicts (stores: 32 lanes = 32 pixels of one
+  // channel; loads: lanes = 8-channel groups of a few pixels that are TC/8 apart)
+  __shared__ float tile[TC][32];
+  const float sc = pack_scale(sr, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0);
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
   const int j0 = blockIdx.x * 32, i = blockIdx.y;
-  const int cblocks = (g.C + TC - 1) / TC;
+  const int cblocks = (g.c_limit + TC - 1) / TC;         // blocks cover every column that has to be defined
   const int n = blockIdx.z / cblocks, c0 = (blockIdx.z % cblocks) * TC;
   const int si = i * g.sh - g.off_h;
   const bool row_ok = si >= 0 && si < g.H;
@@ -522,25 +567,26 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
       v[k] = (ok && c < g.C) ? __ldg(s + c * plane) : 0.f;
     }
 #pragma unroll
-    for (int k = 0; k < TC / 8; ++k) tile[ty + 8 * k][tx] = v[k];
+    for (int k = 0; k < TC / 8; ++k) {
+      const int c = ty + 8 * k;
+      tile[c][tx ^ (c >> 3)] = v[k] * sc;
+    }
   }
   __syncthreads();
   {
-    // a warp writes whole pixels: lane -> 4 consecutive channels, TC/4 lanes per pixel, 128/TC pixels per pass
-    constexpr int LPP = TC / 4, PPW = 32 / LPP;       // lanes per pixel, pixels per warp pass
-    const int cl = (tx % LPP) * 4, c = c0 + cl;
-#pragma unroll
-    for (int k = 0; k < 32 / (8 * PPW); ++k) {
-      const int jj = (k * 8 + ty) * PPW + tx / LPP, j = j0 + jj;
+    // a warp pass writes 32 / LPP whole pixels: lane -> (pixel slot, 8-channel group); 16-byte stores of hi and of lo
+    constexpr int LPP = TC / 8;                       // lanes per pixel
+    const int grp = tx % LPP, px = tx / LPP, cl = grp * 8, c = c0 + cl;
+    for (int jb = ty; jb < LPP; jb += 8) {
+      const int jj = jb + px * LPP, j = j0 + jj;
       if (j < g.frame_w && c < g.c_limit) {
-        float4 h, l;
-        split_tf32(tile[cl][jj], h.x, l.x);
-        split_tf32(tile[cl + 1][jj], h.y, l.y);
-        split_tf32(tile[cl + 2][jj], h.z, l.z);
-        split_tf32(tile[cl + 3][jj], h.w, l.w);
+        __align__(16) __half h[8];
+        __align__(16) __half l[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) split_f16(tile[cl + e][jj ^ grp], h[e], l[e]);
         const long long o = (((long long)n * g.frame_h + i) * g.frame_w + j) * g.pitch + g.dst_c0 + c;
-        *reinterpret_cast<float4*>(hi + o) = h;
-        *reinterpret_cast<float4*>(lo + o) = l;
+        *reinterpret_cast<uint4*>(hi + o) = *reinterpret_cast<const uint4*>(h);
+        *reinterpret_cast<uint4*>(lo + o) = *reinterpret_cast<const uint4*>(l);
       }
     }
   }
@@ -548,12 +594,13 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
 
 // NCHW activations -> explicit patch matrix [N*P*Q][pitch], column (c*R + r)*S + s = the filter's own flat index
 // within one output channel, so the convolution becomes a 1x1 one over C*R*S "channels".  Used where the
-// channel count is too small to fill a 32-wide reduction chunk per tap (first layers, C = 3).
+// channel count is too small to fill a 64-wide reduction chunk per tap (first layers, C = 3).
 struct PatchGeom { int N, C, H, W, R, S, P, Q, sh, sw, pad_h, pad_w, cols, pitch; };
-__global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, PatchGeom g) {
+__global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restrict__ src, __half* __restrict__ hi, __half* __restrict__ lo, PatchGeom g, ScaleRef sr) {
   // column -> (source offset relative to the window origin, r, s), the same for every row
   __shared__ int col_off[1024];
   __shared__ short col_r[1024], col_s[1024];
+  const float sc = pack_scale(sr, blockIdx.x == 0 && threadIdx.x == 0);
   const int rs = g.R * g.S;
   for (int col = threadIdx.x; col < g.cols; col += blockDim.x) {
     const int c = col / rs, t = col - c * rs, r = t / g.S, q = t - r * g.S;
@@ -568,25 +615,33 @@ __global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restri
     const int n = (int)(row / pq), rem = (int)(row - (long long)n * pq), pp = rem / g.Q, qq = rem - pp * g.Q;
     const int i0 = pp * g.sh - g.pad_h, j0 = qq * g.sw - g.pad_w;
     const float* base = src + ((long long)n * g.C * g.H + i0) * g.W + j0;
-    float* h_row = hi + row * g.pitch;
-    float* l_row = lo + row * g.pitch;
-    for (int col = lane; col < g.pitch; col += 32) {
-      float a = 0.f;
-      if (col < g.cols) {
-        const int i = i0 + col_r[col], j = j0 + col_s[col];
-        if (i >= 0 && i < g.H && j >= 0 && j < g.W) a = __ldg(base + col_off[col]);
+    __half2* h_row = reinterpret_cast<__half2*>(hi + row * g.pitch);
+    __half2* l_row = reinterpret_cast<__half2*>(lo + row * g.pitch);
+    for (int col2 = lane; col2 < g.pitch / 2; col2 += 32) {        // two columns per lane
+      float a[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int col = 2 * col2 + e;
+        a[e] = 0.f;
+        if (col < g.cols) {
+          const int i = i0 + col_r[col], j = j0 + col_s[col];
+          if (i >= 0 && i < g.H && j >= 0 && j < g.W) a[e] = __ldg(base + col_off[col]) * sc;
+        }
       }
-      float h, l;
-      split_tf32(a, h, l);
-      h_row[col] = h; l_row[col] = l;
+      __half h0, l0, h1, l1;
+      split_f16(a[0], h0, l0);
+      split_f16(a[1], h1, l1);
+      h_row[col2] = __halves2half2(h0, h1);
+      l_row[col2] = __halves2half2(l0, l1);
     }
   }
 }
 
 // filters [K][C][R][S] -> forward pack [K][tap][cpad] (flip = 0) or backward-data pack [C][tap'][kpad] (flip = 1,
 // tap' = (R-1-r)*S + (S-1-s)), zero in the channel padding.
-__global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
-                                                          int K, int C, int R, int S, int flip, int inner_pad) {
+__global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restrict__ w, __half* __restrict__ hi, __half* __restrict__ lo,
+                                                          int K, int C, int R, int S, int flip, int inner_pad, ScaleRef sr) {
+  const float sc = pack_scale(sr, blockIdx.x == 0 && threadIdx.x == 0);
   int taps = R * S;
   long long rows = flip ? C : K, total = rows * taps * inner_pad, stride = (long long)gridDim.x * blockDim.x;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
@@ -598,10 +653,10 @@ __global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restric
     if (in < inner_n) {
       int k = flip ? in : row, c = flip ? row : in;
       int src_tap = flip ? (taps - 1 - tap) : tap;
-      a = w[((long long)k * C + c) * taps + src_tap];
+      a = w[((long long)k * C + c) * taps + src_tap] * sc;
     }
-    float h, l;
-    split_tf32(a, h, l);
+    __half h, l;
+    split_f16(a, h, l);
     hi[idx] = h; lo[idx] = l;
   }
 }
@@ -621,33 +676,32 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D fp32 row-major [rows][cols] with `pitch` floats per row; box = 32 cols x box_rows rows; 128-byte swizzle with
-// 16-byte atoms for K-major operands, with 32-byte atoms for the M/N-major ones (the only form tf32 takes there).
-static int make_map(CUtensorMap* m, const float* base, long long rows, long long cols, long long pitch, int box_rows) {
+// 2-D fp16 row-major [rows][cols] with `pitch` halves per row; box = 64 cols (128 B) x box_rows rows, 128-byte swizzle.
+static int make_map(CUtensorMap* m, const __half* base, long long rows, long long cols, long long pitch, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   TF_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)pitch * 4};
-  cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld pitch %lld)", (int)r, rows, cols, pitch);
   return 0;
 }
-// M/N-major operand: 3-D view {32 columns, rows, pitch / 32 column groups} with a box of `groups` groups x 32 rows.
-// The pack's pitch is a multiple of 32, so every group lies inside the allocation; columns past the logical
-// width hold whatever the pack left there and only reach output rows / columns that the epilogue masks.
-static int make_map_mn(CUtensorMap* m, const float* base, long long rows, long long pitch, int groups) {
+// M/N-major operand: 3-D view {64 columns, rows, pitch / 64 column groups} with a box of `groups` groups x 64 rows.
+// The pack's pitch is a multiple of 64, so every group lies inside the allocation; columns past the logical
+// width only reach output rows / columns that the epilogue masks.
+static int make_map_mn(CUtensorMap* m, const __half* base, long long rows, long long pitch, int groups) {
   EncodeTiledFn fn = encode_fn();
   TF_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from this driver");
-  TF_REQUIRE(pitch % 32 == 0, "M/N-major operand pitch %lld is not a multiple of 32", pitch);
-  cuuint64_t dims[3] = {32, (cuuint64_t)rows, (cuuint64_t)(pitch / 32)};
-  cuuint64_t strides[2] = {(cuuint64_t)pitch * 4, 128};
-  cuuint32_t box[3] = {32, 32, (cuuint32_t)groups};
+  TF_REQUIRE(pitch % 64 == 0, "M/N-major operand pitch %lld is not a multiple of 64", pitch);
+  cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(pitch / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)pitch * 2, 128};
+  cuuint32_t box[3] = {64, (cuuint32_t)BK, (cuuint32_t)groups};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (3-D) failed with %d (rows %lld pitch %lld groups %d)", (int)r, rows, pitch, groups);
   return 0;
 }
@@ -679,7 +733,7 @@ template <int BN> static int launch_gemm(const GemmParams& p, cudaStream_t s, do
   using L = SmemLayout<BN>;
   constexpr int slot = BN == 64 ? 0 : (BN == 128 ? 1 : 2);
   if (!g_attr_done[slot]) {
-    TF_CUDA(cudaFuncSetAttribute(gemm3xtf32_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    TF_CUDA(cudaFuncSetAttribute(gemm3xf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     g_attr_done[slot] = true;
   }
   TF_REQUIRE(tensor_path_error() == 0, "%s: an earlier tensor-core kernel timed out on a barrier; refusing to launch", what);
@@ -690,9 +744,9 @@ template <int BN> static int launch_gemm(const GemmParams& p, cudaStream_t s, do
   note_compute_stream(s);
   static const bool detail = getenv("TINYFLOW_TIMING_DETAIL") != nullptr;    // one timing row per distinct problem shape
   char name[160];
-  if (detail) snprintf(name, sizeof(name), "gemm3xtf32 mode%d M%d N%d kiters%d taps%d splits%d bn%d tiles%d %s", p.mode, p.M, p.N, p.k_iters, p.tap_tiles, p.splits, BN, tiles, what + 5);
-  KernelTimer kt(detail ? name : "gemm3xtf32_tcgen05", s, flops, 0, 1);
-  gemm3xtf32_kernel<BN><<<grid, kThreads, L::kTotal, s>>>(p);
+  if (detail) snprintf(name, sizeof(name), "gemm3xf16 mode%d M%d N%d kiters%d taps%d splits%d bn%d tiles%d %s", p.mode, p.M, p.N, p.k_iters, p.tap_tiles, p.splits, BN, tiles, what + 5);
+  KernelTimer kt(detail ? name : "gemm3xf16_tcgen05", s, flops, 0, 1);
+  gemm3xf16_kernel<BN><<<grid, kThreads, L::kTotal, s>>>(p);
   TF_AFTER(s, what);
   return 0;
 }
@@ -703,18 +757,26 @@ static inline int pick_bn(long long n) { return n <= 64 ? 64 : 128; }
 static inline long long round_up(long long a, long long b) { return (a + b - 1) / b * b; }
 
 struct Pack {           // a packed operand living in pooled device memory
-  float* hi = nullptr; float* lo = nullptr;
+  __half* hi = nullptr; __half* lo = nullptr;
+  uint32_t* words = nullptr;       // device: amax[0], amax[1] (alternating between uses), scale (float), spare
+  unsigned uses = 0;
   long long rows = 0, cols = 0, pitch = 0;
   const void* src = nullptr; uint64_t version = 0; int tag = 0;   // cache key
-  size_t bytes() const { return (size_t)rows * pitch * 4; }
+  size_t bytes() const { return (size_t)rows * pitch * 2; }
+  const float* scale() const { return reinterpret_cast<const float*>(words + 2); }
 };
-static int pack_alloc(Pack& pk, long long rows, long long cols, int* oom) {
-  long long pitch = round_up(cols, 32);
+static int pack_alloc(Pack& pk, long long rows, long long cols, cudaStream_t s, int* oom) {
+  long long pitch = round_up(cols, 64);
+  if (!pk.words) {
+    pk.words = (uint32_t*)pool_alloc(16);
+    if (!pk.words || cudaMemsetAsync(pk.words, 0, 16, s) != cudaSuccess) { if (oom) *oom = 16; return 1; }
+    pk.uses = 0;
+  }
   if (pk.hi && pk.rows == rows && pk.pitch == pitch) { pk.cols = cols; return 0; }
   if (pk.hi) { pool_free(pk.hi); pool_free(pk.lo); pk.hi = pk.lo = nullptr; }
   pk.rows = rows; pk.cols = cols; pk.pitch = pitch; pk.src = nullptr;
-  pk.hi = (float*)pool_alloc(pk.bytes());
-  pk.lo = pk.hi ? (float*)pool_alloc(pk.bytes()) : nullptr;
+  pk.hi = (__half*)pool_alloc(pk.bytes());
+  pk.lo = pk.hi ? (__half*)pool_alloc(pk.bytes()) : nullptr;
   if (!pk.lo) {
     if (pk.hi) pool_free(pk.hi);
     pk.hi = nullptr;
@@ -723,35 +785,48 @@ static int pack_alloc(Pack& pk, long long rows, long long cols, int* oom) {
   }
   return 0;
 }
-static void pack_release(Pack& pk) { if (pk.hi) { pool_free(pk.hi); pool_free(pk.lo); pk.hi = pk.lo = nullptr; } }
+static void pack_release(Pack& pk) {
+  if (pk.hi) { pool_free(pk.hi); pool_free(pk.lo); pk.hi = pk.lo = nullptr; }
+  if (pk.words) { pool_free(pk.words); pk.words = nullptr; }
+}
+// Starts one use of the pack: reduces max|src| over n contiguous floats into this use's amax word and returns the
+// references the pack kernel needs.  Several pack launches of the same use (stride phases) share one ScaleRef.
+static ScaleRef begin_pack(Pack& pk, const float* src, long long n, cudaStream_t s) {
+  const unsigned k = pk.uses++ & 1;
+  ScaleRef r{pk.words + k, pk.words + (k ^ 1), reinterpret_cast<float*>(pk.words + 2)};
+  KernelTimer kt("amax", s, 0, 4.0 * n);
+  amax_kernel<<<grid_for(n, 256, 16), 256, 0, s>>>(src, n, pk.words + k);
+  return r;
+}
 
 static int run_pack_matrix(const float* src, long long ld, Pack& pk, cudaStream_t s) {
   long long total = pk.rows * pk.cols;
-  KernelTimer kt("pack_matrix", s, 0, 12.0 * total);
-  pack_matrix_kernel<<<grid_for(total, 256, 4), 256, 0, s>>>(src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols);
+  ScaleRef sr = begin_pack(pk, src, total, s);          // callers pass ld == cols: the matrix is contiguous
+  KernelTimer kt("pack_matrix", s, 0, 8.0 * total);
+  pack_matrix_kernel<<<grid_for(total, 256, 4), 256, 0, s>>>(src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols, sr);
   TF_AFTER(s, "pack_matrix");
   return 0;
 }
 
 // ---- matmul ---------------------------------------------------------------------------------------
 int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_t M, int64_t N, int64_t K, cudaStream_t s, int* oom) {
-  if (M < 16 || N < 16 || K < 32 || (double)M * N * K < 4e6) return 0;      // launch-bound sizes stay on the CUDA cores
+  if (M < 16 || N < 16 || K < 64 || (double)M * N * K < 4e6) return 0;      // launch-bound sizes stay on the CUDA cores
   if (!encode_fn()) return 0;
   // A is stored [M][K] (K-major) or, transposed, [K][M] (M-major); B is stored [K][N] (N-major) or [N][K] (K-major)
   Pack pa, pb;
   long long a_rows = tA ? K : M, a_cols = tA ? M : K, b_rows = tB ? N : K, b_cols = tB ? K : N;
-  if (pack_alloc(pa, a_rows, a_cols, oom)) return 0;
-  if (pack_alloc(pb, b_rows, b_cols, oom)) { pack_release(pa); return 0; }
+  if (pack_alloc(pa, a_rows, a_cols, s, oom)) { pack_release(pa); return 0; }
+  if (pack_alloc(pb, b_rows, b_cols, s, oom)) { pack_release(pa); pack_release(pb); return 0; }
   int rc = run_pack_matrix(A, a_cols, pa, s);
   if (!rc) rc = run_pack_matrix(B, b_cols, pb, s);
   GemmParams p;
   memset(&p, 0, sizeof(p));
   const int bn = pick_bn(N);
   p.mode = kModeGemm; p.a_mn = tA ? 1 : 0; p.b_mn = tB ? 0 : 1; p.epi = kEpiRowMajor;
-  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_hi, pa.hi, pa.rows, pa.pitch, BM / 32) : make_map(&p.a_hi, pa.hi, pa.rows, pa.cols, pa.pitch, BM);
-  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_lo, pa.lo, pa.rows, pa.pitch, BM / 32) : make_map(&p.a_lo, pa.lo, pa.rows, pa.cols, pa.pitch, BM);
-  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_hi, pb.hi, pb.rows, pb.pitch, bn / 32) : make_map(&p.b_hi, pb.hi, pb.rows, pb.cols, pb.pitch, bn);
-  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_lo, pb.lo, pb.rows, pb.pitch, bn / 32) : make_map(&p.b_lo, pb.lo, pb.rows, pb.cols, pb.pitch, bn);
+  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_hi, pa.hi, pa.rows, pa.pitch, BM / 64) : make_map(&p.a_hi, pa.hi, pa.rows, pa.cols, pa.pitch, BM);
+  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_lo, pa.lo, pa.rows, pa.pitch, BM / 64) : make_map(&p.a_lo, pa.lo, pa.rows, pa.cols, pa.pitch, BM);
+  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_hi, pb.hi, pb.rows, pb.pitch, bn / 64) : make_map(&p.b_hi, pb.hi, pb.rows, pb.cols, pb.pitch, bn);
+  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_lo, pb.lo, pb.rows, pb.pitch, bn / 64) : make_map(&p.b_lo, pb.lo, pb.rows, pb.cols, pb.pitch, bn);
   if (!rc) {
     p.M = (int)M; p.N = (int)N;
     p.m_tiles = (int)((M + BM - 1) / BM); p.n_tiles = (int)((N + bn - 1) / bn); p.tap_tiles = 1;
@@ -764,6 +839,7 @@ int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_
     p.splits = (kit + p.k_iters - 1) / p.k_iters;
     p.atomic = p.splits > 1;
     p.out = C; p.ldc = N; p.err = error_word();
+    p.a_scale = pa.scale(); p.b_scale = pb.scale();
     if (p.atomic) { if (cudaMemsetAsync(C, 0, sizeof(float) * M * N, s) != cudaSuccess) rc = -1; }
     if (!rc) rc = launch_gemm_bn(bn, p, s, 2.0 * M * N * K, "DLGpuMatrixMultiply");
   }
@@ -777,7 +853,7 @@ int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_
 //   class B: stride 1, padding <= window - 1 on each axis, any window: frame = (H + R - 1) x (W + S - 1); x sits at
 //            offset (pad_h, pad_w), dy at (R - 1 - pad_h, S - 1 - pad_w), which gives each the zero halo its role
 //            needs (forward padding for x, "full" correlation for dy);
-//   class D: strided windows with C a multiple of 32: space-to-depth phases (see conv_state);
+//   class D: strided windows: space-to-depth phases (see conv_state);
 //   class C: too few input channels for a per-tap reduction chunk: x is expanded into patches (C*R*S columns) and
 //            the problem runs as class A over C*R*S channels; forward and filter gradient only.
 struct ConvTc {
@@ -785,6 +861,7 @@ struct ConvTc {
   int frame_h = 0, frame_w = 0;                          // frame geometry shared by the x and dy packs
   int x_off_h = 0, x_off_w = 0, dy_off_h = 0, dy_off_w = 0;
   int eC = 0, eR = 1, eS = 1;                            // reduction channels and window of the problem as the GEMM sees it
+  int cp = 0;                                            // class D: columns per stride phase (C rounded up to 64)
   Pack x, dy, wf, wd;
   std::mutex mu;
 };
@@ -799,11 +876,11 @@ static ConvTc* conv_state(ConvPlan* p) {
     } else if (ok && p->stride_h == 1 && p->stride_w == 1 && p->pad_h <= p->R - 1 && p->pad_w <= p->S - 1) {
       st->cls = 2; st->frame_h = p->H + p->R - 1; st->frame_w = p->W + p->S - 1;
       st->x_off_h = p->pad_h; st->x_off_w = p->pad_w; st->dy_off_h = p->R - 1 - p->pad_h; st->dy_off_w = p->S - 1 - p->pad_w;
-    } else if (ok && p->C % 32 == 0 && p->stride_h * p->stride_w <= 16 && p->pad_h <= p->R - 1 && p->pad_w <= p->S - 1 &&
-               (long long)p->stride_h * p->stride_w * p->C < 32768) {
+    } else if (ok && p->stride_h * p->stride_w <= 16 && p->pad_h <= p->R - 1 && p->pad_w <= p->S - 1 &&
+               (long long)p->stride_h * p->stride_w * round_up(p->C, 64) < 32768) {
       // strided window: x is split into stride_h*stride_w phases (space to depth), each tap reads one phase at a
       // stride-1 shift; dy sits behind a halo of (R-1)/stride_h, (S-1)/stride_w for the backward-data pass
-      st->cls = 4;
+      st->cls = 4; st->cp = (int)round_up(p->C, 64);
       st->dy_off_h = (p->R - 1) / p->stride_h; st->dy_off_w = (p->S - 1) / p->stride_w;
       int uh = (p->H - 1 + p->pad_h) / p->stride_h + 1, uw = (p->W - 1 + p->pad_w) / p->stride_w + 1;
       st->frame_h = (uh > p->P ? uh : p->P) + st->dy_off_h; st->frame_w = (uw > p->Q ? uw : p->Q) + st->dy_off_w;
@@ -819,16 +896,17 @@ static ConvTc* conv_state(ConvPlan* p) {
   return (ConvTc*)p->tc_state;
 }
 
-// One launch of the frame pack: `chans` channels of an NCHW tensor (spatial dims H x W) into columns dst_c0.. of pk
-static int launch_pack_nchw(Pack& pk, const float* src, int N, int chans, int H, int W, const ConvTc* st, int off_h, int off_w, int sh, int sw,
-                            int dst_c0, bool last, cudaStream_t s) {
-  PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, off_h, off_w, sh, sw, (int)pk.pitch, dst_c0, last ? (int)pk.pitch - dst_c0 : chans};
-  const int tc = chans > 64 ? 128 : chans > 32 ? 64 : 32;
-  dim3 grid((st->frame_w + 31) / 32, st->frame_h, N * ((chans + tc - 1) / tc));
-  KernelTimer kt("pack_nchw", s, 0, 12.0 * pk.rows * chans);
-  if (tc == 128) pack_nchw_kernel<128><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
-  else if (tc == 64) pack_nchw_kernel<64><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
-  else pack_nchw_kernel<32><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g);
+// One launch of the frame pack: `chans` channels of an NCHW tensor (spatial dims H x W) into columns dst_c0 .. dst_c0 + cover
+// of pk (zeros past `chans`)
+static int launch_pack_nchw(Pack& pk, const ScaleRef& sr, const float* src, int N, int chans, int H, int W, const ConvTc* st, int off_h, int off_w,
+                            int sh, int sw, int dst_c0, int cover, cudaStream_t s) {
+  PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, off_h, off_w, sh, sw, (int)pk.pitch, dst_c0, cover};
+  const int tc = cover > 64 ? 128 : cover > 32 ? 64 : 32;
+  dim3 grid((st->frame_w + 31) / 32, st->frame_h, N * ((cover + tc - 1) / tc));
+  KernelTimer kt("pack_nchw", s, 0, 4.0 * N * chans * H * W / (sh * sw) + 4.0 * pk.rows * cover);
+  if (tc == 128) pack_nchw_kernel<128><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g, sr);
+  else if (tc == 64) pack_nchw_kernel<64><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g, sr);
+  else pack_nchw_kernel<32><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g, sr);
   TF_AFTER(s, "pack_nchw");
   return 0;
 }
@@ -839,31 +917,35 @@ static bool pack_valid(const Pack& pk, const void* src, uint64_t ver, int tag, l
 static int pack_x(ConvTc* st, const ConvPlan* p, const float* x, cudaStream_t s, int* oom) {
   Pack& pk = st->x;
   const uint64_t ver = version_of(x);
+  const long long n_src = (long long)p->N * p->C * p->H * p->W;
   if (st->cls == 3) {
     long long rows = (long long)p->N * p->P * p->Q;
     if (pack_valid(pk, x, ver, 3, rows, st->eC)) return 0;
-    if (pack_alloc(pk, rows, st->eC, oom)) return 1;
+    if (pack_alloc(pk, rows, st->eC, s, oom)) return 1;
+    ScaleRef sr = begin_pack(pk, x, n_src, s);
     PatchGeom g{p->N, p->C, p->H, p->W, p->R, p->S, p->P, p->Q, p->stride_h, p->stride_w, p->pad_h, p->pad_w, st->eC, (int)pk.pitch};
-    KernelTimer kt("pack_patches", s, 0, 8.0 * rows * pk.pitch);
-    pack_patches_kernel<<<grid_for(rows * 32, 256, 4), 256, 0, s>>>(x, pk.hi, pk.lo, g);
+    KernelTimer kt("pack_patches", s, 0, 4.0 * rows * pk.pitch);
+    pack_patches_kernel<<<grid_for(rows * 32, 256, 4), 256, 0, s>>>(x, pk.hi, pk.lo, g, sr);
     TF_AFTER(s, "pack_patches");
     pk.src = x; pk.version = ver; pk.tag = 3;
     return 0;
   }
   const long long rows = (long long)p->N * st->frame_h * st->frame_w;
   const int phases = st->cls == 4 ? p->stride_h * p->stride_w : 1;
-  if (pack_valid(pk, x, ver, st->cls, rows, (long long)phases * p->C)) return 0;
-  if (pack_alloc(pk, rows, (long long)phases * p->C, oom)) return 1;
+  const long long cols = st->cls == 4 ? (long long)phases * st->cp : p->C;
+  if (pack_valid(pk, x, ver, st->cls, rows, cols)) return 0;
+  if (pack_alloc(pk, rows, cols, s, oom)) return 1;
+  ScaleRef sr = begin_pack(pk, x, n_src, s);
   int rc = 0;
   if (st->cls == 4) {
     // phase (a, b) holds x_padded(sh*u + a, sw*v + b) = x(sh*u + a - pad_h, sw*v + b - pad_w) at frame position (u, v)
     for (int a = 0; a < p->stride_h && !rc; ++a)
       for (int b = 0; b < p->stride_w && !rc; ++b) {
         int ph = a * p->stride_w + b;
-        rc = launch_pack_nchw(pk, x, p->N, p->C, p->H, p->W, st, p->pad_h - a, p->pad_w - b, p->stride_h, p->stride_w, ph * p->C, ph == phases - 1, s);
+        rc = launch_pack_nchw(pk, sr, x, p->N, p->C, p->H, p->W, st, p->pad_h - a, p->pad_w - b, p->stride_h, p->stride_w, ph * st->cp, st->cp, s);
       }
   } else {
-    rc = launch_pack_nchw(pk, x, p->N, p->C, p->H, p->W, st, st->x_off_h, st->x_off_w, p->stride_h, p->stride_w, 0, true, s);
+    rc = launch_pack_nchw(pk, sr, x, p->N, p->C, p->H, p->W, st, st->x_off_h, st->x_off_w, p->stride_h, p->stride_w, 0, (int)pk.pitch, s);
   }
   if (rc) return -1;
   pk.src = x; pk.version = ver; pk.tag = st->cls;
@@ -874,16 +956,18 @@ static int pack_dy(ConvTc* st, const ConvPlan* p, const float* dy, cudaStream_t 
   const uint64_t ver = version_of(dy);
   const long long rows = (long long)p->N * st->frame_h * st->frame_w;
   if (pack_valid(pk, dy, ver, 2, rows, p->K)) return 0;
-  if (pack_alloc(pk, rows, p->K, oom)) return 1;
-  if (launch_pack_nchw(pk, dy, p->N, p->K, p->P, p->Q, st, st->dy_off_h, st->dy_off_w, 1, 1, 0, true, s)) return -1;
+  if (pack_alloc(pk, rows, p->K, s, oom)) return 1;
+  ScaleRef sr = begin_pack(pk, dy, (long long)p->N * p->K * p->P * p->Q, s);
+  if (launch_pack_nchw(pk, sr, dy, p->N, p->K, p->P, p->Q, st, st->dy_off_h, st->dy_off_w, 1, 1, 0, (int)pk.pitch, s)) return -1;
   pk.src = dy; pk.version = ver; pk.tag = 2;
   return 0;
 }
 static int pack_filter(Pack& pk, const float* w, const ConvPlan* p, const ConvTc* st, int flip, cudaStream_t s, int* oom) {
-  int taps = st->eR * st->eS, rows = flip ? st->eC : p->K, inner = flip ? p->K : st->eC, inner_pad = (int)round_up(inner, 32);
-  if (pack_alloc(pk, rows, (long long)taps * inner_pad, oom)) return 1;
+  int taps = st->eR * st->eS, rows = flip ? st->eC : p->K, inner = flip ? p->K : st->eC, inner_pad = (int)round_up(inner, BK);
+  if (pack_alloc(pk, rows, (long long)taps * inner_pad, s, oom)) return 1;
+  ScaleRef sr = begin_pack(pk, w, (long long)p->K * p->C * p->R * p->S, s);
   long long total = (long long)rows * taps * inner_pad;
-  pack_filter_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, pk.hi, pk.lo, p->K, st->eC, st->eR, st->eS, flip, inner_pad);
+  pack_filter_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, pk.hi, pk.lo, p->K, st->eC, st->eR, st->eS, flip, inner_pad, sr);
   TF_AFTER(s, "pack_filter");
   return 0;
 }
@@ -924,7 +1008,7 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, c
   g.m_tiles = (int)((act.rows + BM - 1) / BM); g.n_tiles = (ch_out + bn - 1) / bn; g.tap_tiles = 1; g.splits = 1;
   g.ntaps = taps.n;
   g.chunks_per_tap = (ch_in + BK - 1) / BK;
-  g.b_tap_pitch = (int)round_up(ch_in, 32);
+  g.b_tap_pitch = (int)round_up(ch_in, BK);
   g.k_total = g.ntaps * g.chunks_per_tap;
   g.k_iters = g.k_total;
   {   // Split the reduction when the tile count quantises badly onto the SMs and the reduction is long enough.
@@ -937,6 +1021,7 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, c
   }
   for (int t = 0; t < taps.n; ++t) { g.tap_off[t] = taps.off[t]; g.tap_col[t] = (short)taps.col[t]; g.tap_b[t] = (short)taps.b[t]; }
   g.out = out; g.err = error_word();
+  g.a_scale = act.scale(); g.b_scale = filt.scale();
   g.frame_h = st->frame_h; g.frame_w = st->frame_w; g.valid_h = og.valid_h; g.valid_w = og.valid_w;
   g.out_c = ch_out; g.out_h = og.out_h; g.out_w = og.out_w; g.out_sh = og.out_sh; g.out_sw = og.out_sw; g.out_off_h = og.out_off_h; g.out_off_w = og.out_off_w;
   if (g.atomic && !out_is_zero) TF_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)p->N * ch_out * og.out_h * og.out_w, s));
@@ -953,7 +1038,7 @@ int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStrea
   TapList taps;
   for (int r = 0; r < st->eR; ++r)
     for (int q = 0; q < st->eS; ++q) {
-      if (st->cls == 4) taps.add((r / p->stride_h) * st->frame_w + q / p->stride_w, ((r % p->stride_h) * p->stride_w + q % p->stride_w) * p->C, r * st->eS + q);
+      if (st->cls == 4) taps.add((r / p->stride_h) * st->frame_w + q / p->stride_w, ((r % p->stride_h) * p->stride_w + q % p->stride_w) * st->cp, r * st->eS + q);
       else taps.add(r * st->frame_w + q, 0, r * st->eS + q);
     }
   OutGeom og{p->P, p->Q, p->P, p->Q, 1, 1, 0, 0};
@@ -1010,15 +1095,16 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
   const int bn = pick_bn(p->K);
   g.mode = kModeWgrad; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiWgrad; g.atomic = 1;
   g.M = st->eC; g.N = p->K; g.ntaps = st->eR * st->eS;
-  // Few input channels: several filter taps share one 128-row tile (slots of 32, 64 or 128 channels), so that the
-  // tensor core's M dimension is full and dy is read once for all of them.
-  g.slot = st->eC >= 128 ? BM : (int)round_up(st->eC, 32) == 96 ? BM : (int)round_up(st->eC, 32);
+  // Few input channels: two filter taps share one 128-row tile (slots of 64 channels), so that the tensor core's
+  // M dimension is full and dy is read once for both.
+  g.slot = st->eC > 64 ? BM : 64;
   g.taps_per_tile = BM / g.slot;
-  int rc = make_map_mn(&g.a_hi, st->x.hi, st->x.rows, st->x.pitch, g.slot / 32);
-  if (!rc) rc = make_map_mn(&g.a_lo, st->x.lo, st->x.rows, st->x.pitch, g.slot / 32);
-  if (!rc) rc = make_map_mn(&g.b_hi, st->dy.hi, st->dy.rows, st->dy.pitch, bn / 32);
-  if (!rc) rc = make_map_mn(&g.b_lo, st->dy.lo, st->dy.rows, st->dy.pitch, bn / 32);
+  int rc = make_map_mn(&g.a_hi, st->x.hi, st->x.rows, st->x.pitch, g.slot / 64);
+  if (!rc) rc = make_map_mn(&g.a_lo, st->x.lo, st->x.rows, st->x.pitch, g.slot / 64);
+  if (!rc) rc = make_map_mn(&g.b_hi, st->dy.hi, st->dy.rows, st->dy.pitch, bn / 64);
+  if (!rc) rc = make_map_mn(&g.b_lo, st->dy.lo, st->dy.rows, st->dy.pitch, bn / 64);
   if (rc) return -1;
+  g.a_scale = st->x.scale(); g.b_scale = st->dy.scale();
   g.m_tiles = (st->eC + g.slot - 1) / g.slot;
   g.tap_tiles = (g.ntaps + g.taps_per_tile - 1) / g.taps_per_tile;
   g.n_tiles = (p->K + bn - 1) / bn;
@@ -1029,7 +1115,7 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
       int t = r * st->eS + q;
       if (st->cls == 4) {
         g.tap_off[t] = (r / p->stride_h - st->dy_off_h) * st->frame_w + (q / p->stride_w - st->dy_off_w);
-        g.tap_col[t] = (short)(((r % p->stride_h) * p->stride_w + q % p->stride_w) * p->C);
+        g.tap_col[t] = (short)(((r % p->stride_h) * p->stride_w + q % p->stride_w) * st->cp);
       } else {
         g.tap_off[t] = (r - st->dy_off_h) * st->frame_w + (q - st->dy_off_w);
       }
