@@ -55,6 +55,34 @@ void note_write(const void* p);
 uint64_t version_of(const void* p);
 inline float* out_f32(DLArray* a) { note_write(a->data); return (float*)a->data; }
 
+// ---- largest magnitude of a tensor, tracked by its producer ---------------------------
+// The tensor path scales each operand by a power of two chosen from max|x|.  Kernels that write a whole tensor
+// can fold that maximum into their pass: the launcher asks for a pair of device words after bumping the write
+// version (amax_track_begin), the kernel ends with amax_commit(), and the consumer gets the word back through
+// amax_tracked() for as long as nobody else wrote the tensor.  The two words of a tensor alternate between
+// writes (the kernel of write k clears the word write k+1 will use), so no clearing launch is needed.
+struct AmaxOut { uint32_t* word = nullptr; uint32_t* clear = nullptr; };
+AmaxOut amax_track_begin(const void* data);
+const uint32_t* amax_tracked(const void* data);
+#ifdef __CUDACC__
+__device__ __forceinline__ uint32_t amax_bits(float v) { return __float_as_uint(fabsf(v)); }
+// Every thread of the block calls this once, after its last store, with the largest bit pattern it produced.
+__device__ __forceinline__ void amax_commit(const AmaxOut& am, uint32_t m) {
+  if (!am.word) return;                                  // uniform over the grid
+  __shared__ uint32_t amax_red[32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  m = __reduce_max_sync(0xffffffffu, m);
+  if (lane == 0) amax_red[w] = m;
+  __syncthreads();
+  if (w == 0) {
+    uint32_t t = lane < nw ? amax_red[lane] : 0u;
+    t = __reduce_max_sync(0xffffffffu, t);
+    if (lane == 0 && t) atomicMax(am.word, t);
+  }
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0 && am.clear) *am.clear = 0u;
+}
+#endif
+
 // ---- shapes -------------------------------------------------------------------
 inline int64_t numel(const DLArray* a) {
   int64_t n = 1;

@@ -43,15 +43,52 @@ namespace tf {
 static std::mutex g_ver_mu;
 static std::unordered_map<const void*, uint64_t> g_versions;
 static uint64_t g_ver_counter = 1;
+static uint64_t version_locked(const void* p) {
+  auto it = g_versions.find(p);
+  if (it == g_versions.end()) { g_versions[p] = ++g_ver_counter; return g_ver_counter; }
+  return it->second;
+}
 void note_write(const void* p) {
   std::lock_guard<std::mutex> lk(g_ver_mu);
   g_versions[p] = ++g_ver_counter;
 }
 uint64_t version_of(const void* p) {
   std::lock_guard<std::mutex> lk(g_ver_mu);
-  auto it = g_versions.find(p);
-  if (it == g_versions.end()) { g_versions[p] = ++g_ver_counter; return g_ver_counter; }
-  return it->second;
+  return version_locked(p);
+}
+
+// producer-tracked maxima: two device words per tensor, handed out from zero-filled chunks
+struct AmaxSlot { uint32_t* words = nullptr; unsigned uses = 0; uint64_t version = 0; int cur = 0; };
+static std::unordered_map<const void*, AmaxSlot> g_amax;
+static uint32_t* g_amax_chunk = nullptr;
+static int g_amax_left = 0;
+AmaxOut amax_track_begin(const void* data) {
+  std::lock_guard<std::mutex> lk(g_ver_mu);
+  AmaxSlot& sl = g_amax[data];
+  if (!sl.words) {
+    if (g_amax_left < 2) {
+      const int kWords = 16384;
+      uint32_t* chunk = nullptr;
+      if (cudaMalloc((void**)&chunk, kWords * sizeof(uint32_t)) != cudaSuccess || cudaMemset(chunk, 0, kWords * sizeof(uint32_t)) != cudaSuccess ||
+          cudaDeviceSynchronize() != cudaSuccess) {
+        cudaGetLastError();
+        g_amax.erase(data);
+        return AmaxOut{};
+      }
+      g_amax_chunk = chunk; g_amax_left = kWords;
+    }
+    sl.words = g_amax_chunk; g_amax_chunk += 2; g_amax_left -= 2;
+  }
+  const int k = (int)(sl.uses++ & 1u);
+  sl.cur = k;
+  sl.version = version_locked(data);
+  return AmaxOut{sl.words + k, sl.words + (k ^ 1)};
+}
+const uint32_t* amax_tracked(const void* data) {
+  std::lock_guard<std::mutex> lk(g_ver_mu);
+  auto it = g_amax.find(data);
+  if (it == g_amax.end() || !it->second.words) return nullptr;
+  return it->second.version == version_locked(data) ? it->second.words + it->second.cur : nullptr;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -486,13 +523,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
 __global__ void __launch_bounds__(256) amax_kernel(const float* __restrict__ src, long long n, uint32_t* __restrict__ amax) {
   uint32_t m = 0;
   const long long stride = (long long)gridDim.x * blockDim.x, tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  auto fold = [&](float4 v) {
+    m = max(max(m, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)), max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)))));
+  };
   if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
     const float4* s4 = reinterpret_cast<const float4*>(src);
-    for (long long i = tid; i < n / 4; i += stride) {
-      float4 v = __ldg(s4 + i);
-      m = max(max(m, __float_as_uint(fabsf(v.x))), max(__float_as_uint(fabsf(v.y)), max(__float_as_uint(fabsf(v.z)), __float_as_uint(fabsf(v.w)))));
+    const long long n4 = n / 4;
+    long long i = tid;
+    for (; i + 3 * stride < n4; i += 4 * stride) {       // four independent 16-byte loads in flight per thread
+      float4 a = __ldg(s4 + i), b = __ldg(s4 + i + stride), c = __ldg(s4 + i + 2 * stride), d = __ldg(s4 + i + 3 * stride);
+      fold(a); fold(b); fold(c); fold(d);
     }
-    for (long long i = (n / 4) * 4 + tid; i < n; i += stride) m = max(m, __float_as_uint(fabsf(__ldg(src + i))));
+    for (; i < n4; i += stride) fold(__ldg(s4 + i));
+    for (long long k = n4 * 4 + tid; k < n; k += stride) m = max(m, __float_as_uint(fabsf(__ldg(src + k))));
   } else {
     for (long long i = tid; i < n; i += stride) m = max(m, __float_as_uint(fabsf(__ldg(src + i))));
   }
@@ -545,19 +588,19 @@ __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restric
 struct PackGeom { int N, C, H, W, frame_h, frame_w, off_h, off_w, sh, sw, pitch, dst_c0, c_limit; };
 template <int TC>
 __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, __half* __restrict__ hi, __half* __restrict__ lo, PackGeom g, ScaleRef sr) {
-  // tile[c][j ^ (c / 8)]: the XOR keeps both phases free of bank conflicts (stores: 32 lanes = 32 pixels of one
-  // channel; loads: lanes = 8-channel groups of a few pixels that are TC/8 apart)
+  // tile[c][f ^ (c / 8)]: the XOR keeps both phases free of bank conflicts (stores: 32 lanes = 32 frame positions
+  // of one channel; loads: lanes = 8-channel groups of a few positions that are TC/8 apart)
   __shared__ float tile[TC][32];
-  const float sc = pack_scale(sr, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0);
+  const float sc = pack_scale(sr, blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0);
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
-  const int j0 = blockIdx.x * 32, i = blockIdx.y;
-  const int cblocks = (g.c_limit + TC - 1) / TC;         // blocks cover every column that has to be defined
-  const int n = blockIdx.z / cblocks, c0 = (blockIdx.z % cblocks) * TC;
-  const int si = i * g.sh - g.off_h;
-  const bool row_ok = si >= 0 && si < g.H;
+  const int fsize = g.frame_h * g.frame_w;
+  const int f0 = blockIdx.y * 32;                              // 32 consecutive frame positions (row-major over the frame)
+  const int cblocks = (g.c_limit + TC - 1) / TC;               // blocks cover every column that has to be defined
+  const int n = blockIdx.x / cblocks, c0 = (blockIdx.x % cblocks) * TC;
   {
-    const int j = j0 + tx, sj = j * g.sw - g.off_w;
-    const bool ok = row_ok && sj >= 0 && sj < g.W && j < g.frame_w;
+    const int f = f0 + tx, i = f / g.frame_w, j = f - i * g.frame_w;
+    const int si = i * g.sh - g.off_h, sj = j * g.sw - g.off_w;
+    const bool ok = f < fsize && si >= 0 && si < g.H && sj >= 0 && sj < g.W;
     const float* s = src + ((long long)n * g.C * g.H + (long long)si) * g.W + (long long)sj;
     const long long plane = (long long)g.H * g.W;
     float v[TC / 8];
@@ -578,13 +621,18 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
     constexpr int LPP = TC / 8;                       // lanes per pixel
     const int grp = tx % LPP, px = tx / LPP, cl = grp * 8, c = c0 + cl;
     for (int jb = ty; jb < LPP; jb += 8) {
-      const int jj = jb + px * LPP, j = j0 + jj;
-      if (j < g.frame_w && c < g.c_limit) {
-        __align__(16) __half h[8];
-        __align__(16) __half l[8];
+      const int ff = jb + px * LPP, f = f0 + ff;
+      if (f < fsize && c < g.c_limit) {
+        __align__(16) __half2 h[4];
+        __align__(16) __half2 l[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) split_f16(tile[cl + e][jj ^ grp], h[e], l[e]);
-        const long long o = (((long long)n * g.frame_h + i) * g.frame_w + j) * g.pitch + g.dst_c0 + c;
+        for (int e = 0; e < 4; ++e) {
+          const float a0 = tile[cl + 2 * e][ff ^ grp], a1 = tile[cl + 2 * e + 1][ff ^ grp];
+          h[e] = __floats2half2_rn(a0, a1);
+          const float2 hf = __half22float2(h[e]);
+          l[e] = __floats2half2_rn(a0 - hf.x, a1 - hf.y);
+        }
+        const long long o = ((long long)n * fsize + f) * g.pitch + g.dst_c0 + c;
         *reinterpret_cast<uint4*>(hi + o) = *reinterpret_cast<const uint4*>(h);
         *reinterpret_cast<uint4*>(lo + o) = *reinterpret_cast<const uint4*>(l);
       }
@@ -794,8 +842,13 @@ static void pack_release(Pack& pk) {
 static ScaleRef begin_pack(Pack& pk, const float* src, long long n, cudaStream_t s) {
   const unsigned k = pk.uses++ & 1;
   ScaleRef r{pk.words + k, pk.words + (k ^ 1), reinterpret_cast<float*>(pk.words + 2)};
+  static const bool no_track = getenv("TINYFLOW_NO_AMAX_TRACKING") != nullptr;
+  if (const uint32_t* tracked = no_track ? nullptr : amax_tracked(src)) {
+    r.amax_cur = tracked;               // the producer of src already reduced max|src| in its own pass
+    return r;
+  }
   KernelTimer kt("amax", s, 0, 4.0 * n);
-  amax_kernel<<<grid_for(n, 256, 16), 256, 0, s>>>(src, n, pk.words + k);
+  amax_kernel<<<grid_for(n, 256, 32), 256, 0, s>>>(src, n, pk.words + k);
   return r;
 }
 
@@ -902,7 +955,8 @@ static int launch_pack_nchw(Pack& pk, const ScaleRef& sr, const float* src, int 
                             int sh, int sw, int dst_c0, int cover, cudaStream_t s) {
   PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, off_h, off_w, sh, sw, (int)pk.pitch, dst_c0, cover};
   const int tc = cover > 64 ? 128 : cover > 32 ? 64 : 32;
-  dim3 grid((st->frame_w + 31) / 32, st->frame_h, N * ((cover + tc - 1) / tc));
+  dim3 grid(N * ((cover + tc - 1) / tc), (st->frame_h * st->frame_w + 31) / 32);
+  TF_REQUIRE(grid.y <= 65535, "pack: frame of %d x %d positions is too large", st->frame_h, st->frame_w);
   KernelTimer kt("pack_nchw", s, 0, 4.0 * N * chans * H * W / (sh * sw) + 4.0 * pk.rows * cover);
   if (tc == 128) pack_nchw_kernel<128><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g, sr);
   else if (tc == 64) pack_nchw_kernel<64><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g, sr);

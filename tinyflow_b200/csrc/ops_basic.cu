@@ -36,49 +36,61 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats *
 }
 
 // ---- generic vectorised map kernels ---------------------------------------------
-template <class F> __global__ void __launch_bounds__(kBlock) map1_kernel(const float* __restrict__ a, float* __restrict__ o, int64_t n, F f) {
+__device__ __forceinline__ uint32_t amax4(uint32_t m, const float4& r) {
+  return max(max(m, amax_bits(r.x)), max(amax_bits(r.y), max(amax_bits(r.z), amax_bits(r.w))));
+}
+template <class F> __global__ void __launch_bounds__(kBlock) map1_kernel(const float* __restrict__ a, float* __restrict__ o, int64_t n, F f, AmaxOut am) {
   int64_t nv = n >> 2, stride = (int64_t)gridDim.x * blockDim.x;
   const float4* a4 = reinterpret_cast<const float4*>(a);
   float4* o4 = reinterpret_cast<float4*>(o);
+  uint32_t m = 0;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
     float4 x = a4[i];
     x.x = f(x.x); x.y = f(x.y); x.z = f(x.z); x.w = f(x.w);
     o4[i] = x;
+    m = amax4(m, x);
   }
-  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = f(a[i]);
+  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { float r = f(a[i]); o[i] = r; m = max(m, amax_bits(r)); }
+  amax_commit(am, m);
 }
 template <class F> __global__ void __launch_bounds__(kBlock) map1_scalar_kernel(const float* a, float* o, int64_t n, F f) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = f(a[i]);
 }
-template <class F> __global__ void __launch_bounds__(kBlock) map2_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ o, int64_t n, F f) {
+template <class F> __global__ void __launch_bounds__(kBlock) map2_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ o, int64_t n, F f, AmaxOut am) {
   int64_t nv = n >> 2, stride = (int64_t)gridDim.x * blockDim.x;
   const float4* a4 = reinterpret_cast<const float4*>(a);
   const float4* b4 = reinterpret_cast<const float4*>(b);
   float4* o4 = reinterpret_cast<float4*>(o);
+  uint32_t m = 0;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
     float4 x = a4[i], y = b4[i], r;
     r.x = f(x.x, y.x); r.y = f(x.y, y.y); r.z = f(x.z, y.z); r.w = f(x.w, y.w);
     o4[i] = r;
+    m = amax4(m, r);
   }
-  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = f(a[i], b[i]);
+  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { float r = f(a[i], b[i]); o[i] = r; m = max(m, amax_bits(r)); }
+  amax_commit(am, m);
 }
 template <class F> __global__ void __launch_bounds__(kBlock) map2_scalar_kernel(const float* a, const float* b, float* o, int64_t n, F f) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = f(a[i], b[i]);
 }
-template <class F> __global__ void __launch_bounds__(kBlock) map3_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ c, float* __restrict__ o, int64_t n, F f) {
+template <class F> __global__ void __launch_bounds__(kBlock) map3_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ c, float* __restrict__ o, int64_t n, F f, AmaxOut am) {
   int64_t nv = n >> 2, stride = (int64_t)gridDim.x * blockDim.x;
   const float4* a4 = reinterpret_cast<const float4*>(a);
   const float4* b4 = reinterpret_cast<const float4*>(b);
   const float4* c4 = reinterpret_cast<const float4*>(c);
   float4* o4 = reinterpret_cast<float4*>(o);
+  uint32_t m = 0;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
     float4 x = a4[i], y = b4[i], z = c4[i], r;
     r.x = f(x.x, y.x, z.x); r.y = f(x.y, y.y, z.y); r.z = f(x.z, y.z, z.z); r.w = f(x.w, y.w, z.w);
     o4[i] = r;
+    m = amax4(m, r);
   }
-  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = f(a[i], b[i], c[i]);
+  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { float r = f(a[i], b[i], c[i]); o[i] = r; m = max(m, amax_bits(r)); }
+  amax_commit(am, m);
 }
 template <class F> __global__ void __launch_bounds__(kBlock) map3_scalar_kernel(const float* a, const float* b, const float* c, float* o, int64_t n, F f) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -89,7 +101,7 @@ template <class F> static int run_map1(const float* a, float* o, int64_t n, cuda
   if (n <= 0) return 0;
   note_compute_stream(s);
   KernelTimer kt(what, s, 0, 8.0 * n);
-  if (aligned16(a) && aligned16(o)) map1_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, o, n, f);
+  if (aligned16(a) && aligned16(o)) map1_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, o, n, f, amax_track_begin(o));
   else map1_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, o, n, f);
   TF_AFTER(s, what);
   return 0;
@@ -98,7 +110,7 @@ template <class F> static int run_map2(const float* a, const float* b, float* o,
   if (n <= 0) return 0;
   note_compute_stream(s);
   KernelTimer kt(what, s, 0, 12.0 * n);
-  if (aligned16(a) && aligned16(b) && aligned16(o)) map2_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, o, n, f);
+  if (aligned16(a) && aligned16(b) && aligned16(o)) map2_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, o, n, f, amax_track_begin(o));
   else map2_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, b, o, n, f);
   TF_AFTER(s, what);
   return 0;
@@ -107,7 +119,7 @@ template <class F> static int run_map3(const float* a, const float* b, const flo
   if (n <= 0) return 0;
   note_compute_stream(s);
   KernelTimer kt(what, s, 0, 16.0 * n);
-  if (aligned16(a) && aligned16(b) && aligned16(c) && aligned16(o)) map3_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, c, o, n, f);
+  if (aligned16(a) && aligned16(b) && aligned16(c) && aligned16(o)) map3_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, c, o, n, f, amax_track_begin(o));
   else map3_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, b, c, o, n, f);
   TF_AFTER(s, what);
   return 0;
@@ -301,17 +313,24 @@ template <int MODE> __global__ void __launch_bounds__(kBlock) loss_grad_kernel(c
 // slice of dst -> src (the backward split).  Rows are n, `inner` counts floats per sample.
 // One grid row (blockIdx.y) per sample, so no per-element divide; V = float4 when both inner sizes and the offset
 // are multiples of 4 floats, else float.
-template <int MODE, typename V> __global__ void __launch_bounds__(kBlock) slice_copy_kernel(V* __restrict__ part, V* __restrict__ whole, int64_t nrows, int64_t part_inner, int64_t whole_inner, int64_t off) {
+__device__ __forceinline__ uint32_t amax_of(const float4& v) { return amax4(0u, v); }
+__device__ __forceinline__ uint32_t amax_of(float v) { return amax_bits(v); }
+template <int MODE, typename V> __global__ void __launch_bounds__(kBlock) slice_copy_kernel(V* __restrict__ part, V* __restrict__ whole, int64_t nrows, int64_t part_inner, int64_t whole_inner, int64_t off, AmaxOut am) {
+  uint32_t m = 0;
   for (int64_t r = blockIdx.y; r < nrows; r += gridDim.y) {
     V* p = part + r * part_inner;
     V* w = whole + r * whole_inner + off;
     for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < part_inner; j += (int64_t)gridDim.x * blockDim.x) {
-      if (MODE == 0) w[j] = p[j];
-      else p[j] = w[j];
+      V v = MODE == 0 ? p[j] : w[j];
+      if (MODE == 0) w[j] = v; else p[j] = v;
+      m = max(m, amax_of(v));
     }
   }
+  amax_commit(am, m);
 }
-template <int MODE> static void launch_slice_copy(float* part, float* whole, int64_t rows, int64_t part_inner, int64_t whole_inner, int64_t off, cudaStream_t s) {
+// `am` accumulates max|copied values| for the written tensor; a tensor written by two launches (concat forward)
+// passes the clear word to the first launch only.
+template <int MODE> static void launch_slice_copy(float* part, float* whole, int64_t rows, int64_t part_inner, int64_t whole_inner, int64_t off, cudaStream_t s, AmaxOut am) {
   if (rows <= 0 || part_inner <= 0) return;
   bool vec = part_inner % 4 == 0 && whole_inner % 4 == 0 && off % 4 == 0 && ((uintptr_t)part % 16 == 0) && ((uintptr_t)whole % 16 == 0);
   int64_t per_row = vec ? part_inner / 4 : part_inner;
@@ -319,8 +338,8 @@ template <int MODE> static void launch_slice_copy(float* part, float* whole, int
   int64_t want = (per_row + kBlock - 1) / kBlock, cap = (int64_t)8 * 148 / gy + 1;
   int gx = (int)(want < cap ? want : cap);
   dim3 grid(gx < 1 ? 1 : gx, gy);
-  if (vec) slice_copy_kernel<MODE, float4><<<grid, kBlock, 0, s>>>((float4*)part, (float4*)whole, rows, part_inner / 4, whole_inner / 4, off / 4);
-  else slice_copy_kernel<MODE, float><<<grid, kBlock, 0, s>>>(part, whole, rows, part_inner, whole_inner, off);
+  if (vec) slice_copy_kernel<MODE, float4><<<grid, kBlock, 0, s>>>((float4*)part, (float4*)whole, rows, part_inner / 4, whole_inner / 4, off / 4, am);
+  else slice_copy_kernel<MODE, float><<<grid, kBlock, 0, s>>>(part, whole, rows, part_inner, whole_inner, off, am);
 }
 
 // ---- dropout: counter-based keep mask ---------------------------------------------------
@@ -733,8 +752,11 @@ int DLGpuConcatForward(const DLArrayHandle input1, const DLArrayHandle input2, D
   cudaStream_t s = stream_of(cudaStream);
   note_compute_stream(s);
   KernelTimer kt("DLGpuConcatForward", s, 0, 8.0 * rows * (ia + ib), 2);
-  launch_slice_copy<0>((float*)input1->data, FM(output), rows, ia, ia + ib, 0, s);
-  launch_slice_copy<0>((float*)input2->data, FM(output), rows, ib, ia + ib, ia, s);
+  float* whole = FM(output);
+  AmaxOut am = (rows > 0 && ia > 0 && ib > 0) ? amax_track_begin(whole) : AmaxOut{};
+  launch_slice_copy<0>((float*)input1->data, whole, rows, ia, ia + ib, 0, s, am);
+  am.clear = nullptr;
+  launch_slice_copy<0>((float*)input2->data, whole, rows, ib, ia + ib, ia, s, am);
   if (after_launch(s, "DLGpuConcatForward", 2) != 0) return -1;
   return 0;
 }
@@ -745,7 +767,8 @@ int DLGpuConcataBackward(const DLArrayHandle input1, const DLArrayHandle input2,
   cudaStream_t s = stream_of(cudaStream);
   note_compute_stream(s);
   KernelTimer kt("DLGpuConcatBackward", s, 0, 8.0 * rows * ia);
-  launch_slice_copy<1>(FM(dinput1), (float*)doutput->data, rows, ia, ia + ib, 0, s);
+  float* part = FM(dinput1);
+  launch_slice_copy<1>(part, (float*)doutput->data, rows, ia, ia + ib, 0, s, (rows > 0 && ia > 0) ? amax_track_begin(part) : AmaxOut{});
   TF_AFTER(s, "DLGpuConcataBackward");
   return 0;
 }
@@ -756,7 +779,8 @@ int DLGpuConcatbBackward(const DLArrayHandle input1, const DLArrayHandle input2,
   cudaStream_t s = stream_of(cudaStream);
   note_compute_stream(s);
   KernelTimer kt("DLGpuConcatBackward", s, 0, 8.0 * rows * ib);
-  launch_slice_copy<1>(FM(dinput2), (float*)doutput->data, rows, ib, ia + ib, ia, s);
+  float* part = FM(dinput2);
+  launch_slice_copy<1>(part, (float*)doutput->data, rows, ib, ia + ib, ia, s, (rows > 0 && ib > 0) ? amax_track_begin(part) : AmaxOut{});
   TF_AFTER(s, "DLGpuConcatbBackward");
   return 0;
 }

@@ -91,16 +91,20 @@ __device__ __forceinline__ int window_argmax(const float* __restrict__ plane, co
 }
 
 template <int KH, int KW>
-__global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ idx, int64_t total, PoolGeom g) {
+__global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ idx, int64_t total, PoolGeom g, AmaxOut am) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  uint32_t amax = 0;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     int64_t plane; int p, q;
     split_index(i, g.dPQ, g.dQ, plane, p, q);
     float v;
     int a = window_argmax<KH, KW>(x + plane * g.dHW.d, g, p, q, &v);
-    if (y) y[i] = a < 0 ? 0.f : v;
+    v = a < 0 ? 0.f : v;
+    if (y) y[i] = v;
     if (idx) idx[i] = a;
+    amax = max(amax, amax_bits(v));
   }
+  amax_commit(am, amax);
 }
 // Gather form of the max-pool gradient: each input element sums dy over the windows whose
 // first maximum it is.  No atomics, deterministic, dx fully written.
@@ -167,8 +171,9 @@ __global__ void __launch_bounds__(256) pool_bwd_gather_kernel(const int32_t* __r
   }
 }
 template <int KH, int KW>
-__global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t total, PoolGeom g) {
+__global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t total, PoolGeom g, AmaxOut am) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  uint32_t amax = 0;
   float inv = 1.f / (float)(g.kh * g.kw);
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     int64_t plane; int p, q;
@@ -198,7 +203,9 @@ __global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restric
       }
     }
     y[i] = acc * inv;
+    amax = max(amax, amax_bits(acc * inv));
   }
+  amax_commit(am, amax);
 }
 
 static PoolGeom geom_of(const PoolPlan* p) {
@@ -213,10 +220,11 @@ static PoolGeom geom_of(const PoolPlan* p) {
 static void launch_maxpool_fwd(const PoolPlan* p, const float* x, float* y, int32_t* idx, int64_t total, cudaStream_t s) {
   PoolGeom g = geom_of(p);
   int grid = grid_for(total, 256);
-  if (p->win_h == 3 && p->win_w == 3) maxpool_fwd_kernel<3, 3><<<grid, 256, 0, s>>>(x, y, idx, total, g);
-  else if (p->win_h == 2 && p->win_w == 2) maxpool_fwd_kernel<2, 2><<<grid, 256, 0, s>>>(x, y, idx, total, g);
-  else if (p->win_h == 1 && p->win_w == 1) maxpool_fwd_kernel<1, 1><<<grid, 256, 0, s>>>(x, y, idx, total, g);
-  else maxpool_fwd_kernel<0, 0><<<grid, 256, 0, s>>>(x, y, idx, total, g);
+  AmaxOut am = y ? amax_track_begin(y) : AmaxOut{};
+  if (p->win_h == 3 && p->win_w == 3) maxpool_fwd_kernel<3, 3><<<grid, 256, 0, s>>>(x, y, idx, total, g, am);
+  else if (p->win_h == 2 && p->win_w == 2) maxpool_fwd_kernel<2, 2><<<grid, 256, 0, s>>>(x, y, idx, total, g, am);
+  else if (p->win_h == 1 && p->win_w == 1) maxpool_fwd_kernel<1, 1><<<grid, 256, 0, s>>>(x, y, idx, total, g, am);
+  else maxpool_fwd_kernel<0, 0><<<grid, 256, 0, s>>>(x, y, idx, total, g, am);
 }
 template <bool MAXPOOL> static void launch_pool_gather(const PoolPlan* p, const int32_t* idx, const float* dy, float* dx, int64_t total, float scale, cudaStream_t s) {
   PoolGeom g = geom_of(p);
@@ -332,7 +340,7 @@ __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_fwd_regs_kernel(const fl
 }
 
 template <int VEC>
-__global__ void __launch_bounds__(32 * kBnGroups) bn_pa_bwd_regs_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, const float* __restrict__ save_mean, const float* __restrict__ save_inv, int N, int64_t F) {
+__global__ void __launch_bounds__(32 * kBnGroups) bn_pa_bwd_regs_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, const float* __restrict__ save_mean, const float* __restrict__ save_inv, int N, int64_t F, AmaxOut am) {
   using V = typename VecT<VEC>::type;
   __shared__ float red[kBnGroups][32][VEC];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -367,6 +375,7 @@ __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_bwd_regs_kernel(const fl
   bn_group_sum<VEC>(s1, red, tx, ty);
   bn_group_sum<VEC>(s2, red, tx, ty);
   const float rn = 1.f / (float)N;
+  uint32_t amax = 0;
 #pragma unroll
   for (int i = 0; i < kBnPerThread; ++i) {
     int n = ty + i * kBnGroups;
@@ -374,10 +383,11 @@ __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_bwd_regs_kernel(const fl
       V t;
       float* tp = reinterpret_cast<float*>(&t);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) tp[k] = inv[k] * (g[i][k] - s1[k] * rn - xh[i][k] * s2[k] * rn);
+      for (int k = 0; k < VEC; ++k) { tp[k] = inv[k] * (g[i][k] - s1[k] * rn - xh[i][k] * s2[k] * rn); amax = max(amax, amax_bits(tp[k])); }
       ov[(int64_t)n * FV + fv] = t;
     }
   }
+  amax_commit(am, amax);
 }
 
 // Any batch size: three passes over the batch column (the re-reads are served by L2).
@@ -444,8 +454,9 @@ static void launch_bn_fwd_regs(const float* x, float* y, float* sm, float* si, i
   else bn_pa_fwd_regs_kernel<1><<<(unsigned)((F + 31) / 32), 32 * kBnGroups, 0, s>>>(x, y, sm, si, N, F);
 }
 static void launch_bn_bwd_regs(const float* x, const float* dy, float* dx, const float* sm, const float* si, int N, int64_t F, cudaStream_t s) {
-  if (F % 4 == 0 && aligned16(x) && aligned16(dy) && aligned16(dx)) bn_pa_bwd_regs_kernel<4><<<(unsigned)((F / 4 + 31) / 32), 32 * kBnGroups, 0, s>>>(x, dy, dx, sm, si, N, F);
-  else bn_pa_bwd_regs_kernel<1><<<(unsigned)((F + 31) / 32), 32 * kBnGroups, 0, s>>>(x, dy, dx, sm, si, N, F);
+  AmaxOut am = amax_track_begin(dx);          // dx is the output gradient of the convolution in front of this layer
+  if (F % 4 == 0 && aligned16(x) && aligned16(dy) && aligned16(dx)) bn_pa_bwd_regs_kernel<4><<<(unsigned)((F / 4 + 31) / 32), 32 * kBnGroups, 0, s>>>(x, dy, dx, sm, si, N, F, am);
+  else bn_pa_bwd_regs_kernel<1><<<(unsigned)((F + 31) / 32), 32 * kBnGroups, 0, s>>>(x, dy, dx, sm, si, N, F, am);
 }
 
 }  // namespace tf
@@ -497,8 +508,12 @@ int DLGpuPooling2DForward(const DLArrayHandle input, DLArrayHandle output, void*
     p->argmax_src = input->data;
     p->argmax_version = version_of(input->data);
   }
-  else if (p->win_h == 3 && p->win_w == 3) avgpool_fwd_kernel<3, 3><<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), total, geom_of(p));
-  else avgpool_fwd_kernel<0, 0><<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, out_f32(output), total, geom_of(p));
+  else {
+    float* y = out_f32(output);
+    AmaxOut am = amax_track_begin(y);
+    if (p->win_h == 3 && p->win_w == 3) avgpool_fwd_kernel<3, 3><<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, y, total, geom_of(p), am);
+    else avgpool_fwd_kernel<0, 0><<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, y, total, geom_of(p), am);
+  }
   TF_AFTER(s, "DLGpuPooling2DForward");
   return 0;
 }
