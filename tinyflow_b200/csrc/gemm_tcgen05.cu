@@ -552,7 +552,7 @@ __device__ __forceinline__ float scale_from_amax(uint32_t bits) {
   if (bits == 0 || e == 0xff) return 1.f;             // all zero, or Inf/NaN inside (the results are meaningless then)
   if (e == 0) e = 1;
   int se = 14 - (e - 127);
-  se = se > 100 ? 100 : (se < -100 ? -100 : se);
+  se = se > 120 ? 120 : (se < -120 ? -120 : se);
   return __uint_as_float((uint32_t)(se + 127) << 23);
 }
 __device__ __forceinline__ float pack_scale(const ScaleRef& r, bool first_thread) {
