@@ -179,6 +179,71 @@ def test_matmul(env, M, K, N, tA, tB, path):
     close(C.asnumpy(), want, what="matmul %s" % ((M, K, N, tA, tB),))
 
 
+# ---- scaling of the fp16 hi/lo split ------------------------------------------------------------------------------
+@pytest.mark.parametrize("sa,sb", [(1.0, 1.0), (1e-20, 1e15), (3e18, 2e-30), (7e-12, 5e-9)])
+def test_matmul_tensor_path_is_scale_invariant(env, sa, sb):
+    """The tensor path rescales each operand by a power of two taken from its largest magnitude, so operands far
+    outside the fp16 range must give the same relative accuracy as O(1) ones."""
+    M, K, N = 256, 512, 192
+    A, B = (f32(M, K) * sa).astype(np.float32), (f32(K, N) * sb).astype(np.float32)
+    C = env.empty((M, N))
+    env.gpu_op.set_contraction_path(2)
+    try:
+        env.gpu_op.matrix_multiply(env.dev(A), False, env.dev(B), False, C, env.cublas, env.stream)
+    finally:
+        env.gpu_op.set_contraction_path(0)
+    close(C.asnumpy(), A.astype(np.float64) @ B.astype(np.float64), what="matmul scaled %g %g" % (sa, sb))
+
+
+def test_matmul_tensor_path_wide_dynamic_range(env):
+    """Magnitudes spread over 2^-10 .. 2^10 inside one operand: every element still carries 22 bits."""
+    M, K, N = 192, 1024, 256
+    A = (f32(M, K) * np.exp2(RNG.uniform(-10, 10, (M, K)))).astype(np.float32)
+    B = (f32(K, N) * np.exp2(RNG.uniform(-10, 10, (K, N)))).astype(np.float32)
+    C = env.empty((M, N))
+    env.gpu_op.set_contraction_path(2)
+    try:
+        env.gpu_op.matrix_multiply(env.dev(A), False, env.dev(B), False, C, env.cublas, env.stream)
+    finally:
+        env.gpu_op.set_contraction_path(0)
+    close(C.asnumpy(), A.astype(np.float64) @ B.astype(np.float64), what="matmul dynamic range")
+
+
+def test_all_zero_operand_gives_zero(env):
+    A, B = np.zeros((128, 256), np.float32), f32(256, 128)
+    C = env.empty((128, 128))
+    env.gpu_op.set_contraction_path(2)
+    try:
+        env.gpu_op.matrix_multiply(env.dev(A), False, env.dev(B), False, C, env.cublas, env.stream)
+    finally:
+        env.gpu_op.set_contraction_path(0)
+    assert not C.asnumpy().any()
+
+
+def test_tracked_maximum_is_dropped_when_the_tensor_is_overwritten(env):
+    """ReLU records max|y| for its output while it writes it.  Overwriting that array by a host upload with values
+    10^6 times larger must invalidate the recorded maximum: a stale one would overflow the fp16 split."""
+    N, C, H, W, K = 4, 32, 20, 20, 32
+    x_small = np.abs(f32(N, C, H, W)) * 1e-3
+    w = f32(K, C, 3, 3, scale=0.2)
+    g = env.ops.conv_geometry(x_small.shape, w.shape, "SAME", 1, 1)
+    out_shape, cell = env.gpu_op.convolution_2d_forward_get_out_shape(x_small.shape, w.shape, "NCHW", "SAME", 1, 1)
+    act = env.empty(x_small.shape)
+    y = env.empty(out_shape)
+    env.gpu_op.relu(env.dev(x_small), act)                      # tracked producer
+    wd = env.dev(w)
+    env.gpu_op.set_contraction_path(2)
+    try:
+        assert env.gpu_op.convolution_2d_forward(act, wd, y, cell, env.cudnn, env.stream) == 0
+        close(y.asnumpy(), env.ops.conv2d_fwd(x_small.astype(np.float64), w.astype(np.float64), g), what="conv on relu output")
+        x_big = f32(N, C, H, W) * 1e3
+        act._sync_copyfrom(x_big)
+        assert env.gpu_op.convolution_2d_forward(act, wd, y, cell, env.cudnn, env.stream) == 0
+        close(y.asnumpy(), env.ops.conv2d_fwd(x_big.astype(np.float64), w.astype(np.float64), g), what="conv after overwrite")
+    finally:
+        env.gpu_op.set_contraction_path(0)
+
+
 # ---- softmax family ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("rows,cols", [(1000, 10), (64, 1000), (3, 1), (257, 33)])
 def test_softmax_and_cross_entropy(env, rows, cols):
