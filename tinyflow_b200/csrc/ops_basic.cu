@@ -97,11 +97,17 @@ template <class F> __global__ void __launch_bounds__(kBlock) map3_scalar_kernel(
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = f(a[i], b[i], c[i]);
 }
 
+// Functors whose outputs become operands of the tensor path (activations, their gradients, weights) carry a
+// `kTrackAmax` member: only their launches reduce max|y| on the side.
+template <class F, class = void> struct TracksAmax { static constexpr bool value = false; };
+template <class F> struct TracksAmax<F, decltype((void)F::kTrackAmax)> { static constexpr bool value = F::kTrackAmax; };
+template <class F> static AmaxOut track_of(const float* out) { return TracksAmax<F>::value ? amax_track_begin(out) : AmaxOut{}; }
+
 template <class F> static int run_map1(const float* a, float* o, int64_t n, cudaStream_t s, const char* what, F f) {
   if (n <= 0) return 0;
   note_compute_stream(s);
   KernelTimer kt(what, s, 0, 8.0 * n);
-  if (aligned16(a) && aligned16(o)) map1_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, o, n, f, amax_track_begin(o));
+  if (aligned16(a) && aligned16(o)) map1_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, o, n, f, track_of<F>(o));
   else map1_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, o, n, f);
   TF_AFTER(s, what);
   return 0;
@@ -110,7 +116,7 @@ template <class F> static int run_map2(const float* a, const float* b, float* o,
   if (n <= 0) return 0;
   note_compute_stream(s);
   KernelTimer kt(what, s, 0, 12.0 * n);
-  if (aligned16(a) && aligned16(b) && aligned16(o)) map2_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, o, n, f, amax_track_begin(o));
+  if (aligned16(a) && aligned16(b) && aligned16(o)) map2_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, o, n, f, track_of<F>(o));
   else map2_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, b, o, n, f);
   TF_AFTER(s, what);
   return 0;
@@ -119,7 +125,7 @@ template <class F> static int run_map3(const float* a, const float* b, const flo
   if (n <= 0) return 0;
   note_compute_stream(s);
   KernelTimer kt(what, s, 0, 16.0 * n);
-  if (aligned16(a) && aligned16(b) && aligned16(c) && aligned16(o)) map3_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, c, o, n, f, amax_track_begin(o));
+  if (aligned16(a) && aligned16(b) && aligned16(c) && aligned16(o)) map3_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, c, o, n, f, track_of<F>(o));
   else map3_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, b, c, o, n, f);
   TF_AFTER(s, what);
   return 0;
@@ -128,7 +134,7 @@ template <class F> static int run_map3(const float* a, const float* b, const flo
 struct FSet { float v; __device__ float operator()(float) const { return v; } };
 struct FAddC { float c; __device__ float operator()(float x) const { return x + c; } };
 struct FMulC { float c; __device__ float operator()(float x) const { return x * c; } };
-struct FRelu { __device__ float operator()(float x) const { return x > 0.f ? x : (x != x ? x : 0.f); } };   // NaN propagates
+struct FRelu { static constexpr bool kTrackAmax = true; __device__ float operator()(float x) const { return x > 0.f ? x : (x != x ? x : 0.f); } };   // NaN propagates
 struct FExp { __device__ float operator()(float x) const { return expf(x); } };
 struct FLog { __device__ float operator()(float x) const { return logf(x); } };
 struct FRecip { __device__ float operator()(float x) const { return 1.f / x; } };
@@ -137,13 +143,13 @@ struct FSigmoid { __device__ float operator()(float x) const { return 1.f / (1.f
 struct FTanh { __device__ float operator()(float x) const { return tanhf(x); } };
 struct FAdd { __device__ float operator()(float a, float b) const { return a + b; } };
 struct FMul { __device__ float operator()(float a, float b) const { return a * b; } };
-struct FReluGrad { __device__ float operator()(float x, float g) const { return x > 0.f ? g : 0.f; } };
-struct FSgd { float lr; __device__ float operator()(float w, float g) const { return w - lr * g; } };
+struct FReluGrad { static constexpr bool kTrackAmax = true; __device__ float operator()(float x, float g) const { return x > 0.f ? g : 0.f; } };
+struct FSgd { static constexpr bool kTrackAmax = true; float lr; __device__ float operator()(float w, float g) const { return w - lr * g; } };
 struct FCross { float b; __device__ float operator()(float x, float y) const { return logf(x) * y * (-1.f) * b; } };
 struct FCrossBwd { float b; __device__ float operator()(float x, float y, float d) const { return y * (-1.f) * b * (1.0f / x) * d; } };
 struct FSigmoidBwd { __device__ float operator()(float y, float dy) const { return dy * y * (1.f - y); } };
 struct FTanhBwd { __device__ float operator()(float y, float dy) const { return dy * (1.f - y * y); } };
-struct FAdamStep { float c1, c2, e, lr; __device__ float operator()(float w, float m, float v) const { return w - lr * m / c1 / (sqrtf(v / c2) + e); } };
+struct FAdamStep { static constexpr bool kTrackAmax = true; float c1, c2, e, lr; __device__ float operator()(float w, float m, float v) const { return w - lr * m / c1 / (sqrtf(v / c2) + e); } };
 struct FBce { __device__ float operator()(float a, float b) const { return b * logf(a) + (1.f - b) * logf(1.f - a); } };
 
 // ---- broadcast --------------------------------------------------------------------

@@ -428,3 +428,10 @@ def launch_count() -> int:
 def set_contraction_path(path: int):
     """0 = automatic, 1 = CUDA-core kernels only, 2 = tcgen05 kernels only (error if a shape is not taken)."""
     check_call(_LIB.TfSetContractionPath(int(path)))
+
+
+def allocator_stats():
+    """(bytes handed out and not yet freed, bytes cached in the pools) of the device allocator."""
+    used, cached = ctypes.c_longlong(0), ctypes.c_longlong(0)
+    check_call(_LIB.TfAllocatorStats(ctypes.byref(used), ctypes.byref(cached)))
+    return used.value, cached.value
