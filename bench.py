@@ -184,6 +184,8 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--memory-plan", default="none", choices=["none", "vdnn-conv", "vdnn-all"],
+                    help="replay a swap/release plan (reference message format) during every step; not the headline configuration")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch override (profiling on a small case; not the headline configuration)")
     args = ap.parse_args()
     if args.warmup < 3:
@@ -219,7 +221,9 @@ def main():
 
     model, cfg = build_model(args.workload, batch=args.batch)
     model.set_dropout({"resnet50": 0.5, "vgg16": 0.5, "inceptionv3": 0.8}.get(args.workload, 0.0))
-    ex = ad.Executor(model.loss, model.y, cfg["lr"], None, None, None, optimizer="sgd")
+    import queue
+    control = queue.Queue()
+    ex = ad.Executor(model.loss, model.y, cfg["lr"], control, None, None, optimizer="sgd")
     ctx = ndarray.gpu(0)
     Xn, Yn = models.synthetic_batch(model, seed=1234, rank=rank, input_dist=cfg["dist"])
     params = model.init_params(seed=123)          # identical on every rank
@@ -253,8 +257,17 @@ def main():
         if world > 1:
             check_call(_LIB.TfDpFlush(ex.cudaStream))
 
-    for _ in range(args.warmup):
+    plan_info = None
+    for w in range(args.warmup):
+        if w == 1 and args.memory_plan != "none":          # shapes are known after the first step
+            from tinyflow_b200 import memory_plan
+            plan = memory_plan.vdnn_plan(ex, policy=args.memory_plan.split("-")[1])
+            plan_info = {"policy": args.memory_plan, "swapped_tensors": len(plan[0]) // 2, "released_tensors": len(plan[1]),
+                         "bytes_away_at_peak": int(memory_plan.check_plan(ex, plan))}
+            control.put(plan)
         loss, feed = step_resident(feed)
+    if args.memory_plan != "none" and plan_info is None:
+        raise SystemExit("--memory-plan needs --warmup >= 2")
     flush_dp()
     barrier()
     flops = step_flops(ex)
@@ -365,7 +378,8 @@ def main():
             "config": {"workload": "%s b%d/GPU %s fp32 fwd+bwd+SGD" % (args.workload, batch, "x".join(str(d) for d in model.input_shape[1:])),
                        "global_batch": world * batch, "parallelism": "dp%d" % world, "l2": "per-step working set (GBs of activations) exceeds the 126 MB L2",
                        "dropout": (model.dropout_nodes[0].dropout if model.dropout_nodes else 0.0), "device_ms_per_step": dev_ms / args.steps, "host_ms_per_step": wall_ms / args.steps,
-                       "algorithmic_tflop_per_step": flops / 1e12, "final_loss": final_loss},
+                       "algorithmic_tflop_per_step": flops / 1e12, "final_loss": final_loss, "memory_plan": plan_info,
+                       "passive_swap_ins": ex.passive_swap_in},
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(Xn.nbytes + Yn.nbytes), "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
             "clocks": clocks,

@@ -70,22 +70,23 @@ def swapadam(topoorder):
 
 
 class _SwapWorker(threading.Thread):
-    """Executes swap requests (index, to_gpu) for the executor on a side stream."""
+    """Executes swap requests (index, to_gpu) for the executor on a side stream, in the order they were
+    submitted.  A reader of a tensor that still has requests queued waits for them (``wait_for``): it must not pick
+    up the device array of a tensor whose swap-out is about to free it."""
 
     def __init__(self, executor):
         super().__init__(daemon=True)
         self.ex = executor
         self.q = queue.Queue()
         self.stream = None
-        self.idle = threading.Event()
-        self.idle.set()
+        self.cond = threading.Condition()
         self.pending = 0
-        self.lock = threading.Lock()
+        self.pending_for = {}          # tensor index -> queued or running requests
 
     def submit(self, wait_ms, index, to_gpu):
-        with self.lock:
+        with self.cond:
             self.pending += 1
-            self.idle.clear()
+            self.pending_for[index] = self.pending_for.get(index, 0) + 1
         self.q.put((wait_ms, index, to_gpu))
 
     def run(self):
@@ -100,13 +101,20 @@ class _SwapWorker(threading.Thread):
                     time.sleep(wait_ms / 1000.0)
                 self.ex._do_swap(index, to_gpu, self.stream)
             finally:
-                with self.lock:
+                with self.cond:
                     self.pending -= 1
-                    if self.pending == 0:
-                        self.idle.set()
+                    self.pending_for[index] -= 1
+                    self.cond.notify_all()
+
+    def wait_for(self, index):
+        with self.cond:
+            while self.pending_for.get(index, 0) > 0:
+                self.cond.wait()
 
     def drain(self):
-        self.idle.wait()
+        with self.cond:
+            while self.pending > 0:
+                self.cond.wait()
 
 
 class Executor(object):
@@ -223,14 +231,11 @@ class Executor(object):
 
     def _resident(self, n):
         """The GPU array of node ``n``, swapping it in on demand (the reference's passive swap-in)."""
+        if self._swap_worker is not None:
+            self._swap_worker.wait_for(n.index)      # a queued swap-out would free the array under the reader
         arr = self.values.get(n.index)
         if arr is not None:
             return arr
-        if self._swap_worker is not None:
-            self._swap_worker.drain()
-            arr = self.values.get(n.index)
-            if arr is not None:
-                return arr
         host = self.host_values.get(n.index)
         if host is None:
             raise RuntimeError("tensor of node %d (%s) is neither on the GPU nor swapped out" % (n.index, n.name))
