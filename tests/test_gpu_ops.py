@@ -160,7 +160,8 @@ def test_legacy_reductions(env):
 # ---- matmul: the three shapes the reference asserts (tests/test_gpu_op.py:103-131) plus odd ones ------------
 MATMUL = [(500, 700, 1000, False, False), (1000, 500, 2000, False, True), (1000, 500, 2000, True, True),
           (1000, 784, 256, False, False), (784, 1000, 256, True, False), (1000, 10, 100, False, True),
-          (64, 2048, 2048, False, False), (64, 2048, 1000, True, False), (3, 5, 7, False, False), (129, 65, 33, True, True)]
+          (64, 2048, 2048, False, False), (64, 2048, 1000, True, False), (3, 5, 7, False, False), (129, 65, 33, True, True),
+          (300, 512, 192, False, True), (257, 320, 160, True, True), (512, 256, 288, False, True)]
 
 
 @pytest.mark.parametrize("M,K,N,tA,tB", MATMUL)
@@ -334,6 +335,10 @@ CONV = [
     # few input channels: several taps share one tile of the filter-gradient GEMM
     (2, 16, 28, 28, 64, 3, 3, "SAME", 1, 1),
     (2, 48, 35, 35, 64, 5, 5, "SAME", 1, 1),
+    # output widths that take the 96-column tile
+    (2, 128, 17, 17, 160, 1, 7, "SAME", 1, 1),
+    (2, 64, 17, 17, 192, 1, 1, "VALID", 1, 1),
+    (2, 192, 9, 9, 288, 3, 3, "SAME", 1, 1),
     # strided windows: one frame per stride phase
     (2, 32, 35, 35, 64, 3, 3, "VALID", 2, 2),
     (2, 96, 17, 17, 96, 3, 3, "VALID", 2, 2),

@@ -217,7 +217,7 @@ struct alignas(64) GemmParams {
 };
 
 template <int BN> struct SmemLayout {
-  static constexpr int kStages = BN <= 64 ? 4 : 3;
+  static constexpr int kStages = BN <= 96 ? 4 : 3;
   static constexpr int kABytes = BM * BK * 2;           // 16 KiB
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
@@ -227,6 +227,7 @@ template <int BN> struct SmemLayout {
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_constant__ GemmParams p) {
+  constexpr int kTmemCols = 4 * BN <= 256 ? 256 : 512;      // two accumulators of 2*BN columns; the allocation is a power of two
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -247,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {   // TMEM: two accumulators of 2*BN fp32 columns each
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(4 * BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tcgen05_fence_before();
@@ -511,7 +512,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(4 * BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
 }
@@ -799,9 +800,16 @@ template <int BN> static int launch_gemm(const GemmParams& p, cudaStream_t s, do
   return 0;
 }
 static int launch_gemm_bn(int bn, const GemmParams& p, cudaStream_t s, double flops, const char* what) {
-  return bn == 64 ? launch_gemm<64>(p, s, flops, what) : launch_gemm<128>(p, s, flops, what);
+  return bn == 64 ? launch_gemm<64>(p, s, flops, what) : bn == 96 ? launch_gemm<96>(p, s, flops, what) : launch_gemm<128>(p, s, flops, what);
 }
-static inline int pick_bn(long long n) { return n <= 64 ? 64 : 128; }
+// N-tile width.  M/N-major B operands come in 64-column groups, so they take 64 or 128; K-major ones may also take
+// 96, which wastes less on widths such as 96, 160, 192 or 288.
+static inline int pick_bn(long long n, bool b_k_major = false) {
+  if (n <= 64) return 64;
+  if (!b_k_major) return 128;
+  long long w128 = (n + 127) / 128 * 128, w96 = (n + 95) / 96 * 96;
+  return w96 < w128 ? 96 : 128;
+}
 static inline long long round_up(long long a, long long b) { return (a + b - 1) / b * b; }
 
 struct Pack {           // a packed operand living in pooled device memory
@@ -874,7 +882,7 @@ int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_
   if (!rc) rc = run_pack_matrix(B, b_cols, pb, s);
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  const int bn = pick_bn(N);
+  const int bn = pick_bn(N, tB);
   p.mode = kModeGemm; p.a_mn = tA ? 1 : 0; p.b_mn = tB ? 0 : 1; p.epi = kEpiRowMajor;
   if (!rc) rc = p.a_mn ? make_map_mn(&p.a_hi, pa.hi, pa.rows, pa.pitch, BM / 64) : make_map(&p.a_hi, pa.hi, pa.rows, pa.cols, pa.pitch, BM);
   if (!rc) rc = p.a_mn ? make_map_mn(&p.a_lo, pa.lo, pa.rows, pa.pitch, BM / 64) : make_map(&p.a_lo, pa.lo, pa.rows, pa.cols, pa.pitch, BM);
@@ -1051,7 +1059,7 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, c
                      const OutGeom& og, bool out_is_zero, double flops, cudaStream_t s, const char* what) {
   GemmParams g;
   memset(&g, 0, sizeof(g));
-  const int bn = pick_bn(ch_out);
+  const int bn = pick_bn(ch_out, true);
   g.mode = kModeConv; g.epi = kEpiNchw;
   int rc = make_map(&g.a_hi, act.hi, act.rows, act.cols, act.pitch, BM);
   if (!rc) rc = make_map(&g.a_lo, act.lo, act.rows, act.cols, act.pitch, BM);
