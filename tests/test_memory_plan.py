@@ -68,6 +68,7 @@ def test_step_under_a_swap_and_release_plan_matches_the_plain_step(lib_path, opt
     from tests.test_gpu_models import _feed
 
     def one_step(with_plan):
+        base_used, _ = gpu_op.allocator_stats()          # whatever earlier tests of this process still hold
         model = models.inceptionv3(batch=4, image=75, classes=100)
         model.set_dropout(0.0)
         control = queue.Queue()
@@ -87,7 +88,7 @@ def test_step_under_a_swap_and_release_plan_matches_the_plain_step(lib_path, opt
         ex.synchronize()
         used, _cached = gpu_op.allocator_stats()
         out = {n.name: v.asnumpy() for n, v in nxt.items() if n in model.param_shapes}
-        return float(loss.asnumpy().ravel()[0]), out, used, ex.passive_swap_in, len(ex.host_values)
+        return float(loss.asnumpy().ravel()[0]), out, used - base_used, ex.passive_swap_in, len(ex.host_values)
 
     loss0, w0, used0, _p0, _h0 = one_step(False)
     loss1, w1, used1, passive, swapped = one_step(True)

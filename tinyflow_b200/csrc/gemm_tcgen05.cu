@@ -602,19 +602,26 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
     const int f = f0 + tx, i = f / g.frame_w, j = f - i * g.frame_w;
     const int si = i * g.sh - g.off_h, sj = j * g.sw - g.off_w;
     const bool ok = f < fsize && si >= 0 && si < g.H && sj >= 0 && sj < g.W;
-    const float* s = src + ((long long)n * g.C * g.H + (long long)si) * g.W + (long long)sj;
     const long long plane = (long long)g.H * g.W;
+    // one 64-bit address per thread, advanced by eight planes per load; the range checks are hoisted out of the
+    // unrolled loads (a block whose channels all exist and a thread whose position has a source take the plain path)
+    const float* sp = src + ((long long)n * g.C + c0 + ty) * plane + (long long)si * g.W + sj;
+    const long long step = 8 * plane;
+    const int avail = g.C - c0 - ty;                  // channels at or after this thread's first one
     float v[TC / 8];
+    if (ok && c0 + TC <= g.C) {
 #pragma unroll
-    for (int k = 0; k < TC / 8; ++k) {
-      const int c = c0 + ty + 8 * k;
-      v[k] = (ok && c < g.C) ? __ldg(s + c * plane) : 0.f;
-    }
+      for (int k = 0; k < TC / 8; ++k) { v[k] = __ldg(sp); sp += step; }
+    } else if (ok) {
 #pragma unroll
-    for (int k = 0; k < TC / 8; ++k) {
-      const int c = ty + 8 * k;
-      tile[c][tx ^ (c >> 3)] = v[k] * sc;
+      for (int k = 0; k < TC / 8; ++k) { v[k] = 8 * k < avail ? __ldg(sp) : 0.f; sp += step; }
+    } else {
+#pragma unroll
+      for (int k = 0; k < TC / 8; ++k) v[k] = 0.f;
     }
+    float* trow = &tile[ty][0];
+#pragma unroll
+    for (int k = 0; k < TC / 8; ++k) trow[k * 8 * 32 + (tx ^ k)] = v[k] * sc;       // channel ty + 8k, column tx ^ ((ty + 8k) >> 3)
   }
   __syncthreads();
   {
