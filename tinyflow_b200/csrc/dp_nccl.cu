@@ -104,9 +104,16 @@ __global__ void __launch_bounds__(256) dp_copy_kernel(const float* __restrict__ 
   long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = g[i];
 }
-__global__ void __launch_bounds__(256) dp_apply_kernel(float* __restrict__ w, const float* __restrict__ sum, long long n, float scale) {
+// w -= scale * sum, and max|w| of the result for the tensor path's operand scaling (the next forward pass packs w)
+__global__ void __launch_bounds__(256) dp_apply_kernel(float* __restrict__ w, const float* __restrict__ sum, long long n, float scale, AmaxOut am) {
   long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) w[i] -= scale * sum[i];
+  uint32_t m = 0;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float v = w[i] - scale * sum[i];
+    w[i] = v;
+    m = max(m, amax_bits(v));
+  }
+  amax_commit(am, m);
 }
 
 // Hands bucket b to the comm stream: all-reduce, apply every entry, mark applied.
@@ -117,8 +124,8 @@ static int send_bucket(Bucket& b, cudaStream_t compute) {
   TF_NCCL(g_nccl.AllReduce(b.buf, b.buf, (size_t)b.fill, ncclFloat32, ncclSum, g_dp.comm, g_dp.comm_stream));
   g_dp.bytes_reduced += b.fill * 4; g_dp.allreduces += 1;
   for (const Entry& e : b.entries) {
-    dp_apply_kernel<<<grid_for(e.count, 256, 4), 256, 0, g_dp.comm_stream>>>(e.w, b.buf + e.offset, e.count, e.lr / (float)g_dp.world);
     note_write(e.w);
+    dp_apply_kernel<<<grid_for(e.count, 256, 4), 256, 0, g_dp.comm_stream>>>(e.w, b.buf + e.offset, e.count, e.lr / (float)g_dp.world, amax_track_begin(e.w));
   }
   if (after_launch(g_dp.comm_stream, "dp_apply", (int)b.entries.size()) != 0) return -1;
   TF_CUDA(cudaEventRecord(b.applied, g_dp.comm_stream));
@@ -141,8 +148,8 @@ int dp_sgd_update(float* w, const float* g, int64_t n, float lr, cudaStream_t s)
     TF_CUDA(cudaStreamWaitEvent(g_dp.comm_stream, g_dp.ready, 0));
     TF_NCCL(g_nccl.AllReduce(g, (void*)g, (size_t)n, ncclFloat32, ncclSum, g_dp.comm, g_dp.comm_stream));
     g_dp.bytes_reduced += n * 4; g_dp.allreduces += 1;
-    dp_apply_kernel<<<grid_for(n, 256, 4), 256, 0, g_dp.comm_stream>>>(w, g, n, lr / (float)g_dp.world);
     note_write(w);
+    dp_apply_kernel<<<grid_for(n, 256, 4), 256, 0, g_dp.comm_stream>>>(w, g, n, lr / (float)g_dp.world, amax_track_begin(w));
     if (after_launch(g_dp.comm_stream, "dp_apply", 1) != 0) return -1;
     TF_CUDA(cudaEventRecord(g_dp.ready, g_dp.comm_stream));
     TF_CUDA(cudaStreamWaitEvent(s, g_dp.ready, 0));
