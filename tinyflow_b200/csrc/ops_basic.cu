@@ -36,6 +36,10 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats *
 }
 
 // ---- generic vectorised map kernels ---------------------------------------------
+// Functors whose outputs become operands of the tensor path (activations, their gradients, weights) carry a
+// `kTrackAmax` member: only their launches reduce max|y| on the side.
+template <class F, class = void> struct TracksAmax { static constexpr bool value = false; };
+template <class F> struct TracksAmax<F, decltype((void)F::kTrackAmax)> { static constexpr bool value = F::kTrackAmax; };
 __device__ __forceinline__ uint32_t amax4(uint32_t m, const float4& r) {
   return max(max(m, amax_bits(r.x)), max(amax_bits(r.y), max(amax_bits(r.z), amax_bits(r.w))));
 }
@@ -48,10 +52,10 @@ template <class F> __global__ void __launch_bounds__(kBlock) map1_kernel(const f
     float4 x = a4[i];
     x.x = f(x.x); x.y = f(x.y); x.z = f(x.z); x.w = f(x.w);
     o4[i] = x;
-    m = amax4(m, x);
+    if (TracksAmax<F>::value) m = amax4(m, x);
   }
-  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { float r = f(a[i]); o[i] = r; m = max(m, amax_bits(r)); }
-  amax_commit(am, m);
+  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { float r = f(a[i]); o[i] = r; if (TracksAmax<F>::value) m = max(m, amax_bits(r)); }
+  if (TracksAmax<F>::value) amax_commit(am, m);
 }
 template <class F> __global__ void __launch_bounds__(kBlock) map1_scalar_kernel(const float* a, float* o, int64_t n, F f) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -67,10 +71,10 @@ template <class F> __global__ void __launch_bounds__(kBlock) map2_kernel(const f
     float4 x = a4[i], y = b4[i], r;
     r.x = f(x.x, y.x); r.y = f(x.y, y.y); r.z = f(x.z, y.z); r.w = f(x.w, y.w);
     o4[i] = r;
-    m = amax4(m, r);
+    if (TracksAmax<F>::value) m = amax4(m, r);
   }
-  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { float r = f(a[i], b[i]); o[i] = r; m = max(m, amax_bits(r)); }
-  amax_commit(am, m);
+  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { float r = f(a[i], b[i]); o[i] = r; if (TracksAmax<F>::value) m = max(m, amax_bits(r)); }
+  if (TracksAmax<F>::value) amax_commit(am, m);
 }
 template <class F> __global__ void __launch_bounds__(kBlock) map2_scalar_kernel(const float* a, const float* b, float* o, int64_t n, F f) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -87,20 +91,16 @@ template <class F> __global__ void __launch_bounds__(kBlock) map3_kernel(const f
     float4 x = a4[i], y = b4[i], z = c4[i], r;
     r.x = f(x.x, y.x, z.x); r.y = f(x.y, y.y, z.y); r.z = f(x.z, y.z, z.z); r.w = f(x.w, y.w, z.w);
     o4[i] = r;
-    m = amax4(m, r);
+    if (TracksAmax<F>::value) m = amax4(m, r);
   }
-  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { float r = f(a[i], b[i], c[i]); o[i] = r; m = max(m, amax_bits(r)); }
-  amax_commit(am, m);
+  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) { float r = f(a[i], b[i], c[i]); o[i] = r; if (TracksAmax<F>::value) m = max(m, amax_bits(r)); }
+  if (TracksAmax<F>::value) amax_commit(am, m);
 }
 template <class F> __global__ void __launch_bounds__(kBlock) map3_scalar_kernel(const float* a, const float* b, const float* c, float* o, int64_t n, F f) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = f(a[i], b[i], c[i]);
 }
 
-// Functors whose outputs become operands of the tensor path (activations, their gradients, weights) carry a
-// `kTrackAmax` member: only their launches reduce max|y| on the side.
-template <class F, class = void> struct TracksAmax { static constexpr bool value = false; };
-template <class F> struct TracksAmax<F, decltype((void)F::kTrackAmax)> { static constexpr bool value = F::kTrackAmax; };
 template <class F> static AmaxOut track_of(const float* out) { return TracksAmax<F>::value ? amax_track_begin(out) : AmaxOut{}; }
 
 template <class F> static int run_map1(const float* a, float* o, int64_t n, cudaStream_t s, const char* what, F f) {
