@@ -353,7 +353,8 @@ def main():
             ach = top["flops"] / (top["ms"] / 1000.0) / 1e12
             roofline = {"bound": "tensor", "kernel": top["name"], "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
                         "traffic": None, "launches": top["launches"], "avg_us": 1000.0 * top["ms"] / max(top["launches"], 1),
-                        "peak_source": "%s bf16 sustained (fp16 inputs run at the same rate); algorithmic flops, issued tensor flops are 3x" % peak_kind,
+                        "issued": 3.0 * ach, "issued_frac": 3.0 * ach / peak,
+                        "peak_source": "%s bf16 sustained (fp16 inputs run at the same rate); achieved/frac count algorithmic flops, issued/issued_frac the three fp16 products 3xFP16 spends per multiply-add (what the tensor-pipe counter sees)" % peak_kind,
                         "share_of_timed_kernels": top["ms"] / total_ms if total_ms else None}
         else:
             peak = peaks["hbm_gbs"]
