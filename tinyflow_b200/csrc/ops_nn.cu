@@ -57,23 +57,24 @@ __device__ __forceinline__ int window_argmax(const float* __restrict__ plane, co
   int best = -1;
   float bv = 0.f;
   if (KH > 0) {
+    // row / column validity once per window (KH + KW range checks instead of 4 per tap), one base pointer, constant offsets
+    bool rv[KH > 0 ? KH : 1], cv[KW > 0 ? KW : 1];
+#pragma unroll
+    for (int r = 0; r < KH; ++r) rv[r] = (unsigned)(h0 + r) < (unsigned)g.H;
+#pragma unroll
+    for (int s = 0; s < KW; ++s) cv[s] = (unsigned)(w0 + s) < (unsigned)g.W;
+    const int o0 = h0 * g.W + w0;
+    const float* p0 = plane + o0;
     float v[KH > 0 ? KH * KW : 1];
 #pragma unroll
     for (int r = 0; r < KH; ++r)
 #pragma unroll
-      for (int s = 0; s < KW; ++s) {
-        int h = h0 + r, w = w0 + s;
-        bool ok = h >= 0 && h < g.H && w >= 0 && w < g.W;
-        v[r * KW + s] = ok ? __ldg(plane + h * g.W + w) : 0.f;
-      }
+      for (int s = 0; s < KW; ++s) v[r * KW + s] = (rv[r] && cv[s]) ? __ldg(p0 + r * g.W + s) : 0.f;
 #pragma unroll
     for (int r = 0; r < KH; ++r)
 #pragma unroll
-      for (int s = 0; s < KW; ++s) {
-        int h = h0 + r, w = w0 + s;
-        bool ok = h >= 0 && h < g.H && w >= 0 && w < g.W;
-        if (ok && (best < 0 || v[r * KW + s] > bv)) { best = h * g.W + w; bv = v[r * KW + s]; }
-      }
+      for (int s = 0; s < KW; ++s)
+        if (rv[r] && cv[s] && (best < 0 || v[r * KW + s] > bv)) { best = o0 + r * g.W + s; bv = v[r * KW + s]; }
   } else {
     for (int r = 0; r < g.kh; ++r) {
       int h = h0 + r;
@@ -147,15 +148,19 @@ __global__ void __launch_bounds__(256) pool_bwd_gather_kernel(const int32_t* __r
     if (NP > 0) {
       float v[NP > 0 ? NP * NQ : 1];
       int id[NP > 0 ? NP * NQ : 1];
+      bool pv[NP > 0 ? NP : 1], qv[NQ > 0 ? NQ : 1];
+#pragma unroll
+      for (int a = 0; a < NP; ++a) pv[a] = p_lo + a <= p_hi;
+#pragma unroll
+      for (int b = 0; b < NQ; ++b) qv[b] = q_lo + b <= q_hi;
+      const int o0 = p_lo * g.Q + q_lo;
 #pragma unroll
       for (int a = 0; a < NP; ++a)
 #pragma unroll
         for (int b = 0; b < NQ; ++b) {
-          int p = p_lo + a, q = q_lo + b;
-          bool ok = p <= p_hi && q <= q_hi;
-          int o = ok ? p * g.Q + q : 0;
-          v[a * NQ + b] = ok ? __ldg(dp + o) : 0.f;
-          id[a * NQ + b] = MAXPOOL ? (ok ? __ldg(ip + o) : -1) : hw;
+          const bool ok = pv[a] && qv[b];
+          v[a * NQ + b] = ok ? __ldg(dp + o0 + a * g.Q + b) : 0.f;
+          id[a * NQ + b] = MAXPOOL ? (ok ? __ldg(ip + o0 + a * g.Q + b) : -1) : hw;
         }
 #pragma unroll
       for (int k = 0; k < NP * NQ; ++k) acc += id[k] == hw ? v[k] : 0.f;
@@ -182,14 +187,17 @@ __global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restric
     int h0 = p * g.sh - g.ph, w0 = q * g.sw - g.pw;
     float acc = 0.f;
     if (KH > 0) {
+      bool rv[KH > 0 ? KH : 1], cv[KW > 0 ? KW : 1];
+#pragma unroll
+      for (int r = 0; r < KH; ++r) rv[r] = (unsigned)(h0 + r) < (unsigned)g.H;
+#pragma unroll
+      for (int s = 0; s < KW; ++s) cv[s] = (unsigned)(w0 + s) < (unsigned)g.W;
+      const float* p0 = xp + h0 * g.W + w0;
       float v[KH > 0 ? KH * KW : 1];
 #pragma unroll
       for (int r = 0; r < KH; ++r)
 #pragma unroll
-        for (int s = 0; s < KW; ++s) {
-          int h = h0 + r, w = w0 + s;
-          v[r * KW + s] = (h >= 0 && h < g.H && w >= 0 && w < g.W) ? __ldg(xp + h * g.W + w) : 0.f;
-        }
+        for (int s = 0; s < KW; ++s) v[r * KW + s] = (rv[r] && cv[s]) ? __ldg(p0 + r * g.W + s) : 0.f;
 #pragma unroll
       for (int k = 0; k < KH * KW; ++k) acc += v[k];
     } else {
