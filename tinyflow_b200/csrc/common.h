@@ -117,6 +117,31 @@ inline int grid_for(int64_t work_items, int block, int per_thread = 1, int waves
   return (int)need;
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A kernel launched through launch_dep() may be scheduled while the kernel in front of it on the stream is still
+// draining; its first statement has to be grid_dep_sync(), which blocks until that kernel has completed and its
+// writes are visible, and then lets the kernel behind start the same way.  Removes the launch gap between the
+// ~700 short kernels of a step; a kernel launched with <<<>>> serialises as usual.
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dep_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <class... Params, class... Args>
+inline cudaError_t launch_dep(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  static const bool off = getenv("TINYFLOW_NO_DEPENDENT_LAUNCH") != nullptr;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute attr;
+  memset(&attr, 0, sizeof(attr));
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &attr; cfg.numAttrs = off ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
+}
+#endif
+
 // ---- plan structs stored in slot 0 of a descriptor list ----------------------
 enum PlanKind : int { kPlanConv = 0x7f01, kPlanPool, kPlanAct, kPlanReduce, kPlanBN, kPlanTensor, kPlanDropout };
 

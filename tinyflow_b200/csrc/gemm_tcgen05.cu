@@ -255,6 +255,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  grid_dep_sync();          // everything above (barriers, TMEM) overlapped the tail of the kernel in front; operands are read below
 
   // tile index -> coordinates; n fastest so consecutive CTAs share the A tile through L2
   auto kcount_of = [&](int split) { return min(p.k_iters, p.k_total - split * p.k_iters); };
@@ -522,6 +523,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
 // ------------------------------------------------------------------------------------------------
 // Largest magnitude of a tensor, as the bit pattern of a non-negative float (unsigned order = float order).
 __global__ void __launch_bounds__(256) amax_kernel(const float* __restrict__ src, long long n, uint32_t* __restrict__ amax) {
+  grid_dep_sync();
   uint32_t m = 0;
   const long long stride = (long long)gridDim.x * blockDim.x, tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   auto fold = [&](float4 v) {
@@ -569,6 +571,7 @@ __device__ __forceinline__ void split_f16(float a, __half& hi, __half& lo) {
 // rows x cols row-major (pitch src_ld) -> hi/lo with pitch dst_ld
 __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restrict__ src, long long src_ld, __half* __restrict__ hi, __half* __restrict__ lo,
                                                           long long dst_ld, long long rows, long long cols, ScaleRef sr) {
+  grid_dep_sync();
   const float sc = pack_scale(sr, blockIdx.x == 0 && threadIdx.x == 0);
   long long total = rows * cols, stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -589,6 +592,7 @@ __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restric
 struct PackGeom { int N, C, H, W, frame_h, frame_w, off_h, off_w, sh, sw, pitch, dst_c0, c_limit; };
 template <int TC>
 __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, __half* __restrict__ hi, __half* __restrict__ lo, PackGeom g, ScaleRef sr) {
+  grid_dep_sync();
   // tile[c][f ^ (c / 8)]: the XOR keeps both phases free of bank conflicts (stores: 32 lanes = 32 frame positions
   // of one channel; loads: lanes = 8-channel groups of a few positions that are TC/8 apart)
   __shared__ float tile[TC][32];
@@ -653,6 +657,7 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
 // channel count is too small to fill a 64-wide reduction chunk per tap (first layers, C = 3).
 struct PatchGeom { int N, C, H, W, R, S, P, Q, sh, sw, pad_h, pad_w, cols, pitch; };
 __global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restrict__ src, __half* __restrict__ hi, __half* __restrict__ lo, PatchGeom g, ScaleRef sr) {
+  grid_dep_sync();
   // column -> (source offset relative to the window origin, r, s), the same for every row
   __shared__ int col_off[1024];
   __shared__ short col_r[1024], col_s[1024];
@@ -697,6 +702,7 @@ __global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restri
 // tap' = (R-1-r)*S + (S-1-s)), zero in the channel padding.
 __global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restrict__ w, __half* __restrict__ hi, __half* __restrict__ lo,
                                                           int K, int C, int R, int S, int flip, int inner_pad, ScaleRef sr) {
+  grid_dep_sync();
   const float sc = pack_scale(sr, blockIdx.x == 0 && threadIdx.x == 0);
   int taps = R * S;
   long long rows = flip ? C : K, total = rows * taps * inner_pad, stride = (long long)gridDim.x * blockDim.x;
@@ -802,7 +808,7 @@ template <int BN> static int launch_gemm(const GemmParams& p, cudaStream_t s, do
   char name[160];
   if (detail) snprintf(name, sizeof(name), "gemm3xf16 mode%d M%d N%d kiters%d taps%d splits%d bn%d tiles%d %s", p.mode, p.M, p.N, p.k_iters, p.tap_tiles, p.splits, BN, tiles, what + 5);
   KernelTimer kt(detail ? name : "gemm3xf16_tcgen05", s, flops, 0, 1);
-  gemm3xf16_kernel<BN><<<grid, kThreads, L::kTotal, s>>>(p);
+  launch_dep(gemm3xf16_kernel<BN>, dim3(grid), dim3(kThreads), (size_t)L::kTotal, s, p);
   TF_AFTER(s, what);
   return 0;
 }
@@ -863,7 +869,7 @@ static ScaleRef begin_pack(Pack& pk, const float* src, long long n, cudaStream_t
     return r;
   }
   KernelTimer kt("amax", s, 0, 4.0 * n);
-  amax_kernel<<<grid_for(n, 256, 32), 256, 0, s>>>(src, n, pk.words + k);
+  launch_dep(amax_kernel, dim3(grid_for(n, 256, 32)), dim3(256), 0, s, src, n, pk.words + k);
   return r;
 }
 
@@ -871,7 +877,7 @@ static int run_pack_matrix(const float* src, long long ld, Pack& pk, cudaStream_
   long long total = pk.rows * pk.cols;
   ScaleRef sr = begin_pack(pk, src, total, s);          // callers pass ld == cols: the matrix is contiguous
   KernelTimer kt("pack_matrix", s, 0, 8.0 * total);
-  pack_matrix_kernel<<<grid_for(total, 256, 4), 256, 0, s>>>(src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols, sr);
+  launch_dep(pack_matrix_kernel, dim3(grid_for(total, 256, 4)), dim3(256), 0, s, src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols, sr);
   TF_AFTER(s, "pack_matrix");
   return 0;
 }
@@ -973,9 +979,9 @@ static int launch_pack_nchw(Pack& pk, const ScaleRef& sr, const float* src, int 
   dim3 grid(N * ((cover + tc - 1) / tc), (st->frame_h * st->frame_w + 31) / 32);
   TF_REQUIRE(grid.y <= 65535, "pack: frame of %d x %d positions is too large", st->frame_h, st->frame_w);
   KernelTimer kt("pack_nchw", s, 0, 4.0 * N * chans * H * W / (sh * sw) + 4.0 * pk.rows * cover);
-  if (tc == 128) pack_nchw_kernel<128><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g, sr);
-  else if (tc == 64) pack_nchw_kernel<64><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g, sr);
-  else pack_nchw_kernel<32><<<grid, 256, 0, s>>>(src, pk.hi, pk.lo, g, sr);
+  if (tc == 128) launch_dep(pack_nchw_kernel<128>, grid, dim3(256), 0, s, src, pk.hi, pk.lo, g, sr);
+  else if (tc == 64) launch_dep(pack_nchw_kernel<64>, grid, dim3(256), 0, s, src, pk.hi, pk.lo, g, sr);
+  else launch_dep(pack_nchw_kernel<32>, grid, dim3(256), 0, s, src, pk.hi, pk.lo, g, sr);
   TF_AFTER(s, "pack_nchw");
   return 0;
 }
@@ -994,7 +1000,7 @@ static int pack_x(ConvTc* st, const ConvPlan* p, const float* x, cudaStream_t s,
     ScaleRef sr = begin_pack(pk, x, n_src, s);
     PatchGeom g{p->N, p->C, p->H, p->W, p->R, p->S, p->P, p->Q, p->stride_h, p->stride_w, p->pad_h, p->pad_w, st->eC, (int)pk.pitch};
     KernelTimer kt("pack_patches", s, 0, 4.0 * rows * pk.pitch);
-    pack_patches_kernel<<<grid_for(rows * 32, 256, 4), 256, 0, s>>>(x, pk.hi, pk.lo, g, sr);
+    launch_dep(pack_patches_kernel, dim3(grid_for(rows * 32, 256, 4)), dim3(256), 0, s, x, pk.hi, pk.lo, g, sr);
     TF_AFTER(s, "pack_patches");
     pk.src = x; pk.version = ver; pk.tag = 3;
     return 0;
@@ -1036,7 +1042,7 @@ static int pack_filter(Pack& pk, const float* w, const ConvPlan* p, const ConvTc
   if (pack_alloc(pk, rows, (long long)taps * inner_pad, s, oom)) return 1;
   ScaleRef sr = begin_pack(pk, w, (long long)p->K * p->C * p->R * p->S, s);
   long long total = (long long)rows * taps * inner_pad;
-  pack_filter_kernel<<<grid_for(total, 256), 256, 0, s>>>(w, pk.hi, pk.lo, p->K, st->eC, st->eR, st->eS, flip, inner_pad, sr);
+  launch_dep(pack_filter_kernel, dim3(grid_for(total, 256)), dim3(256), 0, s, w, pk.hi, pk.lo, p->K, st->eC, st->eR, st->eS, flip, inner_pad, sr);
   TF_AFTER(s, "pack_filter");
   return 0;
 }

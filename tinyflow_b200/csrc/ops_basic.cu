@@ -44,6 +44,7 @@ __device__ __forceinline__ uint32_t amax4(uint32_t m, const float4& r) {
   return max(max(m, amax_bits(r.x)), max(amax_bits(r.y), max(amax_bits(r.z), amax_bits(r.w))));
 }
 template <class F> __global__ void __launch_bounds__(kBlock) map1_kernel(const float* __restrict__ a, float* __restrict__ o, int64_t n, F f, AmaxOut am) {
+  grid_dep_sync();
   int64_t nv = n >> 2, stride = (int64_t)gridDim.x * blockDim.x;
   const float4* a4 = reinterpret_cast<const float4*>(a);
   float4* o4 = reinterpret_cast<float4*>(o);
@@ -62,6 +63,7 @@ template <class F> __global__ void __launch_bounds__(kBlock) map1_scalar_kernel(
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = f(a[i]);
 }
 template <class F> __global__ void __launch_bounds__(kBlock) map2_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ o, int64_t n, F f, AmaxOut am) {
+  grid_dep_sync();
   int64_t nv = n >> 2, stride = (int64_t)gridDim.x * blockDim.x;
   const float4* a4 = reinterpret_cast<const float4*>(a);
   const float4* b4 = reinterpret_cast<const float4*>(b);
@@ -81,6 +83,7 @@ template <class F> __global__ void __launch_bounds__(kBlock) map2_scalar_kernel(
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) o[i] = f(a[i], b[i]);
 }
 template <class F> __global__ void __launch_bounds__(kBlock) map3_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ c, float* __restrict__ o, int64_t n, F f, AmaxOut am) {
+  grid_dep_sync();
   int64_t nv = n >> 2, stride = (int64_t)gridDim.x * blockDim.x;
   const float4* a4 = reinterpret_cast<const float4*>(a);
   const float4* b4 = reinterpret_cast<const float4*>(b);
@@ -107,7 +110,7 @@ template <class F> static int run_map1(const float* a, float* o, int64_t n, cuda
   if (n <= 0) return 0;
   note_compute_stream(s);
   KernelTimer kt(what, s, 0, 8.0 * n);
-  if (aligned16(a) && aligned16(o)) map1_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, o, n, f, track_of<F>(o));
+  if (aligned16(a) && aligned16(o)) launch_dep(map1_kernel<F>, dim3(grid_for(n, kBlock, 4)), dim3(kBlock), 0, s, a, o, n, f, track_of<F>(o));
   else map1_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, o, n, f);
   TF_AFTER(s, what);
   return 0;
@@ -116,7 +119,7 @@ template <class F> static int run_map2(const float* a, const float* b, float* o,
   if (n <= 0) return 0;
   note_compute_stream(s);
   KernelTimer kt(what, s, 0, 12.0 * n);
-  if (aligned16(a) && aligned16(b) && aligned16(o)) map2_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, o, n, f, track_of<F>(o));
+  if (aligned16(a) && aligned16(b) && aligned16(o)) launch_dep(map2_kernel<F>, dim3(grid_for(n, kBlock, 4)), dim3(kBlock), 0, s, a, b, o, n, f, track_of<F>(o));
   else map2_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, b, o, n, f);
   TF_AFTER(s, what);
   return 0;
@@ -125,7 +128,7 @@ template <class F> static int run_map3(const float* a, const float* b, const flo
   if (n <= 0) return 0;
   note_compute_stream(s);
   KernelTimer kt(what, s, 0, 16.0 * n);
-  if (aligned16(a) && aligned16(b) && aligned16(c) && aligned16(o)) map3_kernel<<<grid_for(n, kBlock, 4), kBlock, 0, s>>>(a, b, c, o, n, f, track_of<F>(o));
+  if (aligned16(a) && aligned16(b) && aligned16(c) && aligned16(o)) launch_dep(map3_kernel<F>, dim3(grid_for(n, kBlock, 4)), dim3(kBlock), 0, s, a, b, c, o, n, f, track_of<F>(o));
   else map3_scalar_kernel<<<grid_for(n, kBlock, 1), kBlock, 0, s>>>(a, b, c, o, n, f);
   TF_AFTER(s, what);
   return 0;
@@ -322,6 +325,7 @@ template <int MODE> __global__ void __launch_bounds__(kBlock) loss_grad_kernel(c
 __device__ __forceinline__ uint32_t amax_of(const float4& v) { return amax4(0u, v); }
 __device__ __forceinline__ uint32_t amax_of(float v) { return amax_bits(v); }
 template <int MODE, typename V> __global__ void __launch_bounds__(kBlock) slice_copy_kernel(V* __restrict__ part, V* __restrict__ whole, int64_t nrows, int64_t part_inner, int64_t whole_inner, int64_t off, AmaxOut am) {
+  grid_dep_sync();
   uint32_t m = 0;
   for (int64_t r = blockIdx.y; r < nrows; r += gridDim.y) {
     V* p = part + r * part_inner;
@@ -344,8 +348,8 @@ template <int MODE> static void launch_slice_copy(float* part, float* whole, int
   int64_t want = (per_row + kBlock - 1) / kBlock, cap = (int64_t)8 * 148 / gy + 1;
   int gx = (int)(want < cap ? want : cap);
   dim3 grid(gx < 1 ? 1 : gx, gy);
-  if (vec) slice_copy_kernel<MODE, float4><<<grid, kBlock, 0, s>>>((float4*)part, (float4*)whole, rows, part_inner / 4, whole_inner / 4, off / 4, am);
-  else slice_copy_kernel<MODE, float><<<grid, kBlock, 0, s>>>(part, whole, rows, part_inner, whole_inner, off, am);
+  if (vec) launch_dep(slice_copy_kernel<MODE, float4>, grid, dim3(kBlock), 0, s, (float4*)part, (float4*)whole, rows, part_inner / 4, whole_inner / 4, off / 4, am);
+  else launch_dep(slice_copy_kernel<MODE, float>, grid, dim3(kBlock), 0, s, part, whole, rows, part_inner, whole_inner, off, am);
 }
 
 // ---- dropout: counter-based keep mask ---------------------------------------------------

@@ -93,6 +93,7 @@ __device__ __forceinline__ int window_argmax(const float* __restrict__ plane, co
 
 template <int KH, int KW>
 __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int32_t* __restrict__ idx, int64_t total, PoolGeom g, AmaxOut am) {
+  grid_dep_sync();
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   uint32_t amax = 0;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -134,6 +135,7 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restric
 // at run time); with compile-time bounds all index and dy loads are issued before the first use.
 template <bool MAXPOOL, int NP, int NQ>
 __global__ void __launch_bounds__(256) pool_bwd_gather_kernel(const int32_t* __restrict__ idx, const float* __restrict__ dy, float* __restrict__ dx, int64_t total, float scale, PoolGeom g) {
+  grid_dep_sync();
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     int64_t plane; int h, w;
@@ -177,6 +179,7 @@ __global__ void __launch_bounds__(256) pool_bwd_gather_kernel(const int32_t* __r
 }
 template <int KH, int KW>
 __global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t total, PoolGeom g, AmaxOut am) {
+  grid_dep_sync();
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   uint32_t amax = 0;
   float inv = 1.f / (float)(g.kh * g.kw);
@@ -229,20 +232,20 @@ static void launch_maxpool_fwd(const PoolPlan* p, const float* x, float* y, int3
   PoolGeom g = geom_of(p);
   int grid = grid_for(total, 256);
   AmaxOut am = y ? amax_track_begin(y) : AmaxOut{};
-  if (p->win_h == 3 && p->win_w == 3) maxpool_fwd_kernel<3, 3><<<grid, 256, 0, s>>>(x, y, idx, total, g, am);
-  else if (p->win_h == 2 && p->win_w == 2) maxpool_fwd_kernel<2, 2><<<grid, 256, 0, s>>>(x, y, idx, total, g, am);
-  else if (p->win_h == 1 && p->win_w == 1) maxpool_fwd_kernel<1, 1><<<grid, 256, 0, s>>>(x, y, idx, total, g, am);
-  else maxpool_fwd_kernel<0, 0><<<grid, 256, 0, s>>>(x, y, idx, total, g, am);
+  if (p->win_h == 3 && p->win_w == 3) launch_dep(maxpool_fwd_kernel<3, 3>, dim3(grid), dim3(256), 0, s, x, y, idx, total, g, am);
+  else if (p->win_h == 2 && p->win_w == 2) launch_dep(maxpool_fwd_kernel<2, 2>, dim3(grid), dim3(256), 0, s, x, y, idx, total, g, am);
+  else if (p->win_h == 1 && p->win_w == 1) launch_dep(maxpool_fwd_kernel<1, 1>, dim3(grid), dim3(256), 0, s, x, y, idx, total, g, am);
+  else launch_dep(maxpool_fwd_kernel<0, 0>, dim3(grid), dim3(256), 0, s, x, y, idx, total, g, am);
 }
 template <bool MAXPOOL> static void launch_pool_gather(const PoolPlan* p, const int32_t* idx, const float* dy, float* dx, int64_t total, float scale, cudaStream_t s) {
   PoolGeom g = geom_of(p);
   int grid = grid_for(total, 256);
   auto bound = [](int win, int stride, int count) { int n = (win + stride - 1) / stride; return n < count ? n : count; };
   int np = bound(p->win_h, p->stride_h, p->P), nq = bound(p->win_w, p->stride_w, p->Q);
-  if (np == 1 && nq == 1) pool_bwd_gather_kernel<MAXPOOL, 1, 1><<<grid, 256, 0, s>>>(idx, dy, dx, total, scale, g);
-  else if (np <= 2 && nq <= 2) pool_bwd_gather_kernel<MAXPOOL, 2, 2><<<grid, 256, 0, s>>>(idx, dy, dx, total, scale, g);
-  else if (np <= 3 && nq <= 3) pool_bwd_gather_kernel<MAXPOOL, 3, 3><<<grid, 256, 0, s>>>(idx, dy, dx, total, scale, g);
-  else pool_bwd_gather_kernel<MAXPOOL, 0, 0><<<grid, 256, 0, s>>>(idx, dy, dx, total, scale, g);
+  if (np == 1 && nq == 1) launch_dep(pool_bwd_gather_kernel<MAXPOOL, 1, 1>, dim3(grid), dim3(256), 0, s, idx, dy, dx, total, scale, g);
+  else if (np <= 2 && nq <= 2) launch_dep(pool_bwd_gather_kernel<MAXPOOL, 2, 2>, dim3(grid), dim3(256), 0, s, idx, dy, dx, total, scale, g);
+  else if (np <= 3 && nq <= 3) launch_dep(pool_bwd_gather_kernel<MAXPOOL, 3, 3>, dim3(grid), dim3(256), 0, s, idx, dy, dx, total, scale, g);
+  else launch_dep(pool_bwd_gather_kernel<MAXPOOL, 0, 0>, dim3(grid), dim3(256), 0, s, idx, dy, dx, total, scale, g);
 }
 
 // =====================================================================================
@@ -287,6 +290,7 @@ __device__ __forceinline__ void bn_group_sum(float (&part)[VEC], float (*red)[32
 
 template <int VEC>
 __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_fwd_regs_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ save_mean, float* __restrict__ save_inv, int N, int64_t F) {
+  grid_dep_sync();
   using V = typename VecT<VEC>::type;
   __shared__ float red[kBnGroups][32][VEC];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -349,6 +353,7 @@ __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_fwd_regs_kernel(const fl
 
 template <int VEC>
 __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_bwd_regs_kernel(const float* __restrict__ x, const float* __restrict__ dy, float* __restrict__ dx, const float* __restrict__ save_mean, const float* __restrict__ save_inv, int N, int64_t F, AmaxOut am) {
+  grid_dep_sync();
   using V = typename VecT<VEC>::type;
   __shared__ float red[kBnGroups][32][VEC];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -458,17 +463,17 @@ __global__ void __launch_bounds__(512) bn_sp_bwd_kernel(const float* __restrict_
 }
 
 static void launch_bn_fwd_regs(const float* x, float* y, float* sm, float* si, int N, int64_t F, cudaStream_t s) {
-  if (F % 4 == 0 && aligned16(x) && aligned16(y)) bn_pa_fwd_regs_kernel<4><<<(unsigned)((F / 4 + 31) / 32), 32 * kBnGroups, 0, s>>>(x, y, sm, si, N, F);
-  else bn_pa_fwd_regs_kernel<1><<<(unsigned)((F + 31) / 32), 32 * kBnGroups, 0, s>>>(x, y, sm, si, N, F);
+  if (F % 4 == 0 && aligned16(x) && aligned16(y)) launch_dep(bn_pa_fwd_regs_kernel<4>, dim3((unsigned)((F / 4 + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, y, sm, si, N, F);
+  else launch_dep(bn_pa_fwd_regs_kernel<1>, dim3((unsigned)((F + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, y, sm, si, N, F);
 }
 static void launch_bn_bwd_regs(const float* x, const float* dy, float* dx, const float* sm, const float* si, int N, int64_t F, cudaStream_t s) {
   AmaxOut am = amax_track_begin(dx);          // dx is the output gradient of the convolution in front of this layer
   // 8-byte vectors: the 16-byte variant holds 2 x 8 x 4 values per thread (126 registers, two blocks per SM) and its
   // load / reduce / store phases overlap too little; with half the registers three blocks fit (1.89 -> 1.77 ms per
   // ResNet-50 step)
-  if (F % 2 == 0 && aligned16(x) && aligned16(dy) && aligned16(dx)) bn_pa_bwd_regs_kernel<2><<<(unsigned)((F / 2 + 31) / 32), 32 * kBnGroups, 0, s>>>(x, dy, dx, sm, si, N, F, am);
-  else if (F % 4 == 0 && aligned16(x) && aligned16(dy) && aligned16(dx)) bn_pa_bwd_regs_kernel<4><<<(unsigned)((F / 4 + 31) / 32), 32 * kBnGroups, 0, s>>>(x, dy, dx, sm, si, N, F, am);
-  else bn_pa_bwd_regs_kernel<1><<<(unsigned)((F + 31) / 32), 32 * kBnGroups, 0, s>>>(x, dy, dx, sm, si, N, F, am);
+  if (F % 2 == 0 && aligned16(x) && aligned16(dy) && aligned16(dx)) launch_dep(bn_pa_bwd_regs_kernel<2>, dim3((unsigned)((F / 2 + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, dy, dx, sm, si, N, F, am);
+  else if (F % 4 == 0 && aligned16(x) && aligned16(dy) && aligned16(dx)) launch_dep(bn_pa_bwd_regs_kernel<4>, dim3((unsigned)((F / 4 + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, dy, dx, sm, si, N, F, am);
+  else launch_dep(bn_pa_bwd_regs_kernel<1>, dim3((unsigned)((F + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, dy, dx, sm, si, N, F, am);
 }
 
 }  // namespace tf
@@ -523,8 +528,8 @@ int DLGpuPooling2DForward(const DLArrayHandle input, DLArrayHandle output, void*
   else {
     float* y = out_f32(output);
     AmaxOut am = amax_track_begin(y);
-    if (p->win_h == 3 && p->win_w == 3) avgpool_fwd_kernel<3, 3><<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, y, total, geom_of(p), am);
-    else avgpool_fwd_kernel<0, 0><<<grid_for(total, 256), 256, 0, s>>>((const float*)input->data, y, total, geom_of(p), am);
+    if (p->win_h == 3 && p->win_w == 3) launch_dep(avgpool_fwd_kernel<3, 3>, dim3(grid_for(total, 256)), dim3(256), 0, s, (const float*)input->data, y, total, geom_of(p), am);
+    else launch_dep(avgpool_fwd_kernel<0, 0>, dim3(grid_for(total, 256)), dim3(256), 0, s, (const float*)input->data, y, total, geom_of(p), am);
   }
   TF_AFTER(s, "DLGpuPooling2DForward");
   return 0;
