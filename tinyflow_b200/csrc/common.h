@@ -137,7 +137,7 @@ inline cudaError_t launch_dep(void (*kernel)(Params...), dim3 grid, dim3 block, 
   memset(&attr, 0, sizeof(attr));
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = &attr; cfg.numAttrs = off ? 0 : 1;
+  cfg.attrs = &attr; cfg.numAttrs = (off || s == (cudaStream_t)0) ? 0 : 1;      // the legacy default stream keeps plain stream order
   return cudaLaunchKernelEx(&cfg, kernel, Params(args)...);
 }
 #endif
