@@ -31,6 +31,7 @@
 #include "common.h"
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <algorithm>
 #include <mutex>
 #include <type_traits>
 #include <unordered_map>
@@ -723,6 +724,41 @@ __global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restric
   }
 }
 
+// Both filter packs of one convolution in a single launch (the weights do not change between the forward and the
+// backward-data call of a step, so the second pack rides along with the first): element idx of the forward pack and
+// element idx of the backward-data pack per thread.
+__global__ void __launch_bounds__(256) pack_filter_pair_kernel(const float* __restrict__ w, __half* __restrict__ hi_f, __half* __restrict__ lo_f,
+                                                               __half* __restrict__ hi_d, __half* __restrict__ lo_d, int K, int C, int R, int S,
+                                                               int pad_f, int pad_d, ScaleRef sr, float* __restrict__ scale_d) {
+  grid_dep_sync();
+  const bool first = blockIdx.x == 0 && threadIdx.x == 0;
+  const float sc = pack_scale(sr, first);
+  if (first) *scale_d = sc;
+  const int taps = R * S;
+  const long long total_f = (long long)K * taps * pad_f, total_d = (long long)C * taps * pad_d;
+  const long long total = total_f > total_d ? total_f : total_d, stride = (long long)gridDim.x * blockDim.x;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    if (idx < total_f) {
+      int in = (int)(idx % pad_f);
+      long long t2 = idx / pad_f;
+      int tap = (int)(t2 % taps), k = (int)(t2 / taps);
+      float a = in < C ? w[((long long)k * C + in) * taps + tap] * sc : 0.f;
+      __half h, l;
+      split_f16(a, h, l);
+      hi_f[idx] = h; lo_f[idx] = l;
+    }
+    if (idx < total_d) {
+      int in = (int)(idx % pad_d);
+      long long t2 = idx / pad_d;
+      int tap = (int)(t2 % taps), c = (int)(t2 / taps);
+      float a = in < K ? w[((long long)in * C + c) * taps + (taps - 1 - tap)] * sc : 0.f;
+      __half h, l;
+      split_f16(a, h, l);
+      hi_d[idx] = h; lo_d[idx] = l;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
@@ -936,6 +972,7 @@ struct ConvTc {
   int x_off_h = 0, x_off_w = 0, dy_off_h = 0, dy_off_w = 0;
   int eC = 0, eR = 1, eS = 1;                            // reduction channels and window of the problem as the GEMM sees it
   int cp = 0;                                            // class D: columns per stride phase (C rounded up to 64)
+  bool dgrad_seen = false;                               // backward-data has run on this plan: forward also packs its filter layout
   Pack x, dy, wf, wd;
   std::mutex mu;
 };
@@ -1037,13 +1074,37 @@ static int pack_dy(ConvTc* st, const ConvPlan* p, const float* dy, cudaStream_t 
   pk.src = dy; pk.version = ver; pk.tag = 2;
   return 0;
 }
-static int pack_filter(Pack& pk, const float* w, const ConvPlan* p, const ConvTc* st, int flip, cudaStream_t s, int* oom) {
-  int taps = st->eR * st->eS, rows = flip ? st->eC : p->K, inner = flip ? p->K : st->eC, inner_pad = (int)round_up(inner, BK);
-  if (pack_alloc(pk, rows, (long long)taps * inner_pad, s, oom)) return 1;
-  ScaleRef sr = begin_pack(pk, w, (long long)p->K * p->C * p->R * p->S, s);
-  long long total = (long long)rows * taps * inner_pad;
-  launch_dep(pack_filter_kernel, dim3(grid_for(total, 256)), dim3(256), 0, s, w, pk.hi, pk.lo, p->K, st->eC, st->eR, st->eS, flip, inner_pad, sr);
+// Filter packs are keyed like the activation packs (pointer, write version): an optimiser step bumps the version.
+// `with_other` makes the forward call produce the backward-data pack in the same launch.
+static int pack_filter(ConvTc* st, const float* w, const ConvPlan* p, int flip, bool with_other, cudaStream_t s, int* oom) {
+  Pack& pk = flip ? st->wd : st->wf;
+  const uint64_t ver = version_of(w);
+  const int taps = st->eR * st->eS;
+  auto dims = [&](int f, int& rows, int& pad) { rows = f ? st->eC : p->K; pad = (int)round_up(f ? p->K : st->eC, BK); };
+  int rows, pad;
+  dims(flip, rows, pad);
+  if (pack_valid(pk, w, ver, 10 + flip, rows, (long long)taps * pad)) return 0;
+  if (pack_alloc(pk, rows, (long long)taps * pad, s, oom)) return 1;
+  const long long nw = (long long)p->K * p->C * p->R * p->S;
+  if (with_other && !flip) {
+    Pack& pd = st->wd;
+    int rows_d, pad_d;
+    dims(1, rows_d, pad_d);
+    if (pack_alloc(pd, rows_d, (long long)taps * pad_d, s, oom)) return 1;
+    ScaleRef sr = begin_pack(pk, w, nw, s);
+    long long total = std::max((long long)rows * taps * pad, (long long)rows_d * taps * pad_d);
+    launch_dep(pack_filter_pair_kernel, dim3(grid_for(total, 256)), dim3(256), 0, s, w, pk.hi, pk.lo, pd.hi, pd.lo, p->K, st->eC, st->eR, st->eS, pad, pad_d, sr,
+               reinterpret_cast<float*>(pd.words + 2));
+    TF_AFTER(s, "pack_filter");
+    pk.src = w; pk.version = ver; pk.tag = 10;
+    pd.src = w; pd.version = ver; pd.tag = 11;
+    return 0;
+  }
+  ScaleRef sr = begin_pack(pk, w, nw, s);
+  long long total = (long long)rows * taps * pad;
+  launch_dep(pack_filter_kernel, dim3(grid_for(total, 256)), dim3(256), 0, s, w, pk.hi, pk.lo, p->K, st->eC, st->eR, st->eS, flip, pad, sr);
   TF_AFTER(s, "pack_filter");
+  pk.src = w; pk.version = ver; pk.tag = 10 + flip;
   return 0;
 }
 
@@ -1109,7 +1170,7 @@ int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStrea
   if (!st->cls || !encode_fn()) return 0;
   std::lock_guard<std::mutex> lk(st->mu);
   if (pack_x(st, p, x, s, oom)) return *oom ? 1 : -1;
-  if (pack_filter(st->wf, w, p, st, 0, s, oom)) return *oom ? 1 : -1;
+  if (pack_filter(st, w, p, 0, st->dgrad_seen, s, oom)) return *oom ? 1 : -1;
   TapList taps;
   for (int r = 0; r < st->eR; ++r)
     for (int q = 0; q < st->eS; ++q) {
@@ -1126,7 +1187,8 @@ int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaS
   if (!st->cls || st->cls == 3 || !encode_fn()) return 0;
   std::lock_guard<std::mutex> lk(st->mu);
   if (pack_dy(st, p, dy, s, oom)) return *oom ? 1 : -1;
-  if (pack_filter(st->wd, w, p, st, 1, s, oom)) return *oom ? 1 : -1;     // [C][flipped tap][K]
+  st->dgrad_seen = true;                                           // from now on forward packs both layouts in one launch
+  if (pack_filter(st, w, p, 1, false, s, oom)) return *oom ? 1 : -1;     // [C][flipped tap][K]; a no-op when forward made it
   const int ntap = p->R * p->S;
   int rc = 0;
   if (st->cls == 1) {
