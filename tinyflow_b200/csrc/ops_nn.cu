@@ -177,6 +177,53 @@ __global__ void __launch_bounds__(256) pool_bwd_gather_kernel(const int32_t* __r
     dx[i] = acc * scale;
   }
 }
+// Max-pool gradient for 3x3 windows, stride 2, no padding (the ResNet / Inception stem pools): one thread per 2x2
+// block of dx.  The four elements share their candidate windows (p in {a-1, a}, q in {b-1, b}), so the four index / dy
+// pairs are loaded once instead of 2.25 times per element; contributions are added in the same (p, q) order as the
+// general gather, so the result is bit-identical to it.
+__global__ void __launch_bounds__(256) maxpool_bwd_3x3s2_kernel(const int32_t* __restrict__ idx, const float* __restrict__ dy, float* __restrict__ dx,
+                                                                int64_t blocks_total, int H, int W, int P, int Q, FastDiv dAB, FastDiv dB) {
+  grid_dep_sync();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int PQ = P * Q, HW = H * W;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < blocks_total; i += stride) {
+    int64_t plane; int a, b;
+    split_index(i, dAB, dB, plane, a, b);
+    const int32_t* ip = idx + plane * PQ;
+    const float* dp = dy + plane * PQ;
+    float* xp = dx + plane * HW;
+    int id[4]; float v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int p = a - 1 + (k >> 1), q = b - 1 + (k & 1);
+      const bool ok = (unsigned)p < (unsigned)P && (unsigned)q < (unsigned)Q;
+      id[k] = ok ? __ldg(ip + p * Q + q) : -1;
+      v[k] = ok ? __ldg(dp + p * Q + q) : 0.f;
+    }
+    const int h0 = 2 * a, w0 = 2 * b;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int h = h0 + r;
+      if (h >= H) break;
+      float o[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int hw = h * W + w0 + c;
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc += id[k] == hw ? v[k] : 0.f;
+        o[c] = acc;
+      }
+      if (w0 + 1 < W) {
+        if ((W & 1) == 0) *reinterpret_cast<float2*>(xp + h * W + w0) = make_float2(o[0], o[1]);
+        else { xp[h * W + w0] = o[0]; xp[h * W + w0 + 1] = o[1]; }
+      } else {
+        xp[h * W + w0] = o[0];
+      }
+    }
+  }
+}
+
 template <int KH, int KW>
 __global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t total, PoolGeom g, AmaxOut am) {
   grid_dep_sync();
@@ -239,6 +286,15 @@ static void launch_maxpool_fwd(const PoolPlan* p, const float* x, float* y, int3
 }
 template <bool MAXPOOL> static void launch_pool_gather(const PoolPlan* p, const int32_t* idx, const float* dy, float* dx, int64_t total, float scale, cudaStream_t s) {
   PoolGeom g = geom_of(p);
+  if (MAXPOOL && p->win_h == 3 && p->win_w == 3 && p->stride_h == 2 && p->stride_w == 2 && p->pad_h == 0 && p->pad_w == 0 &&
+      (reinterpret_cast<uintptr_t>(dx) & 7) == 0) {
+    const int A = (p->H + 1) / 2, B = (p->W + 1) / 2;
+    const int64_t blocks = (int64_t)p->N * p->C * A * B;
+    FastDiv dAB, dB;
+    dAB.init((uint32_t)(A * B)); dB.init((uint32_t)B);
+    launch_dep(maxpool_bwd_3x3s2_kernel, dim3(grid_for(blocks, 256)), dim3(256), 0, s, idx, dy, dx, blocks, p->H, p->W, p->P, p->Q, dAB, dB);
+    return;
+  }
   int grid = grid_for(total, 256);
   auto bound = [](int win, int stride, int count) { int n = (win + stride - 1) / stride; return n < count ? n : count; };
   int np = bound(p->win_h, p->stride_h, p->P), nq = bound(p->win_w, p->stride_w, p->Q);
