@@ -379,7 +379,7 @@ def test_conv_forward_backward(env, case, path):
 # ---- pooling ---------------------------------------------------------------------------------------------------
 POOL = [(2, 3, 8, 8, 0, 0, 2, 2, 2, 2), (2, 4, 112, 112, 0, 0, 2, 2, 3, 3), (2, 3, 24, 24, 3, 3, 1, 1, 1, 1),
         (3, 5, 7, 7, 0, 0, 1, 1, 7, 7), (2, 6, 17, 17, 1, 1, 1, 1, 3, 3), (2, 6, 17, 17, 0, 0, 2, 2, 3, 3), (1, 2, 8, 8, 0, 0, 1, 1, 8, 8),
-        (2, 5, 147, 147, 0, 0, 2, 2, 3, 3), (3, 2, 20, 13, 0, 0, 2, 2, 3, 3), (2, 3, 9, 10, 0, 0, 2, 2, 3, 3)]
+        (2, 5, 147, 147, 0, 0, 2, 2, 3, 3), (2, 3, 9, 11, 0, 0, 2, 2, 2, 2), (2, 2, 14, 14, 0, 0, 2, 2, 2, 2), (1, 3, 7, 8, 0, 0, 2, 2, 2, 2), (3, 2, 20, 13, 0, 0, 2, 2, 3, 3), (2, 3, 9, 10, 0, 0, 2, 2, 3, 3)]
 
 
 @pytest.mark.parametrize("case", POOL)

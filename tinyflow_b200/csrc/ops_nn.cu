@@ -224,6 +224,33 @@ __global__ void __launch_bounds__(256) maxpool_bwd_3x3s2_kernel(const int32_t* _
   }
 }
 
+// Max-pool gradient for 2x2 windows, stride 2, no padding (VGG, LeNet): windows do not overlap, so one thread owns
+// one window: it reads its index and dy and writes the window's four dx elements (dy at the maximum, 0 elsewhere).
+// Rows / columns of dx past the last window (odd extents) are zero-filled by the threads of the last window row / column.
+__global__ void __launch_bounds__(256) maxpool_bwd_2x2s2_kernel(const int32_t* __restrict__ idx, const float* __restrict__ dy, float* __restrict__ dx,
+                                                                int64_t total, int H, int W, int P, int Q, FastDiv dPQ, FastDiv dQ) {
+  grid_dep_sync();
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int PQ = P * Q, HW = H * W;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    int64_t plane; int p, q;
+    split_index(i, dPQ, dQ, plane, p, q);
+    const int id = __ldg(idx + plane * PQ + p * Q + q);
+    const float v = __ldg(dy + plane * PQ + p * Q + q);
+    float* xp = dx + plane * HW;
+    const int h0 = 2 * p, w0 = 2 * q;
+    const int h_end = p == P - 1 ? H : h0 + 2, w_end = q == Q - 1 ? W : w0 + 2;     // the last windows also clear the leftover edge
+    for (int h = h0; h < h_end; ++h) {
+      if (w_end == w0 + 2 && (W & 1) == 0) {
+        const int hw = h * W + w0;
+        *reinterpret_cast<float2*>(xp + hw) = make_float2(id == hw ? v : 0.f, id == hw + 1 ? v : 0.f);
+      } else {
+        for (int w = w0; w < w_end; ++w) xp[h * W + w] = id == h * W + w ? v : 0.f;
+      }
+    }
+  }
+}
+
 template <int KH, int KW>
 __global__ void __launch_bounds__(256) avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int64_t total, PoolGeom g, AmaxOut am) {
   grid_dep_sync();
@@ -293,6 +320,12 @@ template <bool MAXPOOL> static void launch_pool_gather(const PoolPlan* p, const 
     FastDiv dAB, dB;
     dAB.init((uint32_t)(A * B)); dB.init((uint32_t)B);
     launch_dep(maxpool_bwd_3x3s2_kernel, dim3(grid_for(blocks, 256)), dim3(256), 0, s, idx, dy, dx, blocks, p->H, p->W, p->P, p->Q, dAB, dB);
+    return;
+  }
+  if (MAXPOOL && p->win_h == 2 && p->win_w == 2 && p->stride_h == 2 && p->stride_w == 2 && p->pad_h == 0 && p->pad_w == 0 &&
+      p->P > 0 && p->Q > 0 && (reinterpret_cast<uintptr_t>(dx) & 7) == 0) {
+    const int64_t windows = (int64_t)p->N * p->C * p->P * p->Q;
+    launch_dep(maxpool_bwd_2x2s2_kernel, dim3(grid_for(windows, 256)), dim3(256), 0, s, idx, dy, dx, windows, p->H, p->W, p->P, p->Q, g.dPQ, g.dQ);
     return;
   }
   int grid = grid_for(total, 256);
