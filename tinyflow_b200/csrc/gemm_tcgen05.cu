@@ -569,18 +569,42 @@ __device__ __forceinline__ void split_f16(float a, __half& hi, __half& lo) {
   lo = __float2half_rn(a - __half2float(hi));
 }
 
-// rows x cols row-major (pitch src_ld) -> hi/lo with pitch dst_ld
+// rows x cols row-major (pitch src_ld) -> hi/lo with pitch dst_ld.  VEC8: eight consecutive columns per thread
+// (two 16-byte loads, one 16-byte store each of hi and lo); needs cols and src_ld multiples of 8 and a 16-byte
+// aligned source (the packs' pitch is a multiple of 64).
+template <bool VEC8>
 __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restrict__ src, long long src_ld, __half* __restrict__ hi, __half* __restrict__ lo,
                                                           long long dst_ld, long long rows, long long cols, ScaleRef sr) {
   grid_dep_sync();
   const float sc = pack_scale(sr, blockIdx.x == 0 && threadIdx.x == 0);
-  long long total = rows * cols, stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    long long r = i / cols, c = i - r * cols;
-    __half h, l;
-    split_f16(src[r * src_ld + c] * sc, h, l);
-    hi[r * dst_ld + c] = h;
-    lo[r * dst_ld + c] = l;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  if (VEC8) {
+    const long long cols8 = cols >> 3, total = rows * cols8;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      const long long r = i / cols8, c = (i - r * cols8) << 3;
+      const float4 a = __ldg(reinterpret_cast<const float4*>(src + r * src_ld + c));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(src + r * src_ld + c) + 1);
+      const float v[8] = {a.x * sc, a.y * sc, a.z * sc, a.w * sc, b.x * sc, b.y * sc, b.z * sc, b.w * sc};
+      __align__(16) __half2 h[4];
+      __align__(16) __half2 l[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+        const float2 hf = __half22float2(h[e]);
+        l[e] = __floats2half2_rn(v[2 * e] - hf.x, v[2 * e + 1] - hf.y);
+      }
+      *reinterpret_cast<uint4*>(hi + r * dst_ld + c) = *reinterpret_cast<const uint4*>(h);
+      *reinterpret_cast<uint4*>(lo + r * dst_ld + c) = *reinterpret_cast<const uint4*>(l);
+    }
+  } else {
+    const long long total = rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+      long long r = i / cols, c = i - r * cols;
+      __half h, l;
+      split_f16(src[r * src_ld + c] * sc, h, l);
+      hi[r * dst_ld + c] = h;
+      lo[r * dst_ld + c] = l;
+    }
   }
 }
 
@@ -913,7 +937,10 @@ static int run_pack_matrix(const float* src, long long ld, Pack& pk, cudaStream_
   long long total = pk.rows * pk.cols;
   ScaleRef sr = begin_pack(pk, src, total, s);          // callers pass ld == cols: the matrix is contiguous
   KernelTimer kt("pack_matrix", s, 0, 8.0 * total);
-  launch_dep(pack_matrix_kernel, dim3(grid_for(total, 256, 4)), dim3(256), 0, s, src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols, sr);
+  if (pk.cols % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0)
+    launch_dep(pack_matrix_kernel<true>, dim3(grid_for(total / 8, 256, 2)), dim3(256), 0, s, src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols, sr);
+  else
+    launch_dep(pack_matrix_kernel<false>, dim3(grid_for(total, 256, 4)), dim3(256), 0, s, src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols, sr);
   TF_AFTER(s, "pack_matrix");
   return 0;
 }
