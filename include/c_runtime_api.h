@@ -25,6 +25,13 @@
  *   - Out-of-memory is not an error: the call returns 0 and writes the number of
  *     bytes it failed to get through `int *memorytoSaving` (written only then).
  *   - The library never calls exit()/abort(); bad arguments return -1.
+ *   - Convolutions and matrix products of useful size run on the tensor cores in
+ *     3xFP16: each fp32 operand tensor is scaled by a power of two taken from its
+ *     largest magnitude and split into an fp16 hi/lo pair, products accumulate in
+ *     fp32.  Results agree with fp32 arithmetic to better than 1e-4; precision is
+ *     relative to each operand tensor's largest element (values more than 2^18
+ *     below it lose low-order bits).  TfSetContractionPath(1) selects exact-fp32
+ *     CUDA-core kernels instead.
  */
 #ifndef TINYFLOW_B200_C_RUNTIME_API_H_
 #define TINYFLOW_B200_C_RUNTIME_API_H_
