@@ -701,17 +701,26 @@ __global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restri
     const int n = (int)(row / pq), rem = (int)(row - (long long)n * pq), pp = rem / g.Q, qq = rem - pp * g.Q;
     const int i0 = pp * g.sh - g.pad_h, j0 = qq * g.sw - g.pad_w;
     const float* base = src + ((long long)n * g.C * g.H + i0) * g.W + j0;
+    const bool interior = i0 >= 0 && i0 + g.R <= g.H && j0 >= 0 && j0 + g.S <= g.W;
     __half2* h_row = reinterpret_cast<__half2*>(hi + row * g.pitch);
     __half2* l_row = reinterpret_cast<__half2*>(lo + row * g.pitch);
     for (int col2 = lane; col2 < g.pitch / 2; col2 += 32) {        // two columns per lane
       float a[2];
+      if (interior) {          // the whole window lies inside the image (uniform over the warp): no per-tap range checks
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int col = 2 * col2 + e;
-        a[e] = 0.f;
-        if (col < g.cols) {
-          const int i = i0 + col_r[col], j = j0 + col_s[col];
-          if (i >= 0 && i < g.H && j >= 0 && j < g.W) a[e] = __ldg(base + col_off[col]) * sc;
+        for (int e = 0; e < 2; ++e) {
+          const int col = 2 * col2 + e;
+          a[e] = col < g.cols ? __ldg(base + col_off[col]) * sc : 0.f;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int col = 2 * col2 + e;
+          a[e] = 0.f;
+          if (col < g.cols) {
+            const int i = i0 + col_r[col], j = j0 + col_s[col];
+            if (i >= 0 && i < g.H && j >= 0 && j < g.W) a[e] = __ldg(base + col_off[col]) * sc;
+          }
         }
       }
       __half h0, l0, h1, l1;
