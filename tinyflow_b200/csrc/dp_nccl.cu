@@ -101,6 +101,7 @@ struct DpState {
 static DpState g_dp;
 
 __global__ void __launch_bounds__(256) dp_copy_kernel(const float* __restrict__ g, float* __restrict__ dst, long long n) {
+  grid_dep_sync();
   long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = g[i];
 }
@@ -165,7 +166,7 @@ int dp_sgd_update(float* w, const float* g, int64_t n, float lr, cudaStream_t s)
     TF_CUDA(cudaStreamWaitEvent(s, b->applied, 0));
     b->in_flight = false;
   }
-  dp_copy_kernel<<<grid_for(n, 256, 4), 256, 0, s>>>(g, b->buf + b->fill, n);
+  launch_dep(dp_copy_kernel, dim3(grid_for(n, 256, 4)), dim3(256), 0, s, g, b->buf + b->fill, n);
   if (after_launch(s, "dp_copy", 1) != 0) return -1;
   b->entries.push_back(Entry{w, b->fill, (long long)n, lr});
   b->fill += (n + 3) & ~3ll;       // keep every tensor 16-byte aligned inside the bucket
