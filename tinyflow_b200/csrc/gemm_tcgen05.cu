@@ -1264,6 +1264,35 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
   if (pack_dy(st, p, dy, s, oom)) return *oom ? 1 : -1;
   GemmParams g;
   memset(&g, 0, sizeof(g));
+  if (st->eR * st->eS == 1 && st->dy_off_h == 0 && st->dy_off_w == 0) {
+    // One tap: dW[k][c] = dy^T x is a plain GEMM over the two packs, and either operand may take the M side.
+    // Take the orientation whose padded tile grid is smaller (64 input channels would fill half of a 128-row tile).
+    auto padded = [](long long m, long long n) { int b = pick_bn(n); return ((m + BM - 1) / BM * BM) * ((n + b - 1) / b * b); };
+    const long long slot_rows = st->eC > 64 ? (st->eC + BM - 1) / BM * BM : BM;
+    const int bn_x = pick_bn(p->K);
+    const long long as_is = slot_rows * ((p->K + bn_x - 1) / bn_x * bn_x);
+    if (padded(p->K, st->eC) < as_is) {
+      const int bn = pick_bn(st->eC);
+      g.mode = kModeGemm; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiRowMajor; g.atomic = 1;
+      int rc = make_map_mn(&g.a_hi, st->dy.hi, st->dy.rows, st->dy.pitch, BM / 64);
+      if (!rc) rc = make_map_mn(&g.a_lo, st->dy.lo, st->dy.rows, st->dy.pitch, BM / 64);
+      if (!rc) rc = make_map_mn(&g.b_hi, st->x.hi, st->x.rows, st->x.pitch, bn / 64);
+      if (!rc) rc = make_map_mn(&g.b_lo, st->x.lo, st->x.rows, st->x.pitch, bn / 64);
+      if (rc) return -1;
+      g.a_scale = st->dy.scale(); g.b_scale = st->x.scale();
+      g.M = p->K; g.N = st->eC; g.ldc = st->eC;
+      g.m_tiles = (p->K + BM - 1) / BM; g.n_tiles = (st->eC + bn - 1) / bn; g.tap_tiles = 1; g.ntaps = 1;
+      const int kit = (int)((st->dy.rows + BK - 1) / BK);
+      const int splits = choose_splits(g.m_tiles * g.n_tiles, kit, 4, 1024, true);
+      g.k_total = kit;
+      g.k_iters = (kit + splits - 1) / splits;
+      g.splits = (kit + g.k_iters - 1) / g.k_iters;
+      g.out = dw; g.err = error_word();
+      if (cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)p->K * p->C * p->R * p->S, s) != cudaSuccess) return -1;
+      rc = launch_gemm_bn(bn, g, s, conv_flops(p), "DLGpuConvolutionBackwardFilter");
+      return rc ? -1 : 1;
+    }
+  }
   // A = x (M = tap slots x input channels), B = dy (N = output channels); both M/N-major, reduction over pixel rows.
   const int bn = pick_bn(p->K);
   g.mode = kModeWgrad; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiWgrad; g.atomic = 1;
