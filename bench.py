@@ -143,10 +143,27 @@ def cpu_threads():
     return n, len(os.sched_getaffinity(0))
 
 
+def pin_blas_threads():
+    """Gives the BLAS behind numpy every usable core (at most the 64 OpenBLAS is built for), whatever the launcher put
+    into OMP_NUM_THREADS (torchrun sets it to 1).  Call before numpy is imported; repeated through threadpoolctl for
+    a BLAS that is already loaded."""
+    want = max(1, min(len(os.sched_getaffinity(0)), 64))
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = str(want)
+    try:
+        import numpy  # noqa: F401
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=want)
+    except Exception:
+        pass
+    return want
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
+    pin_blas_threads()
     import numpy as np  # noqa: F401  (loads the BLAS whose thread count is reported)
     workload = args.workload
     cfg = WORKLOADS[workload]
@@ -169,6 +186,8 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    from tinyflow_b200._base import _LIB
+    assert not _LIB.loaded, "the CPU arm must not map the CUDA library"
     print(json.dumps(line))
     return 0
 
@@ -239,23 +258,45 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def flush_dp():
+        # end of a data-parallel step: sends the last, partly filled gradient bucket and makes the compute stream
+        # wait for every applied update, so the next forward pass reads the new weights
+        if world > 1:
+            check_call(_LIB.TfDpFlush(ex.cudaStream))
+
     def step_resident(fd):
         fd[model.X], fd[model.y_] = Xd, Yd
         loss, nxt = ex.run(fd)
+        flush_dp()
         return loss, nxt
 
-    def step_e2e(fd):
-        # host -> device copy of this step's inputs from pinned memory, device -> host read of the loss
-        fd[model.X] = Xh.copyto(ctx, None)
-        fd[model.y_] = Yh.copyto(ctx, None)
-        loss, nxt = ex.run(fd)
-        if world > 1:
-            check_call(_LIB.TfDpFlush(ex.cudaStream))
-        return loss.asnumpy(), nxt
+    # End-to-end arm: every step uploads its inputs from pinned host memory and reads its loss back.  The upload of
+    # step k+1 runs on a side stream from a helper thread while step k computes (the swap threads of the reference's
+    # executor use DLArrayCopyFromTo the same way): two device buffers alternate, the helper's call returns when its
+    # copy has completed, and the step that consumes a buffer joins the helper first.
+    in_bufs = [(ndarray.empty(Xn.shape, ctx), ndarray.empty(Yn.shape, ctx)) for _ in range(2)]
+    copy_stream = gpu_op.create_cudaStream()
+    upload = {"thread": None, "k": 0}
 
-    def flush_dp():
-        if world > 1:
-            check_call(_LIB.TfDpFlush(ex.cudaStream))
+    def start_upload(slot):
+        def work():
+            Xh.copyto(in_bufs[slot][0], copy_stream)
+            Yh.copyto(in_bufs[slot][1], copy_stream)
+        t = threading.Thread(target=work, daemon=True)
+        t.start()
+        upload["thread"] = t
+
+    def step_e2e(fd):
+        k = upload["k"]
+        if upload["thread"] is None:
+            start_upload(k & 1)
+        upload["thread"].join()                       # this step's inputs are on the device
+        fd[model.X], fd[model.y_] = in_bufs[k & 1]
+        start_upload((k + 1) & 1)                     # next step's inputs travel while this step computes
+        upload["k"] = k + 1
+        loss, nxt = ex.run(fd)
+        flush_dp()
+        return loss.asnumpy(), nxt                    # device -> host read of the loss: the step has finished
 
     plan_info = None
     for w in range(args.warmup):
@@ -268,7 +309,6 @@ def main():
         loss, feed = step_resident(feed)
     if args.memory_plan != "none" and plan_info is None:
         raise SystemExit("--memory-plan needs --warmup >= 2")
-    flush_dp()
     barrier()
     flops = step_flops(ex)
 
@@ -285,7 +325,6 @@ def main():
     e0.record(ext)
     for _ in range(args.steps):
         loss, feed = step_resident(feed)
-    flush_dp()
     e1.record(ext)
     barrier()
     wall = time.perf_counter() - t_wall0
@@ -300,7 +339,6 @@ def main():
     t_i0 = time.perf_counter()
     for _ in range(args.steps):
         loss, feed = step_resident(feed)
-    flush_dp()
     barrier()
     instrumented_ms = (time.perf_counter() - t_i0) * 1000.0 / args.steps
     report = ctypes.create_string_buffer(1 << 16)
@@ -319,13 +357,13 @@ def main():
         lv, feed = step_e2e(feed)
     barrier()
     e2e_s = time.perf_counter() - t0
+    upload["thread"].join()                           # the look-ahead upload of a step that is never run
 
     # ---- untimed extra steps with every instrumented kernel timed: the per-kernel table
     _LIB.TfKernelTimingEnable(2)
     prof_steps = 2
     for _ in range(prof_steps):
         loss, feed = step_resident(feed)
-    flush_dp()
     barrier()
     _LIB.TfKernelTimingReport(report, len(report))
     _LIB.TfKernelTimingEnable(0)
@@ -341,6 +379,21 @@ def main():
 
     if os.environ.get("TINYFLOW_KERNEL_TABLE") and rank == 0:
         json.dump(all_rows, open(os.environ["TINYFLOW_KERNEL_TABLE"], "w"), indent=0)
+
+    # Data-parallel correctness bit: every rank must hold bit-identical weights after the timed steps.  Each weight
+    # tensor is digested (sum of its 32-bit patterns, and its float64 sum) and the digests' minimum and maximum over
+    # the ranks are compared.
+    dp_identical = None
+    if dist is not None:
+        digest = []
+        for var in model.param_shapes:
+            w = feed[var].asnumpy()
+            digest += [float(w.view(np.uint32).astype(np.uint64).sum() % (1 << 52)), float(w.astype(np.float64).sum())]
+        lo = torch.tensor(digest, dtype=torch.float64, device="cuda:0")
+        hi = lo.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        dp_identical = bool(torch.equal(lo, hi))
 
     ms = torch.tensor([max(dev_ms, 0.0), wall * 1000.0, e2e_s * 1000.0], dtype=torch.float64, device="cuda:0")
     if dist is not None:
@@ -392,7 +445,8 @@ def main():
                        "global_batch": world * batch, "parallelism": "dp%d" % world, "l2": "per-step working set (GBs of activations) exceeds the 126 MB L2",
                        "dropout": (model.dropout_nodes[0].dropout if model.dropout_nodes else 0.0), "device_ms_per_step": dev_ms / args.steps, "host_ms_per_step": wall_ms / args.steps,
                        "algorithmic_tflop_per_step": flops / 1e12, "final_loss": final_loss, "memory_plan": plan_info,
-                       "passive_swap_ins": ex.passive_swap_in},
+                       "passive_swap_ins": ex.passive_swap_in, "arithmetic": gpu_op.tensor_arithmetic(),
+                       "dp_weights_identical": dp_identical},
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(Xn.nbytes + Yn.nbytes), "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
             "clocks": clocks,
@@ -405,7 +459,7 @@ def main():
         _LIB.TfDpShutdown()
         dist.destroy_process_group()
     sys.stdout.flush()
-    os._exit(0)
+    return 0
 
 
 if __name__ == "__main__":

@@ -293,6 +293,16 @@ int TfKernelTimingEnable(int level);      /* CUDA-event timing per kernel family
 int TfKernelTimingReport(char *buf, int buflen);  /* JSON rows {name, launches, ms, flops, bytes} */
 int TfLaunchCount(long long *count);      /* kernels launched by this library so far */
 int TfSetContractionPath(int path);       /* 0 = auto, 1 = force CUDA-core path, 2 = force tcgen05 path */
+int TfLastContractionPath(void);          /* engine that served this thread's last matmul / convolution: 1 = CUDA cores, 2 = tensor cores */
+/* Arithmetic of the tensor-core path: 0 = 3xFP16 (default; fp16 hi/lo pairs of the operand scaled by a per-tensor
+ * power of two), 1 = 3xTF32 (tf32 hi/lo pairs, no scaling, half the tensor rate and twice the operand bytes).
+ * Also settable with the environment variable TINYFLOW_ARITH=3xfp16|3xtf32.  Takes effect at the next call. */
+int TfSetArithmetic(int arithmetic);
+int TfGetArithmetic(void);
+/* A tensor-core kernel whose barrier wait ran out raises a sticky error word and later launches are refused;
+ * TfTensorPathError reads it, TfClearTensorPathError resets it once the cause has been dealt with. */
+int TfTensorPathError(void);
+int TfClearTensorPathError(void);
 int TfLastError(char *buf, int buflen);   /* message of the last -1 return on this thread */
 int TfAllocatorStats(long long *bytes_in_use, long long *bytes_cached);
 int TfReleaseCachedMemory(void);

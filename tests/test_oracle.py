@@ -209,3 +209,23 @@ def test_small_resnet_style_graph_gradients_match_torch(lib_path):
     np.testing.assert_allclose(vals[loss][0], lt.item(), rtol=1e-10)
     for gnode, t in zip(grads, (wt, wdt, bdt)):
         np.testing.assert_allclose(vals[gnode], t.grad.numpy(), rtol=1e-7, atol=1e-11)
+
+
+@pytest.mark.parametrize("case", [(2, 5, 9, 10, 4, 3, 3, "SAME", 1, 1), (2, 3, 11, 9, 6, 5, 3, "VALID", 2, 2),
+                                  (3, 4, 8, 8, 5, 1, 7, "SAME", 1, 1), (2, 6, 10, 10, 4, 3, 3, "SAME", 2, 2)])
+def test_sampled_convolution_oracle_equals_the_dense_one(case):
+    """The coordinate-sampled convolution functions (used at benchmark sizes, where the dense oracle is too slow)
+    give the dense oracle's values at those coordinates."""
+    N, C, H, W, K, R, S, pad, sh, sw = case
+    rng = np.random.RandomState(5)
+    x, w = rng.randn(N, C, H, W), rng.randn(K, C, R, S)
+    g = ops.conv_geometry(x.shape, w.shape, pad, sh, sw)
+    dy = rng.randn(N, K, g["P"], g["Q"])
+    T = 64
+    n, k, c = rng.randint(0, N, T), rng.randint(0, K, T), rng.randint(0, C, T)
+    p, q = rng.randint(0, g["P"], T), rng.randint(0, g["Q"], T)
+    h, wi = rng.randint(0, H, T), rng.randint(0, W, T)
+    r, s = rng.randint(0, R, T), rng.randint(0, S, T)
+    np.testing.assert_allclose(ops.conv2d_fwd_at(x, w, g, n, k, p, q), ops.conv2d_fwd(x, w, g)[n, k, p, q], rtol=1e-12, atol=1e-12)
+    np.testing.assert_allclose(ops.conv2d_dgrad_at(dy, w, g, n, c, h, wi), ops.conv2d_dgrad(dy, w, g)[n, c, h, wi], rtol=1e-12, atol=1e-12)
+    np.testing.assert_allclose(ops.conv2d_wgrad_at(x, dy, g, k, c, r, s), ops.conv2d_wgrad(x, dy, g)[k, c, r, s], rtol=1e-12, atol=1e-12)

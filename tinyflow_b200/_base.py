@@ -3,6 +3,10 @@
 Mirrors pycode/tinyflow/_base.py of the reference: one process-wide ``_LIB`` opened with
 RTLD_GLOBAL from ``<repo>/build/lib/libc_runtime_api.so``.  There is no CPU fallback: a
 missing library is an ImportError that says how to build it.
+
+The library is mapped on the first call into it, not at import: building and analysing a graph
+(``graph``, ``models``, ``Executor.__init__``) needs no device code, so a process that only walks
+graphs (the CPU baseline arm of the benchmark) never maps the CUDA library.
 """
 from __future__ import annotations
 
@@ -21,7 +25,28 @@ def _load_lib():
     return ctypes.CDLL(LIB_PATH, ctypes.RTLD_GLOBAL)
 
 
-_LIB = _load_lib()
+class _LazyLib(object):
+    """Stands for the ``ctypes.CDLL``; opens it when the first symbol is looked up."""
+
+    def __init__(self):
+        object.__setattr__(self, "_cdll", None)
+
+    def _load(self):
+        cdll = object.__getattribute__(self, "_cdll")
+        if cdll is None:
+            cdll = _load_lib()
+            object.__setattr__(self, "_cdll", cdll)
+        return cdll
+
+    @property
+    def loaded(self):
+        return object.__getattribute__(self, "_cdll") is not None
+
+    def __getattr__(self, name):
+        return getattr(self._load(), name)
+
+
+_LIB = _LazyLib()
 
 
 class TinyflowError(RuntimeError):

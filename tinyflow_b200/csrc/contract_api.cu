@@ -18,12 +18,30 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
 
 static int g_path = [] { const char* e = getenv("TINYFLOW_CONTRACTION"); return e ? atoi(e) : 0; }();   // 0 auto, 1 CUDA cores, 2 tensor cores
 int contraction_path() { return g_path; }
+int tensor_arithmetic();
+void set_tensor_arithmetic(int a);
+int tensor_path_error();
+void tensor_path_error_clear();
+// which engine served this thread's most recent contraction: 1 = CUDA cores, 2 = tensor cores (0 = none yet)
+static thread_local int t_last_path = 0;
 
 }  // namespace tf
 
 using namespace tf;
 
 extern "C" {
+
+int TfLastContractionPath(void) { return t_last_path; }
+
+int TfSetArithmetic(int arithmetic) {
+  TF_REQUIRE(arithmetic == 0 || arithmetic == 1, "TfSetArithmetic: 0 = 3xFP16, 1 = 3xTF32");
+  set_tensor_arithmetic(arithmetic);
+  return 0;
+}
+int TfGetArithmetic(void) { return tensor_arithmetic(); }
+
+int TfTensorPathError(void) { return tensor_path_error(); }
+int TfClearTensorPathError(void) { tensor_path_error_clear(); return 0; }
 
 int TfSetContractionPath(int path) {
   TF_REQUIRE(path >= 0 && path <= 2, "TfSetContractionPath: path must be 0, 1 or 2");
@@ -48,9 +66,10 @@ int DLGpuMatrixMultiply(const DLArrayHandle matA, bool transposeA, const DLArray
     int oom = 0;
     int r = tc_matmul(A, transposeA, B, transposeB, C, M, N, K, s, &oom);
     if (r < 0) return -1;
-    if (r == 1) return 0;
+    if (r == 1) { t_last_path = 2; return 0; }
     TF_REQUIRE(g_path != 2, "DLGpuMatrixMultiply: shape not taken by the tensor-core path (forced)");
   }
+  t_last_path = 1;
   return cudacore_matmul(A, transposeA, B, transposeB, C, M, N, K, matA->shape[1], matB->shape[1], s);
 }
 
@@ -104,9 +123,10 @@ int DLGpuConvolution2DForward(const DLArrayHandle input, const DLArrayHandle fil
     int r = tc_conv_fwd(p, (const float*)input->data, (const float*)filter->data, out_f32(output), s, &oom);
     if (r < 0) return -1;
     if (oom) { if (memorytoSaving) *memorytoSaving = oom; return 0; }
-    if (r == 1) return 0;
+    if (r == 1) { t_last_path = 2; return 0; }
     TF_REQUIRE(g_path != 2, "DLGpuConvolution2DForward: shape not taken by the tensor-core path (forced)");
   }
+  t_last_path = 1;
   return cudacore_conv_fwd(p, (const float*)input->data, (const float*)filter->data, out_f32(output), s);
 }
 
@@ -122,9 +142,10 @@ int DLGpuConvolutionBackwardData(const DLArrayHandle input, const DLArrayHandle 
     int r = tc_conv_dgrad(p, (const float*)doutput->data, (const float*)filter->data, out_f32(dinput), s, &oom);
     if (r < 0) return -1;
     if (oom) { if (memorytoSaving) *memorytoSaving = oom; return 0; }
-    if (r == 1) return 0;
+    if (r == 1) { t_last_path = 2; return 0; }
     TF_REQUIRE(g_path != 2, "DLGpuConvolutionBackwardData: shape not taken by the tensor-core path (forced)");
   }
+  t_last_path = 1;
   return cudacore_conv_dgrad(p, (const float*)doutput->data, (const float*)filter->data, out_f32(dinput), s);
 }
 
@@ -140,9 +161,10 @@ int DLGpuConvolutionBackwardFilter(const DLArrayHandle input, const DLArrayHandl
     int r = tc_conv_wgrad(p, (const float*)input->data, (const float*)doutput->data, out_f32(dfilter), s, &oom);
     if (r < 0) return -1;
     if (oom) { if (memorytoSaving) *memorytoSaving = oom; return 0; }
-    if (r == 1) return 0;
+    if (r == 1) { t_last_path = 2; return 0; }
     TF_REQUIRE(g_path != 2, "DLGpuConvolutionBackwardFilter: shape not taken by the tensor-core path (forced)");
   }
+  t_last_path = 1;
   return cudacore_conv_wgrad(p, (const float*)input->data, (const float*)doutput->data, out_f32(dfilter), s);
 }
 

@@ -96,8 +96,32 @@ const uint32_t* amax_tracked(const void* data) {
 // device-side primitives (inline PTX)
 // ------------------------------------------------------------------------------------------------
 constexpr int BM = 128;            // UMMA M (TMEM lanes)
-constexpr int BK = 64;             // fp16 elements of K per stage = one 128-byte swizzle row
 constexpr int kThreads = 320;
+// The two arithmetic modes differ only in the element type of the packed operands.  A stage always holds one
+// 128-byte swizzle row of K per tile row (K-major) or 128 bytes of M/N per K row (M/N-major), and is consumed by four
+// MMAs; the tile byte sizes are therefore the same in both modes and only the element counts change.
+enum { kArithF16 = 0, kArithTF32 = 1 };
+template <int AR> struct Arith;
+template <> struct Arith<kArithF16> {
+  typedef __half Elem;
+  static constexpr int kBK = 64;            // elements of K per stage (128 B)
+  static constexpr int kGW = 64;            // M/N-major operands: elements of M/N per 128-byte group row
+  static constexpr uint32_t kFormat = 0;    // instruction-descriptor operand format: f16
+  // M/N-major shared-memory descriptor: 128-byte swizzle with 16-byte atoms (layout type 2), 8-row K groups 1024 B apart
+  static constexpr uint32_t kMnLayout = 2, kMnSbo = 1024;
+};
+template <> struct Arith<kArithTF32> {
+  typedef float Elem;
+  static constexpr int kBK = 32;
+  static constexpr int kGW = 32;
+  static constexpr uint32_t kFormat = 2;    // tf32
+  // 32-bit M/N-major operands exist only with the 128-byte swizzle of 32-byte atoms (layout type 1): 4-row K groups
+  // 512 B apart; the tensor map of such an operand asks for the same swizzle
+  static constexpr uint32_t kMnLayout = 1, kMnSbo = 512;
+};
+static inline int bk_of(int ar) { return ar == kArithTF32 ? 32 : 64; }
+static inline int gw_of(int ar) { return ar == kArithTF32 ? 32 : 64; }
+static inline int elem_of(int ar) { return ar == kArithTF32 ? 4 : 2; }
 constexpr int kGroupIters = 4;     // stages accumulated in TMEM before the epilogue promotes them to registers
 constexpr long long kWaitCycles = 3000000000ll;   // ~1.5 s at 2 GHz: far beyond any legitimate wait
 
@@ -145,12 +169,21 @@ __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fe
 __device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+template <int AR>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (AR == kArithF16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+  }
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
@@ -173,12 +206,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, descriptor version 1 (Blackwell), 128-byte swizzle with 16-byte atoms
-// (layout type 2) for both majors:
-//   K-major operand : rows of 128 B (64 halves of K), 8-row groups 1024 B apart (SBO); LBO unused (= 16 B);
-//                     one MMA (K = 16) advances the start address by 32 B.
-//   MN-major operand: [64 K-rows][128 B = 64 halves of M/N] per column group; 8-row K groups 1024 B apart (SBO),
-//                     column groups 8192 B apart (LBO); one MMA (K = 16) advances the start address by 2048 B.
+// Shared-memory matrix descriptor, descriptor version 1 (Blackwell), 128-byte swizzle:
+//   K-major operand : rows of 128 B (64 halves / 32 floats of K), 16-byte atoms (layout type 2), 8-row groups 1024 B
+//                     apart (SBO); LBO unused (= 16 B); one MMA advances the start address by 32 B.
+//   MN-major operand: [K rows of one stage][128 B of M/N] per column group, column groups one stage of K rows apart
+//                     (LBO).  fp16: 16-byte atoms (layout type 2), 8-row K groups 1024 B apart (SBO), one MMA (K = 16)
+//                     advances the start address by 2048 B.  tf32: 32-byte atoms (layout type 1), 4-row K groups 512 B
+//                     apart, one MMA (K = 8) advances it by 1024 B.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type) {
   return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
          (1ull << 46) | ((uint64_t)layout_type << 61);
@@ -195,13 +229,19 @@ struct alignas(64) GemmParams {
   CUtensorMap a_hi, a_lo, b_hi, b_lo;
   int mode, a_mn, b_mn, epi;
   int M, N;                       // valid extents of the output tile grid
-  int m_tiles, n_tiles, tap_tiles, splits;
-  int k_iters;                    // stages per (tile, split)
-  int k_total;                    // stages of the whole reduction; the last split may be shorter
-  int chunks_per_tap;             // kModeConv: 32-channel chunks per tap
+  int m_tiles, n_tiles, tap_tiles;
+  int k_total;                    // stages of one output tile's whole reduction
+  // Schedule.  Tiles [0, full_tiles) are computed whole, round robin over the CTAs (whole waves).  The remaining
+  // tail_tiles tiles - a partial wave - either run whole as well (tail_share == 0) or have their
+  // tail_tiles * k_total stages cut into one contiguous range of tail_share stages per CTA, so that every SM does the
+  // same amount of work; a range may cover pieces of several tiles.  Each piece leaves its raw partial sums in a
+  // workspace slot and reduce_partials_kernel adds the pieces of a tile in a fixed order (no atomics: results are
+  // bit-identical from run to run).
+  int full_tiles, tail_tiles, tail_share, slots_per_cta;
+  float* workspace;               // [slot][BN columns][128 rows] fp32
+  int chunks_per_tap;             // kModeConv: K stages per tap
   int b_tap_pitch;                // kModeConv: columns per tap in the packed filter
   int ntaps;
-  int atomic;                     // epilogue adds into `out` (pre-zeroed) instead of storing
   float* out;
   const float* a_scale; const float* b_scale;   // device words: the power-of-two scales the packs were made with
   long long ldc;                  // kEpiRowMajor
@@ -219,15 +259,82 @@ struct alignas(64) GemmParams {
 
 template <int BN> struct SmemLayout {
   static constexpr int kStages = BN <= 96 ? 4 : 3;
-  static constexpr int kABytes = BM * BK * 2;           // 16 KiB
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kABytes = BM * 128;              // 16 KiB: 128 tile rows x one 128-byte swizzle row
+  static constexpr int kBBytes = BN * 128;
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;   // + slack to align to 1024
 };
 
-template <int BN>
-__global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_constant__ GemmParams p) {
+// One unit of a CTA's work: `kcount` stages of tile `tile` starting at stage k0.  slot < 0: the item is the tile's
+// whole reduction and its epilogue stores to the output; otherwise its partial sums go to that workspace slot.
+struct WorkItem { int tile, k0, kcount, slot; };
+// The sequence of items of this CTA; the three warp roles walk it independently and must see the same sequence.
+struct WorkIter {
+  int tile, u, u1, first_tail_tile;
+  __device__ __forceinline__ explicit WorkIter(const GemmParams& p) {
+    tile = blockIdx.x;
+    u = u1 = first_tail_tile = 0;
+    if (p.tail_share > 0) {
+      u = blockIdx.x * p.tail_share;
+      u1 = min(u + p.tail_share, p.tail_tiles * p.k_total);
+      first_tail_tile = u / p.k_total;
+    }
+  }
+  __device__ __forceinline__ bool next(const GemmParams& p, WorkItem& w) {
+    const int whole = p.tail_share > 0 ? p.full_tiles : p.full_tiles + p.tail_tiles;
+    if (tile < whole) {
+      w.tile = tile; w.k0 = 0; w.kcount = p.k_total; w.slot = -1;
+      tile += gridDim.x;
+      return true;
+    }
+    if (u < u1) {
+      const int t = u / p.k_total, k0 = u - t * p.k_total;
+      const int len = min(p.k_total - k0, u1 - u);
+      w.tile = p.full_tiles + t; w.k0 = k0; w.kcount = len;
+      w.slot = blockIdx.x * p.slots_per_cta + (t - first_tail_tile);
+      u += len;
+      return true;
+    }
+    return false;
+  }
+};
+// tile index -> coordinates; n fastest so consecutive CTAs share the A tile through L2
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& mt, int& nt, int& tap) {
+  nt = tile % p.n_tiles; tile /= p.n_tiles;
+  tap = tile % p.tap_tiles;
+  mt = tile / p.tap_tiles;
+}
+// Where row `row_in_tile` of tile (mt, tap) lands in the output: everything of the address but the column term.
+struct RowAddr { bool ok; long long base; uint32_t col_stride; };
+__device__ __forceinline__ RowAddr row_address(const GemmParams& p, int mt, int tap, int row_in_tile) {
+  const long long m = (long long)mt * BM + row_in_tile;
+  RowAddr r;
+  r.ok = m < p.M; r.base = 0; r.col_stride = 1;
+  if (p.epi == kEpiRowMajor) {
+    r.base = m * p.ldc;
+  } else if (p.epi == kEpiNchw) {
+    const int per_img = p.frame_h * p.frame_w;
+    const int img = (int)(m / per_img);
+    const int rem = (int)(m - (long long)img * per_img), i = rem / p.frame_w, j = rem - i * p.frame_w;
+    const int oi = i * p.out_sh + p.out_off_h, oj = j * p.out_sw + p.out_off_w;
+    r.ok = r.ok && i < p.valid_h && j < p.valid_w && oi >= 0 && oi < p.out_h && oj >= 0 && oj < p.out_w;
+    r.col_stride = (uint32_t)(p.out_h * p.out_w);
+    r.base = ((long long)img * p.out_c) * r.col_stride + (long long)oi * p.out_w + oj;
+  } else {   // kEpiWgrad: tile row -> (tap slot, input channel c), column n = output channel: out[(n * C + c) * ntaps + tap]
+    const int sl = row_in_tile / p.slot, c = mt * p.slot + row_in_tile - sl * p.slot, t = tap * p.taps_per_tile + sl;
+    r.ok = t < p.ntaps && c < p.M;
+    r.base = (long long)c * p.ntaps + t;
+    r.col_stride = (uint32_t)(p.M * p.ntaps);
+  }
+  return r;
+}
+
+template <int BN, int AR>
+__global__ void __launch_bounds__(kThreads, 1) gemm3x_kernel(const __grid_constant__ GemmParams p) {
+  using T = Arith<AR>;
+  constexpr int BK = T::kBK;
+  constexpr uint32_t kGroupStride = BK * 128;               // M/N-major operands: bytes between 128-byte-wide column groups
   constexpr int kTmemCols = 4 * BN <= 256 ? 256 : 512;      // two accumulators of 2*BN columns; the allocation is a power of two
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -240,7 +347,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = p.m_tiles * p.n_tiles * p.tap_tiles * p.splits;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -258,15 +364,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
   const uint32_t tmem_base = *tmem_slot;
   grid_dep_sync();          // everything above (barriers, TMEM) overlapped the tail of the kernel in front; operands are read below
 
-  // tile index -> coordinates; n fastest so consecutive CTAs share the A tile through L2
-  auto kcount_of = [&](int split) { return min(p.k_iters, p.k_total - split * p.k_iters); };
-  auto decode = [&](int tile, int& mt, int& nt, int& tap, int& split) {
-    split = tile % p.splits; tile /= p.splits;
-    nt = tile % p.n_tiles; tile /= p.n_tiles;
-    tap = tile % p.tap_tiles; tile /= p.tap_tiles;
-    mt = tile;
-  };
-
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
@@ -274,55 +371,56 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
       bool armed[L::kStages]; uint32_t armed_phase[L::kStages];
       for (int s = 0; s < L::kStages; ++s) { armed[s] = false; armed_phase[s] = 0; }
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int mt, nt, tap, split;
-        decode(tile, mt, nt, tap, split);
+      WorkIter iter(p);
+      WorkItem w;
+      while (ok && iter.next(p, w)) {
+        int mt, nt, tap;
+        decode_tile(p, w.tile, mt, nt, tap);
         const int m0 = mt * BM, n0 = nt * BN;
-        const int kcount = kcount_of(split);
-        for (int it = 0; it < kcount; ++it) {
+        for (int it = 0; it < w.kcount; ++it) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* st = smem + stage * L::kStageBytes;
           uint8_t *a_hi = st, *a_lo = st + L::kABytes, *b_hi = st + 2 * L::kABytes, *b_lo = b_hi + L::kBBytes;
           mbar_expect_tx(&full[stage], L::kStageBytes);
           armed[stage] = true; armed_phase[stage] = phase;
+          const int git = w.k0 + it;                  // stage index within the tile's reduction
           int a_col, a_row, b_col, b_row;
           if (p.mode == kModeConv) {
-            int git = split * p.k_iters + it;
             int t = git / p.chunks_per_tap, ch = git - t * p.chunks_per_tap;
             a_col = p.tap_col[t] + ch * BK; a_row = m0 + p.tap_off[t];
             b_col = p.tap_b[t] * p.b_tap_pitch + ch * BK; b_row = n0;
           } else if (p.mode == kModeWgrad) {
-            int krow = (split * p.k_iters + it) * BK;
+            int krow = git * BK;
             a_col = mt * p.slot; a_row = krow;      // per-box tap shift applied below
             b_col = n0; b_row = krow;
           } else {
-            int kk = (split * p.k_iters + it) * BK;
+            int kk = git * BK;
             if (p.a_mn) { a_col = m0; a_row = kk; } else { a_col = kk; a_row = m0; }
             if (p.b_mn) { b_col = n0; b_row = kk; } else { b_col = kk; b_row = n0; }
           }
-          // M/N-major operands come through a 3-D view {64 columns, rows, column groups}: one copy lands
-          // [groups][64 rows][128 B], the layout the M/N-major descriptor expects.
+          // M/N-major operands come through a 3-D view {group width, rows, column groups}: one copy lands
+          // [groups][BK rows][128 B], the layout the M/N-major descriptor expects.
           if (p.mode == kModeWgrad) {
             // One copy per tap slot; a slot past the last tap reads rows beyond the pack (the copy still completes
             // with its full byte count and fills zeros).
-            const int gps = p.slot >> 6;
+            const int gps = p.slot / T::kGW;
             for (int sl = 0; sl < p.taps_per_tile; ++sl) {
               int t = tap * p.taps_per_tile + sl;
               int row = t < p.ntaps ? a_row + p.tap_off[t] : 0x40000000;
-              int grp = (a_col + (t < p.ntaps ? p.tap_col[t] : 0)) >> 6;
-              tma_load_3d(a_hi + sl * gps * 8192, &p.a_hi, 0, row, grp, &full[stage]);
-              tma_load_3d(a_lo + sl * gps * 8192, &p.a_lo, 0, row, grp, &full[stage]);
+              int grp = (a_col + (t < p.ntaps ? p.tap_col[t] : 0)) / T::kGW;
+              tma_load_3d(a_hi + sl * gps * kGroupStride, &p.a_hi, 0, row, grp, &full[stage]);
+              tma_load_3d(a_lo + sl * gps * kGroupStride, &p.a_lo, 0, row, grp, &full[stage]);
             }
           } else if (p.a_mn) {
-            tma_load_3d(a_hi, &p.a_hi, 0, a_row, a_col >> 6, &full[stage]);
-            tma_load_3d(a_lo, &p.a_lo, 0, a_row, a_col >> 6, &full[stage]);
+            tma_load_3d(a_hi, &p.a_hi, 0, a_row, a_col / T::kGW, &full[stage]);
+            tma_load_3d(a_lo, &p.a_lo, 0, a_row, a_col / T::kGW, &full[stage]);
           } else {
             tma_load_2d(a_hi, &p.a_hi, a_col, a_row, &full[stage]);
             tma_load_2d(a_lo, &p.a_lo, a_col, a_row, &full[stage]);
           }
           if (p.b_mn) {
-            tma_load_3d(b_hi, &p.b_hi, 0, b_row, b_col >> 6, &full[stage]);
-            tma_load_3d(b_lo, &p.b_lo, 0, b_row, b_col >> 6, &full[stage]);
+            tma_load_3d(b_hi, &p.b_hi, 0, b_row, b_col / T::kGW, &full[stage]);
+            tma_load_3d(b_lo, &p.b_lo, 0, b_row, b_col / T::kGW, &full[stage]);
           } else {
             tma_load_2d(b_hi, &p.b_hi, b_col, b_row, &full[stage]);
             tma_load_2d(b_lo, &p.b_lo, b_col, b_row, &full[stage]);
@@ -343,37 +441,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
     // ===================== MMA issuer =====================
     if (lane == 0) {
       // The B stage holds [B_hi ; B_lo] back to back, so ONE instruction with N = 2*BN computes A_hi*B_hi (columns
-      // 0..BN-1) and A_hi*B_lo (columns BN..2BN-1); a second one with N = BN adds A_lo*B_hi.  Two instructions per
-      // K step instead of three: a tcgen05.mma of this size costs ~115 cycles to issue whatever its N.
-      // instruction descriptor: D = f32 (bits 4-5 = 1), A = B = f16 (format 0), majors, N >> 3 at bit 17, M >> 4 at bit 24
-      const uint32_t idesc_base = (1u << 4) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) | ((uint32_t)(BM >> 4) << 24);
+      // 0..BN-1) and A_hi*B_lo (columns BN..2BN-1); a second one with N = BN adds A_lo*B_hi to the second block.  The
+      // two small cross terms share a block on purpose: every accumulation into TMEM truncates the sum, an error
+      // proportional to the accumulator's magnitude, and the cross terms are 2^-11 of the main one, so the large
+      // accumulator sees one truncation per K step instead of two.
+      // instruction descriptor: D = f32 (bits 4-5 = 1), A format at bit 7, B format at bit 10, majors at bits 15 / 16,
+      // N >> 3 at bit 17, M >> 4 at bit 24
+      const uint32_t idesc_base = (1u << 4) | (T::kFormat << 7) | (T::kFormat << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
+                                  ((uint32_t)(BM >> 4) << 24);
       const uint32_t idesc_wide = idesc_base | ((uint32_t)((2 * BN) >> 3) << 17), idesc_narrow = idesc_base | ((uint32_t)(BN >> 3) << 17);
-      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
-      const uint32_t a_kstep = p.a_mn ? 2048u : 32u, b_kstep = p.b_mn ? 2048u : 32u;
-      const uint32_t a_sbo = 1024u, b_sbo = 1024u;
-      const uint32_t a_lt = 2u, b_lt = 2u;
+      // K-major: one MMA advances 32 bytes along the 128-byte row; M/N-major: one MMA covers K rows of 128 bytes each
+      // (16 rows of fp16, 8 of tf32), column groups kGroupStride apart
+      const uint32_t a_lbo = p.a_mn ? kGroupStride : 16u, b_lbo = p.b_mn ? kGroupStride : 16u;
+      const uint32_t a_kstep = p.a_mn ? kGroupStride / 4 : 32u, b_kstep = p.b_mn ? kGroupStride / 4 : 32u;
+      const uint32_t a_sbo = p.a_mn ? T::kMnSbo : 1024u, b_sbo = p.b_mn ? T::kMnSbo : 1024u;
+      const uint32_t a_lt = p.a_mn ? T::kMnLayout : 2u, b_lt = p.b_mn ? T::kMnLayout : 2u;
       int stage = 0; uint32_t phase = 0;
       int group = 0;            // accumulator groups issued so far (alternating TMEM buffers)
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int kcount = kcount_of(tile % p.splits);
-        for (int it0 = 0; it0 < kcount && ok; it0 += p.group_iters, ++group) {
+      WorkIter iter(p);
+      WorkItem w;
+      while (ok && iter.next(p, w)) {
+        for (int it0 = 0; it0 < w.kcount && ok; it0 += p.group_iters, ++group) {
           const int acc = group & 1;
           if (!mbar_wait(&acc_empty[acc], ((group >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t d_tmem = tmem_base + acc * 2 * BN;
-          const int it1 = min(it0 + p.group_iters, kcount);
+          const int it1 = min(it0 + p.group_iters, w.kcount);
           for (int it = it0; it < it1; ++it) {
             if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
             const uint32_t st = smem_u32(smem + stage * L::kStageBytes);
             const uint32_t a_hi = st, a_lo = st + L::kABytes, b_hi = st + 2 * L::kABytes;
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k) {
+            for (int k = 0; k < 4; ++k) {
               const uint64_t ah = umma_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lt), al = umma_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lt);
               const uint64_t bh = umma_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lt);      // N = 2*BN runs on into B_lo
-              umma_f16(d_tmem, ah, bh, idesc_wide, (it > it0 || k > 0) ? 1u : 0u);
-              umma_f16(d_tmem, al, bh, idesc_narrow, 1u);
+              umma<AR>(d_tmem, ah, bh, idesc_wide, (it > it0 || k > 0) ? 1u : 0u);
+              umma<AR>(d_tmem + BN, al, bh, idesc_narrow, 1u);
             }
             tcgen05_commit(&empty[stage]);       // frees the stage once the MMAs above have read it
             if (++stage == L::kStages) { stage = 0; phase ^= 1; }
@@ -394,35 +499,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
     const float inv_scale = (1.f / __ldg(p.a_scale)) * (1.f / __ldg(p.b_scale));     // powers of two: exact
     int group = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      int mt, nt, tap, split;
-      decode(tile, mt, nt, tap, split);
-      const int kcount = kcount_of(split);
-      const long long m = (long long)mt * BM + row_in_tile;
+    WorkIter iter(p);
+    WorkItem w;
+    while (ok && iter.next(p, w)) {
+      int mt, nt, tap;
+      decode_tile(p, w.tile, mt, nt, tap);
+      const int kcount = w.kcount;
       const int n0 = nt * BN + half * HC;
-      // per-row output address (everything but the column term)
-      bool row_ok = m < p.M;
-      long long base = 0;
-      uint32_t col_stride = 1;
-      if (p.epi == kEpiRowMajor) {
-        base = m * p.ldc;
-      } else if (p.epi == kEpiNchw) {
-        int per_img = p.frame_h * p.frame_w;
-        int img = (int)(m / per_img);
-        int rem = (int)(m - (long long)img * per_img), i = rem / p.frame_w, j = rem - i * p.frame_w;
-        int oi = i * p.out_sh + p.out_off_h, oj = j * p.out_sw + p.out_off_w;
-        row_ok = row_ok && i < p.valid_h && j < p.valid_w && oi >= 0 && oi < p.out_h && oj >= 0 && oj < p.out_w;
-        col_stride = (uint32_t)(p.out_h * p.out_w);
-        base = ((long long)img * p.out_c) * col_stride + (long long)oi * p.out_w + oj;
-      } else {   // kEpiWgrad: tile row -> (tap slot, input channel c), column n = output channel: out[(n * C + c) * ntaps + tap]
-        int sl = row_in_tile / p.slot, c = mt * p.slot + row_in_tile - sl * p.slot, t = tap * p.taps_per_tile + sl;
-        row_ok = t < p.ntaps && c < p.M;
-        base = (long long)c * p.ntaps + t;
-        col_stride = (uint32_t)(p.M * p.ntaps);
-      }
-      float* const row_out = p.out + base + (long long)n0 * col_stride;
+      const RowAddr ra = row_address(p, mt, tap, row_in_tile);
+      const bool row_ok = ra.ok;
+      const uint32_t col_stride = ra.col_stride;
+      float* const row_out = p.out + ra.base + (long long)n0 * col_stride;
       const int ncols = max(0, min(HC, p.N - n0));
-      const bool vec_ok = p.epi == kEpiRowMajor && !p.atomic && ((base + n0) & 3) == 0;
+      const bool vec_ok = p.epi == kEpiRowMajor && ((ra.base + n0) & 3) == 0;
 
       auto wait_group = [&](int acc_buf, int grp) -> bool {   // lane 0 polls, the warp follows (keeps .sync.aligned loads converged)
         int got = lane == 0 ? (int)mbar_wait(&acc_full[acc_buf], (grp >> 1) & 1, abort_flag) : 1;
@@ -437,23 +526,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
           float4* dst = reinterpret_cast<float4*>(row_out + c0);
 #pragma unroll
           for (int q = 0; q < NC / 4; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        } else if (c0 + NC <= ncols && !p.atomic) {
+        } else if (c0 + NC <= ncols) {
           float* dst = row_out + (size_t)((uint32_t)c0 * col_stride);
 #pragma unroll
           for (int q = 0; q < NC; ++q) dst[(size_t)((uint32_t)q * col_stride)] = v[q];
         } else {
           float* dst = row_out + (size_t)((uint32_t)c0 * col_stride);
 #pragma unroll
-          for (int q = 0; q < NC; ++q) {
-            if (c0 + q < ncols) {
-              float* d = dst + (size_t)((uint32_t)q * col_stride);
-              if (p.atomic) atomicAdd(d, v[q]); else *d = v[q];
-            }
-          }
+          for (int q = 0; q < NC; ++q)
+            if (c0 + q < ncols) dst[(size_t)((uint32_t)q * col_stride)] = v[q];
         }
       };
 
-      if (kcount <= p.group_iters) {
+      if (w.slot < 0 && kcount <= p.group_iters) {
         // One accumulator group: stream TMEM straight to memory, 32 columns at a time.
         const int acc = group & 1;
         if (!wait_group(acc, group)) { ok = false; break; }
@@ -479,7 +564,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
       }
 
       // The tensor core accumulates with truncation, so a long chain of MMAs into one TMEM accumulator
-      // drifts; each group of kGroupIters stages is therefore accumulated in TMEM on its own and promoted
+      // drifts; each group of group_iters stages is therefore accumulated in TMEM on its own and promoted
       // here into fp32 registers with round-to-nearest adds.
       float accv[HC];
 #pragma unroll
@@ -492,8 +577,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
 #pragma unroll
         for (int c0 = 0; c0 < HC; c0 += 16) {
           float v1[16], v2[16];
-          tmem_ld16(t_base + c0, v1);              // A_hi*B_hi + A_lo*B_hi
-          tmem_ld16(t_base + BN + c0, v2);         // A_hi*B_lo
+          tmem_ld16(t_base + c0, v1);              // A_hi*B_hi
+          tmem_ld16(t_base + BN + c0, v2);         // A_hi*B_lo + A_lo*B_hi
           tmem_ld_wait();
 #pragma unroll
           for (int q = 0; q < 16; ++q) accv[c0 + q] += v1[q] + v2[q];
@@ -503,6 +588,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
       }
       if (!ok) break;
+      if (w.slot >= 0) {
+        // a piece of a split tile: raw partial sums to the workspace, [column][row] so that a warp's 32 rows coalesce
+        float* ws = p.workspace + ((size_t)w.slot * BN + half * HC) * BM + row_in_tile;
+#pragma unroll
+        for (int q = 0; q < HC; ++q) ws[(size_t)q * BM] = accv[q];
+        continue;
+      }
 #pragma unroll
       for (int q = 0; q < HC; ++q) accv[q] *= inv_scale;
       store_cols(accv, 0, std::integral_constant<int, HC>{});
@@ -517,6 +609,50 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3xf16_kernel(const __grid_con
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
+}
+
+// Adds up the pieces of every split tile (the tail of the schedule) in a fixed order and writes the result where the
+// GEMM's own epilogue would have.  grid (tail_tiles, BN / kReduceCols), block (128 rows, kReduceWays): the pieces of a
+// tile are dealt round robin to the kReduceWays row groups, each adds its share in piece order, and the row group 0
+// adds the kReduceWays subtotals in order - the same order every run, so the result is bit-reproducible.
+constexpr int kReduceCols = 4, kReduceWays = 8;
+template <int BN>
+__global__ void __launch_bounds__(BM * kReduceWays) reduce_partials_kernel(const __grid_constant__ GemmParams p) {
+  __shared__ float part[kReduceWays][kReduceCols][BM];
+  grid_dep_sync();
+  const int t = blockIdx.x;                            // tail tile
+  int mt, nt, tap;
+  decode_tile(p, p.full_tiles + t, mt, nt, tap);
+  const int row = threadIdx.x, way = threadIdx.y;
+  // CTA g of the GEMM covered stages [g * share, (g + 1) * share) of the tail; its first piece belongs to tail tile
+  // (g * share) / k_total and its pieces sit in consecutive workspace slots
+  const int g_first = (int)(((long long)t * p.k_total) / p.tail_share);
+  const int g_last = (int)((((long long)t + 1) * p.k_total - 1) / p.tail_share);
+  const int c_begin = blockIdx.y * kReduceCols;
+  float sum[kReduceCols];
+#pragma unroll
+  for (int q = 0; q < kReduceCols; ++q) sum[q] = 0.f;
+  for (int g = g_first + way; g <= g_last; g += kReduceWays) {
+    const int slot = g * p.slots_per_cta + (t - (int)(((long long)g * p.tail_share) / p.k_total));
+    const float* ws = p.workspace + ((size_t)slot * BN + c_begin) * BM + row;
+#pragma unroll
+    for (int q = 0; q < kReduceCols; ++q) sum[q] += ws[(size_t)q * BM];
+  }
+#pragma unroll
+  for (int q = 0; q < kReduceCols; ++q) part[way][q][row] = sum[q];
+  __syncthreads();
+  if (way != 0) return;
+  const RowAddr ra = row_address(p, mt, tap, row);
+  if (!ra.ok) return;
+  const float inv_scale = (1.f / __ldg(p.a_scale)) * (1.f / __ldg(p.b_scale));
+#pragma unroll
+  for (int q = 0; q < kReduceCols; ++q) {
+    float v = sum[q];
+#pragma unroll
+    for (int w2 = 1; w2 < kReduceWays; ++w2) v += part[w2][q][row];
+    const int n = nt * BN + c_begin + q;
+    if (n < p.N) p.out[ra.base + (long long)n * ra.col_stride] = v * inv_scale;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -559,21 +695,54 @@ __device__ __forceinline__ float scale_from_amax(uint32_t bits) {
   se = se > 120 ? 120 : (se < -120 ? -120 : se);
   return __uint_as_float((uint32_t)(se + 127) << 23);
 }
+// A tf32 pack is not scaled: its ScaleRef has no amax word and the scale in force is 1.
 __device__ __forceinline__ float pack_scale(const ScaleRef& r, bool first_thread) {
-  const float s = scale_from_amax(__ldg(r.amax_cur));
-  if (first_thread) { *r.scale = s; *r.amax_next = 0; }
+  const float s = r.amax_cur ? scale_from_amax(__ldg(r.amax_cur)) : 1.f;
+  if (first_thread) { *r.scale = s; if (r.amax_next) *r.amax_next = 0; }
   return s;
 }
-__device__ __forceinline__ void split_f16(float a, __half& hi, __half& lo) {
+// hi / lo pair of one value: fp16 (22 mantissa bits together) or tf32 (round to nearest, low 13 bits zero)
+__device__ __forceinline__ void split_pair(float a, __half& hi, __half& lo) {
   hi = __float2half_rn(a);
   lo = __float2half_rn(a - __half2float(hi));
+}
+__device__ __forceinline__ float tf32_rn(float a) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(a));
+  return __uint_as_float(r);
+}
+__device__ __forceinline__ void split_pair(float a, float& hi, float& lo) {
+  hi = tf32_rn(a);
+  lo = tf32_rn(a - hi);
+}
+// eight consecutive values -> eight hi and eight lo elements at hi + o, lo + o (o a multiple of 8): 16-byte stores
+__device__ __forceinline__ void store8(__half* hi, __half* lo, long long o, const float* v) {
+  __align__(16) __half2 h[4];
+  __align__(16) __half2 l[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+    const float2 hf = __half22float2(h[e]);
+    l[e] = __floats2half2_rn(v[2 * e] - hf.x, v[2 * e + 1] - hf.y);
+  }
+  *reinterpret_cast<uint4*>(hi + o) = *reinterpret_cast<const uint4*>(h);
+  *reinterpret_cast<uint4*>(lo + o) = *reinterpret_cast<const uint4*>(l);
+}
+__device__ __forceinline__ void store8(float* hi, float* lo, long long o, const float* v) {
+  float h[8], l[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) split_pair(v[e], h[e], l[e]);
+  float4* hp = reinterpret_cast<float4*>(hi + o);
+  float4* lp = reinterpret_cast<float4*>(lo + o);
+  hp[0] = make_float4(h[0], h[1], h[2], h[3]); hp[1] = make_float4(h[4], h[5], h[6], h[7]);
+  lp[0] = make_float4(l[0], l[1], l[2], l[3]); lp[1] = make_float4(l[4], l[5], l[6], l[7]);
 }
 
 // rows x cols row-major (pitch src_ld) -> hi/lo with pitch dst_ld.  VEC8: eight consecutive columns per thread
 // (two 16-byte loads, one 16-byte store each of hi and lo); needs cols and src_ld multiples of 8 and a 16-byte
 // aligned source (the packs' pitch is a multiple of 64).
-template <bool VEC8>
-__global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restrict__ src, long long src_ld, __half* __restrict__ hi, __half* __restrict__ lo,
+template <bool VEC8, class E>
+__global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restrict__ src, long long src_ld, E* __restrict__ hi, E* __restrict__ lo,
                                                           long long dst_ld, long long rows, long long cols, ScaleRef sr) {
   grid_dep_sync();
   const float sc = pack_scale(sr, blockIdx.x == 0 && threadIdx.x == 0);
@@ -585,23 +754,14 @@ __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restric
       const float4 a = __ldg(reinterpret_cast<const float4*>(src + r * src_ld + c));
       const float4 b = __ldg(reinterpret_cast<const float4*>(src + r * src_ld + c) + 1);
       const float v[8] = {a.x * sc, a.y * sc, a.z * sc, a.w * sc, b.x * sc, b.y * sc, b.z * sc, b.w * sc};
-      __align__(16) __half2 h[4];
-      __align__(16) __half2 l[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        h[e] = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-        const float2 hf = __half22float2(h[e]);
-        l[e] = __floats2half2_rn(v[2 * e] - hf.x, v[2 * e + 1] - hf.y);
-      }
-      *reinterpret_cast<uint4*>(hi + r * dst_ld + c) = *reinterpret_cast<const uint4*>(h);
-      *reinterpret_cast<uint4*>(lo + r * dst_ld + c) = *reinterpret_cast<const uint4*>(l);
+      store8(hi, lo, r * dst_ld + c, v);
     }
   } else {
     const long long total = rows * cols;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
       long long r = i / cols, c = i - r * cols;
-      __half h, l;
-      split_f16(src[r * src_ld + c] * sc, h, l);
+      E h, l;
+      split_pair(src[r * src_ld + c] * sc, h, l);
       hi[r * dst_ld + c] = h;
       lo[r * dst_ld + c] = l;
     }
@@ -615,8 +775,8 @@ __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restric
 // row through shared memory: reads run along w (TC/8 independent loads per thread in flight), writes along c as
 // 16-byte vectors (8 halves) of hi and of lo.
 struct PackGeom { int N, C, H, W, frame_h, frame_w, off_h, off_w, sh, sw, pitch, dst_c0, c_limit; };
-template <int TC>
-__global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, __half* __restrict__ hi, __half* __restrict__ lo, PackGeom g, ScaleRef sr) {
+template <int TC, class E>
+__global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, E* __restrict__ hi, E* __restrict__ lo, PackGeom g, ScaleRef sr) {
   grid_dep_sync();
   // tile[c][f ^ (c / 8)]: the XOR keeps both phases free of bank conflicts (stores: 32 lanes = 32 frame positions
   // of one channel; loads: lanes = 8-channel groups of a few positions that are TC/8 apart)
@@ -660,28 +820,23 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
     for (int jb = ty; jb < LPP; jb += 8) {
       const int ff = jb + px * LPP, f = f0 + ff;
       if (f < fsize && c < g.c_limit) {
-        __align__(16) __half2 h[4];
-        __align__(16) __half2 l[4];
+        float v[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float a0 = tile[cl + 2 * e][ff ^ grp], a1 = tile[cl + 2 * e + 1][ff ^ grp];
-          h[e] = __floats2half2_rn(a0, a1);
-          const float2 hf = __half22float2(h[e]);
-          l[e] = __floats2half2_rn(a0 - hf.x, a1 - hf.y);
-        }
-        const long long o = ((long long)n * fsize + f) * g.pitch + g.dst_c0 + c;
-        *reinterpret_cast<uint4*>(hi + o) = *reinterpret_cast<const uint4*>(h);
-        *reinterpret_cast<uint4*>(lo + o) = *reinterpret_cast<const uint4*>(l);
+        for (int e = 0; e < 8; ++e) v[e] = tile[cl + e][ff ^ grp];
+        store8(hi, lo, ((long long)n * fsize + f) * g.pitch + g.dst_c0 + c, v);
       }
     }
   }
 }
 
+__device__ __forceinline__ void store_two(__half* p, __half a, __half b) { *reinterpret_cast<__half2*>(p) = __halves2half2(a, b); }
+__device__ __forceinline__ void store_two(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
 // NCHW activations -> explicit patch matrix [N*P*Q][pitch], column (c*R + r)*S + s = the filter's own flat index
 // within one output channel, so the convolution becomes a 1x1 one over C*R*S "channels".  Used where the
 // channel count is too small to fill a 64-wide reduction chunk per tap (first layers, C = 3).
 struct PatchGeom { int N, C, H, W, R, S, P, Q, sh, sw, pad_h, pad_w, cols, pitch; };
-__global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restrict__ src, __half* __restrict__ hi, __half* __restrict__ lo, PatchGeom g, ScaleRef sr) {
+template <class E>
+__global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restrict__ src, E* __restrict__ hi, E* __restrict__ lo, PatchGeom g, ScaleRef sr) {
   grid_dep_sync();
   // column -> (source offset relative to the window origin, r, s), the same for every row
   __shared__ int col_off[1024];
@@ -702,8 +857,8 @@ __global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restri
     const int i0 = pp * g.sh - g.pad_h, j0 = qq * g.sw - g.pad_w;
     const float* base = src + ((long long)n * g.C * g.H + i0) * g.W + j0;
     const bool interior = i0 >= 0 && i0 + g.R <= g.H && j0 >= 0 && j0 + g.S <= g.W;
-    __half2* h_row = reinterpret_cast<__half2*>(hi + row * g.pitch);
-    __half2* l_row = reinterpret_cast<__half2*>(lo + row * g.pitch);
+    E* h_row = hi + row * g.pitch;
+    E* l_row = lo + row * g.pitch;
     for (int col2 = lane; col2 < g.pitch / 2; col2 += 32) {        // two columns per lane
       float a[2];
       if (interior) {          // the whole window lies inside the image (uniform over the warp): no per-tap range checks
@@ -723,18 +878,19 @@ __global__ void __launch_bounds__(256) pack_patches_kernel(const float* __restri
           }
         }
       }
-      __half h0, l0, h1, l1;
-      split_f16(a[0], h0, l0);
-      split_f16(a[1], h1, l1);
-      h_row[col2] = __halves2half2(h0, h1);
-      l_row[col2] = __halves2half2(l0, l1);
+      E h0, l0, h1, l1;
+      split_pair(a[0], h0, l0);
+      split_pair(a[1], h1, l1);
+      store_two(h_row + 2 * col2, h0, h1);
+      store_two(l_row + 2 * col2, l0, l1);
     }
   }
 }
 
 // filters [K][C][R][S] -> forward pack [K][tap][cpad] (flip = 0) or backward-data pack [C][tap'][kpad] (flip = 1,
 // tap' = (R-1-r)*S + (S-1-s)), zero in the channel padding.
-__global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restrict__ w, __half* __restrict__ hi, __half* __restrict__ lo,
+template <class E>
+__global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restrict__ w, E* __restrict__ hi, E* __restrict__ lo,
                                                           int K, int C, int R, int S, int flip, int inner_pad, ScaleRef sr) {
   grid_dep_sync();
   const float sc = pack_scale(sr, blockIdx.x == 0 && threadIdx.x == 0);
@@ -751,8 +907,8 @@ __global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restric
       int src_tap = flip ? (taps - 1 - tap) : tap;
       a = w[((long long)k * C + c) * taps + src_tap] * sc;
     }
-    __half h, l;
-    split_f16(a, h, l);
+    E h, l;
+    split_pair(a, h, l);
     hi[idx] = h; lo[idx] = l;
   }
 }
@@ -760,8 +916,9 @@ __global__ void __launch_bounds__(256) pack_filter_kernel(const float* __restric
 // Both filter packs of one convolution in a single launch (the weights do not change between the forward and the
 // backward-data call of a step, so the second pack rides along with the first): element idx of the forward pack and
 // element idx of the backward-data pack per thread.
-__global__ void __launch_bounds__(256) pack_filter_pair_kernel(const float* __restrict__ w, __half* __restrict__ hi_f, __half* __restrict__ lo_f,
-                                                               __half* __restrict__ hi_d, __half* __restrict__ lo_d, int K, int C, int R, int S,
+template <class E>
+__global__ void __launch_bounds__(256) pack_filter_pair_kernel(const float* __restrict__ w, E* __restrict__ hi_f, E* __restrict__ lo_f,
+                                                               E* __restrict__ hi_d, E* __restrict__ lo_d, int K, int C, int R, int S,
                                                                int pad_f, int pad_d, ScaleRef sr, float* __restrict__ scale_d) {
   grid_dep_sync();
   const bool first = blockIdx.x == 0 && threadIdx.x == 0;
@@ -776,8 +933,8 @@ __global__ void __launch_bounds__(256) pack_filter_pair_kernel(const float* __re
       long long t2 = idx / pad_f;
       int tap = (int)(t2 % taps), k = (int)(t2 / taps);
       float a = in < C ? w[((long long)k * C + in) * taps + tap] * sc : 0.f;
-      __half h, l;
-      split_f16(a, h, l);
+      E h, l;
+      split_pair(a, h, l);
       hi_f[idx] = h; lo_f[idx] = l;
     }
     if (idx < total_d) {
@@ -785,8 +942,8 @@ __global__ void __launch_bounds__(256) pack_filter_pair_kernel(const float* __re
       long long t2 = idx / pad_d;
       int tap = (int)(t2 % taps), c = (int)(t2 / taps);
       float a = in < K ? w[((long long)in * C + c) * taps + (taps - 1 - tap)] * sc : 0.f;
-      __half h, l;
-      split_f16(a, h, l);
+      E h, l;
+      split_pair(a, h, l);
       hi_d[idx] = h; lo_d[idx] = l;
     }
   }
@@ -806,83 +963,142 @@ static EncodeTiledFn encode_fn() {
   }();
   return fn;
 }
+static inline CUtensorMapDataType map_type(int ar) { return ar == kArithTF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16; }
 
-// 2-D fp16 row-major [rows][cols] with `pitch` halves per row; box = 64 cols (128 B) x box_rows rows, 128-byte swizzle.
-static int make_map(CUtensorMap* m, const __half* base, long long rows, long long cols, long long pitch, int box_rows) {
+// 2-D row-major [rows][cols] with `pitch` elements per row; box = one 128-byte row of K x box_rows rows, 128-byte swizzle.
+static int make_map(CUtensorMap* m, int ar, const void* base, long long rows, long long cols, long long pitch, int box_rows) {
   EncodeTiledFn fn = encode_fn();
   TF_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch * elem_of(ar)};
+  cuuint32_t box[2] = {(cuuint32_t)bk_of(ar), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = fn(m, map_type(ar), 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with %d (rows %lld cols %lld pitch %lld)", (int)r, rows, cols, pitch);
   return 0;
 }
-// M/N-major operand: 3-D view {64 columns, rows, pitch / 64 column groups} with a box of `groups` groups x 64 rows.
-// The pack's pitch is a multiple of 64, so every group lies inside the allocation; columns past the logical
-// width only reach output rows / columns that the epilogue masks.
-static int make_map_mn(CUtensorMap* m, const __half* base, long long rows, long long pitch, int groups) {
+// M/N-major operand: 3-D view {group width, rows, pitch / group width column groups} (a group is 128 bytes of M/N) with
+// a box of `tile_cols` columns x one stage of K rows.  The pack's pitch is a multiple of 64 elements, so every group lies
+// inside the allocation; columns past the logical width only reach output rows / columns that the epilogue masks.
+static int make_map_mn(CUtensorMap* m, int ar, const void* base, long long rows, long long pitch, int tile_cols) {
   EncodeTiledFn fn = encode_fn();
   TF_REQUIRE(fn, "cuTensorMapEncodeTiled is not available from this driver");
-  TF_REQUIRE(pitch % 64 == 0, "M/N-major operand pitch %lld is not a multiple of 64", pitch);
-  cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(pitch / 64)};
-  cuuint64_t strides[2] = {(cuuint64_t)pitch * 2, 128};
-  cuuint32_t box[3] = {64, (cuuint32_t)BK, (cuuint32_t)groups};
+  const int gw = gw_of(ar);
+  TF_REQUIRE(pitch % gw == 0 && tile_cols % gw == 0, "M/N-major operand: pitch %lld / tile width %d are not multiples of %d", pitch, tile_cols, gw);
+  cuuint64_t dims[3] = {(cuuint64_t)gw, (cuuint64_t)rows, (cuuint64_t)(pitch / gw)};
+  cuuint64_t strides[2] = {(cuuint64_t)pitch * elem_of(ar), 128};
+  cuuint32_t box[3] = {(cuuint32_t)gw, (cuuint32_t)bk_of(ar), (cuuint32_t)(tile_cols / gw)};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  TF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (3-D) failed with %d (rows %lld pitch %lld groups %d)", (int)r, rows, pitch, groups);
+  CUresult r = fn(m, map_type(ar), 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  ar == kArithTF32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (3-D) failed with %d (rows %lld pitch %lld tile %d)", (int)r, rows, pitch, tile_cols);
   return 0;
 }
 
+static std::mutex g_tc_mu;      // guards the lazily created process-wide state below
 static int* error_word() {      // mapped pinned word: the kernels raise it, the host polls it for free
   static int* host = nullptr;
   static int* dev = nullptr;
+  std::lock_guard<std::mutex> lk(g_tc_mu);
   if (!host) {
-    if (cudaHostAlloc((void**)&host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (cudaHostAlloc((void**)&host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) { cudaGetLastError(); host = nullptr; return nullptr; }
     *host = 0;
     if (cudaHostGetDevicePointer((void**)&dev, host, 0) != cudaSuccess) { cudaGetLastError(); dev = nullptr; }
   }
   return dev;
 }
 static int* error_word_host() {
-  static int* host = nullptr;
-  if (!host) {
+  static std::atomic<int*> host{nullptr};
+  int* h = host.load(std::memory_order_acquire);
+  if (!h) {
     int* dev = error_word();
     if (!dev) return nullptr;
     cudaPointerAttributes at;
-    if (cudaPointerGetAttributes(&at, dev) == cudaSuccess) host = (int*)at.hostPointer;
+    if (cudaPointerGetAttributes(&at, dev) == cudaSuccess) { h = (int*)at.hostPointer; host.store(h, std::memory_order_release); }
   }
-  return host;
+  return h;
 }
-int tensor_path_error() { int* h = error_word_host(); return h ? *h : 0; }
+int tensor_path_error() { int* h = error_word_host(); return h ? *(volatile int*)h : 0; }
+void tensor_path_error_clear() { int* h = error_word_host(); if (h) *(volatile int*)h = 0; }
 
-static bool g_attr_done[3] = {false, false, false};
-template <int BN> static int launch_gemm(const GemmParams& p, cudaStream_t s, double flops, const char* what) {
+// Arithmetic of the tensor path: 0 = 3xFP16 (scaled fp16 hi/lo pairs, kind::f16), 1 = 3xTF32 (tf32 hi/lo pairs, kind::tf32).
+static std::atomic<int> g_arith{[] { const char* e = getenv("TINYFLOW_ARITH"); return (e && (!strcmp(e, "3xtf32") || !strcmp(e, "1"))) ? 1 : 0; }()};
+int tensor_arithmetic() { return g_arith.load(std::memory_order_relaxed); }
+void set_tensor_arithmetic(int a) { g_arith.store(a, std::memory_order_relaxed); }
+
+// ---- schedule: whole waves of tiles, then the partial wave cut into equal per-CTA ranges of stages -------------------
+// Costs are in units of one stage of one tile.  Splitting the tail pays a fixed price per CTA (the partial sums make a
+// round trip through the workspace and a second kernel adds them), so it is taken only when the tail is clearly
+// unbalanced and its reductions are long enough to share.
+static float g_tail_gain = [] { const char* e = getenv("TINYFLOW_TAIL_GAIN"); return e ? (float)atof(e) : 0.9f; }();
+static float g_tail_cost = [] { const char* e = getenv("TINYFLOW_TAIL_COST"); return e ? (float)atof(e) : 12.f; }();     // workspace round trip + second kernel, in stages
+static int plan_schedule(GemmParams& g, int bn, cudaStream_t s, int* oom) {
+  const int sms = device_sm_count();
+  const int tiles = g.m_tiles * g.n_tiles * g.tap_tiles;
+  g.full_tiles = tiles; g.tail_tiles = 0; g.tail_share = 0; g.slots_per_cta = 0; g.workspace = nullptr;
+  const int rem = tiles % sms;
+  static const bool no_split = getenv("TINYFLOW_NO_TAIL_SPLIT") != nullptr;
+  if (rem == 0 || g.k_total < 8 || no_split) return 0;
+  const long long units = (long long)rem * g.k_total;
+  int share = (int)((units + sms - 1) / sms);
+  if (share < 4) share = 4;                                   // shorter pieces are all overhead
+  const double whole = g.k_total + 8.0, split = share + 8.0 + g_tail_cost;
+  if (split >= g_tail_gain * whole) return 0;
+  g.full_tiles = tiles - rem; g.tail_tiles = rem; g.tail_share = share;
+  g.slots_per_cta = (share - 1 + g.k_total - 1) / g.k_total + 1;       // tiles a range of `share` stages can touch
+  const int ctas = (int)((units + share - 1) / share);
+  const size_t bytes = (size_t)ctas * g.slots_per_cta * bn * BM * sizeof(float);
+  g.workspace = (float*)persistent_scratch(1, bytes);
+  if (!g.workspace) { if (oom) *oom = bytes > 0x7fffffffu ? 0x7fffffff : (int)bytes; return 1; }
+  (void)s;
+  return 0;
+}
+
+static bool g_attr_done[2][3] = {{false, false, false}, {false, false, false}};
+template <int BN, int AR> static int launch_gemm(const GemmParams& p, cudaStream_t s, double flops, const char* what) {
   using L = SmemLayout<BN>;
   constexpr int slot = BN == 64 ? 0 : (BN == 128 ? 1 : 2);
-  if (!g_attr_done[slot]) {
-    TF_CUDA(cudaFuncSetAttribute(gemm3xf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    g_attr_done[slot] = true;
+  {
+    std::lock_guard<std::mutex> lk(g_tc_mu);
+    if (!g_attr_done[AR][slot]) {
+      TF_CUDA(cudaFuncSetAttribute(gemm3x_kernel<BN, AR>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      g_attr_done[AR][slot] = true;
+    }
   }
   TF_REQUIRE(tensor_path_error() == 0, "%s: an earlier tensor-core kernel timed out on a barrier; refusing to launch", what);
   static const int group_iters = getenv("TINYFLOW_GROUP_ITERS") ? atoi(getenv("TINYFLOW_GROUP_ITERS")) : kGroupIters;
   const_cast<GemmParams&>(p).group_iters = group_iters > 0 ? group_iters : kGroupIters;
-  int tiles = p.m_tiles * p.n_tiles * p.tap_tiles * p.splits;
-  int grid = tiles < device_sm_count() ? tiles : device_sm_count();
+  const int sms = device_sm_count();
+  const int tiles = p.full_tiles + p.tail_tiles;
+  int grid = tiles < sms ? tiles : sms;
+  if (p.tail_share > 0) {
+    const int ctas = (int)(((long long)p.tail_tiles * p.k_total + p.tail_share - 1) / p.tail_share);
+    grid = p.full_tiles > 0 ? sms : ctas;
+  }
   note_compute_stream(s);
   static const bool detail = getenv("TINYFLOW_TIMING_DETAIL") != nullptr;    // one timing row per distinct problem shape
-  char name[160];
-  if (detail) snprintf(name, sizeof(name), "gemm3xf16 mode%d M%d N%d kiters%d taps%d splits%d bn%d tiles%d %s", p.mode, p.M, p.N, p.k_iters, p.tap_tiles, p.splits, BN, tiles, what + 5);
-  KernelTimer kt(detail ? name : "gemm3xf16_tcgen05", s, flops, 0, 1);
-  launch_dep(gemm3xf16_kernel<BN>, dim3(grid), dim3(kThreads), (size_t)L::kTotal, s, p);
+  char name[192];
+  if (detail) snprintf(name, sizeof(name), "gemm3x%s mode%d M%d N%d ktotal%d taps%d bn%d tiles%d tail%d share%d %s", AR == kArithTF32 ? "tf32" : "f16", p.mode, p.M,
+                       p.N, p.k_total, p.tap_tiles, BN, tiles, p.tail_tiles, p.tail_share, what + 5);
+  KernelTimer kt(detail ? name : (AR == kArithTF32 ? "gemm3xtf32_tcgen05" : "gemm3xf16_tcgen05"), s, flops, 0, 1);
+  launch_dep(gemm3x_kernel<BN, AR>, dim3(grid), dim3(kThreads), (size_t)L::kTotal, s, p);
   TF_AFTER(s, what);
+  if (p.tail_share > 0) {
+    launch_dep(reduce_partials_kernel<BN>, dim3(p.tail_tiles, BN / kReduceCols), dim3(BM, kReduceWays), 0, s, p);
+    TF_AFTER(s, what);
+  }
   return 0;
 }
-static int launch_gemm_bn(int bn, const GemmParams& p, cudaStream_t s, double flops, const char* what) {
-  return bn == 64 ? launch_gemm<64>(p, s, flops, what) : bn == 96 ? launch_gemm<96>(p, s, flops, what) : launch_gemm<128>(p, s, flops, what);
+template <int AR> static int launch_gemm_ar(int bn, const GemmParams& p, cudaStream_t s, double flops, const char* what) {
+  return bn == 64 ? launch_gemm<64, AR>(p, s, flops, what) : bn == 96 ? launch_gemm<96, AR>(p, s, flops, what) : launch_gemm<128, AR>(p, s, flops, what);
+}
+// Plans the schedule (which may need workspace) and launches.  Returns 0 on success, -1 on error, 1 when the workspace
+// could not be allocated (*oom holds the byte count).
+static int launch_gemm_bn(int bn, int ar, GemmParams& p, cudaStream_t s, double flops, const char* what, int* oom) {
+  if (int rc = plan_schedule(p, bn, s, oom)) return rc;
+  return ar == kArithTF32 ? launch_gemm_ar<kArithTF32>(bn, p, s, flops, what) : launch_gemm_ar<kArithF16>(bn, p, s, flops, what);
 }
 // N-tile width.  M/N-major B operands come in 64-column groups, so they take 64 or 128; K-major ones may also take
 // 96, which wastes less on widths such as 96, 160, 192 or 288.
@@ -895,26 +1111,27 @@ static inline int pick_bn(long long n, bool b_k_major = false) {
 static inline long long round_up(long long a, long long b) { return (a + b - 1) / b * b; }
 
 struct Pack {           // a packed operand living in pooled device memory
-  __half* hi = nullptr; __half* lo = nullptr;
+  void* hi = nullptr; void* lo = nullptr;
   uint32_t* words = nullptr;       // device: amax[0], amax[1] (alternating between uses), scale (float), spare
   unsigned uses = 0;
+  int arith = kArithF16;           // element type of hi / lo
   long long rows = 0, cols = 0, pitch = 0;
   const void* src = nullptr; uint64_t version = 0; int tag = 0;   // cache key
-  size_t bytes() const { return (size_t)rows * pitch * 2; }
+  size_t bytes() const { return (size_t)rows * pitch * elem_of(arith); }
   const float* scale() const { return reinterpret_cast<const float*>(words + 2); }
 };
-static int pack_alloc(Pack& pk, long long rows, long long cols, cudaStream_t s, int* oom) {
+static int pack_alloc(Pack& pk, int ar, long long rows, long long cols, cudaStream_t s, int* oom) {
   long long pitch = round_up(cols, 64);
   if (!pk.words) {
     pk.words = (uint32_t*)pool_alloc(16);
     if (!pk.words || cudaMemsetAsync(pk.words, 0, 16, s) != cudaSuccess) { if (oom) *oom = 16; return 1; }
     pk.uses = 0;
   }
-  if (pk.hi && pk.rows == rows && pk.pitch == pitch) { pk.cols = cols; return 0; }
+  if (pk.hi && pk.rows == rows && pk.pitch == pitch && pk.arith == ar) { pk.cols = cols; return 0; }
   if (pk.hi) { pool_free(pk.hi); pool_free(pk.lo); pk.hi = pk.lo = nullptr; }
-  pk.rows = rows; pk.cols = cols; pk.pitch = pitch; pk.src = nullptr;
-  pk.hi = (__half*)pool_alloc(pk.bytes());
-  pk.lo = pk.hi ? (__half*)pool_alloc(pk.bytes()) : nullptr;
+  pk.rows = rows; pk.cols = cols; pk.pitch = pitch; pk.src = nullptr; pk.arith = ar;
+  pk.hi = pool_alloc(pk.bytes());
+  pk.lo = pk.hi ? pool_alloc(pk.bytes()) : nullptr;
   if (!pk.lo) {
     if (pk.hi) pool_free(pk.hi);
     pk.hi = nullptr;
@@ -929,7 +1146,9 @@ static void pack_release(Pack& pk) {
 }
 // Starts one use of the pack: reduces max|src| over n contiguous floats into this use's amax word and returns the
 // references the pack kernel needs.  Several pack launches of the same use (stride phases) share one ScaleRef.
+// A tf32 pack needs no maximum: its scale is 1.
 static ScaleRef begin_pack(Pack& pk, const float* src, long long n, cudaStream_t s) {
+  if (pk.arith == kArithTF32) return ScaleRef{nullptr, nullptr, reinterpret_cast<float*>(pk.words + 2)};
   const unsigned k = pk.uses++ & 1;
   ScaleRef r{pk.words + k, pk.words + (k ^ 1), reinterpret_cast<float*>(pk.words + 2)};
   static const bool no_track = getenv("TINYFLOW_NO_AMAX_TRACKING") != nullptr;
@@ -941,15 +1160,22 @@ static ScaleRef begin_pack(Pack& pk, const float* src, long long n, cudaStream_t
   launch_dep(amax_kernel, dim3(grid_for(n, 256, 32)), dim3(256), 0, s, src, n, pk.words + k);
   return r;
 }
+// Calls `fn(hi, lo)` with the pack's buffers typed by its element type.
+template <class F> static void with_elems(const Pack& pk, F&& fn) {
+  if (pk.arith == kArithTF32) fn((float*)pk.hi, (float*)pk.lo);
+  else fn((__half*)pk.hi, (__half*)pk.lo);
+}
 
 static int run_pack_matrix(const float* src, long long ld, Pack& pk, cudaStream_t s) {
   long long total = pk.rows * pk.cols;
   ScaleRef sr = begin_pack(pk, src, total, s);          // callers pass ld == cols: the matrix is contiguous
-  KernelTimer kt("pack_matrix", s, 0, 8.0 * total);
-  if (pk.cols % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0)
-    launch_dep(pack_matrix_kernel<true>, dim3(grid_for(total / 8, 256, 2)), dim3(256), 0, s, src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols, sr);
-  else
-    launch_dep(pack_matrix_kernel<false>, dim3(grid_for(total, 256, 4)), dim3(256), 0, s, src, ld, pk.hi, pk.lo, pk.pitch, pk.rows, pk.cols, sr);
+  KernelTimer kt("pack_matrix", s, 0, 4.0 * total + 2.0 * elem_of(pk.arith) * total);
+  const bool vec = pk.cols % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+  with_elems(pk, [&](auto* hi, auto* lo) {
+    using E = std::remove_pointer_t<decltype(hi)>;
+    if (vec) launch_dep(pack_matrix_kernel<true, E>, dim3(grid_for(total / 8, 256, 2)), dim3(256), 0, s, src, ld, hi, lo, pk.pitch, pk.rows, pk.cols, sr);
+    else launch_dep(pack_matrix_kernel<false, E>, dim3(grid_for(total, 256, 4)), dim3(256), 0, s, src, ld, hi, lo, pk.pitch, pk.rows, pk.cols, sr);
+  });
   TF_AFTER(s, "pack_matrix");
   return 0;
 }
@@ -958,39 +1184,32 @@ static int run_pack_matrix(const float* src, long long ld, Pack& pk, cudaStream_
 int tc_matmul(const float* A, bool tA, const float* B, bool tB, float* C, int64_t M, int64_t N, int64_t K, cudaStream_t s, int* oom) {
   if (M < 16 || N < 16 || K < 64 || (double)M * N * K < 4e6) return 0;      // launch-bound sizes stay on the CUDA cores
   if (!encode_fn()) return 0;
+  const int ar = tensor_arithmetic(), bk = bk_of(ar);
   // A is stored [M][K] (K-major) or, transposed, [K][M] (M-major); B is stored [K][N] (N-major) or [N][K] (K-major)
   Pack pa, pb;
   long long a_rows = tA ? K : M, a_cols = tA ? M : K, b_rows = tB ? N : K, b_cols = tB ? K : N;
-  if (pack_alloc(pa, a_rows, a_cols, s, oom)) { pack_release(pa); return 0; }
-  if (pack_alloc(pb, b_rows, b_cols, s, oom)) { pack_release(pa); pack_release(pb); return 0; }
+  if (pack_alloc(pa, ar, a_rows, a_cols, s, oom)) { pack_release(pa); return 0; }
+  if (pack_alloc(pb, ar, b_rows, b_cols, s, oom)) { pack_release(pa); pack_release(pb); return 0; }
   int rc = run_pack_matrix(A, a_cols, pa, s);
   if (!rc) rc = run_pack_matrix(B, b_cols, pb, s);
   GemmParams p;
   memset(&p, 0, sizeof(p));
   const int bn = pick_bn(N, tB);
   p.mode = kModeGemm; p.a_mn = tA ? 1 : 0; p.b_mn = tB ? 0 : 1; p.epi = kEpiRowMajor;
-  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_hi, pa.hi, pa.rows, pa.pitch, BM / 64) : make_map(&p.a_hi, pa.hi, pa.rows, pa.cols, pa.pitch, BM);
-  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_lo, pa.lo, pa.rows, pa.pitch, BM / 64) : make_map(&p.a_lo, pa.lo, pa.rows, pa.cols, pa.pitch, BM);
-  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_hi, pb.hi, pb.rows, pb.pitch, bn / 64) : make_map(&p.b_hi, pb.hi, pb.rows, pb.cols, pb.pitch, bn);
-  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_lo, pb.lo, pb.rows, pb.pitch, bn / 64) : make_map(&p.b_lo, pb.lo, pb.rows, pb.cols, pb.pitch, bn);
+  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_hi, ar, pa.hi, pa.rows, pa.pitch, BM) : make_map(&p.a_hi, ar, pa.hi, pa.rows, pa.cols, pa.pitch, BM);
+  if (!rc) rc = p.a_mn ? make_map_mn(&p.a_lo, ar, pa.lo, pa.rows, pa.pitch, BM) : make_map(&p.a_lo, ar, pa.lo, pa.rows, pa.cols, pa.pitch, BM);
+  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_hi, ar, pb.hi, pb.rows, pb.pitch, bn) : make_map(&p.b_hi, ar, pb.hi, pb.rows, pb.cols, pb.pitch, bn);
+  if (!rc) rc = p.b_mn ? make_map_mn(&p.b_lo, ar, pb.lo, pb.rows, pb.pitch, bn) : make_map(&p.b_lo, ar, pb.lo, pb.rows, pb.cols, pb.pitch, bn);
   if (!rc) {
     p.M = (int)M; p.N = (int)N;
     p.m_tiles = (int)((M + BM - 1) / BM); p.n_tiles = (int)((N + bn - 1) / bn); p.tap_tiles = 1;
-    int kit = (int)((K + BK - 1) / BK);
-    int tiles = p.m_tiles * p.n_tiles, sms = device_sm_count();
-    int splits = 1;
-    if (tiles * 2 <= sms && kit >= 16) { splits = sms / tiles; if (splits > kit / 8) splits = kit / 8; if (splits < 1) splits = 1; }
-    p.k_total = kit;
-    p.k_iters = (kit + splits - 1) / splits;
-    p.splits = (kit + p.k_iters - 1) / p.k_iters;
-    p.atomic = p.splits > 1;
+    p.k_total = (int)((K + bk - 1) / bk);
     p.out = C; p.ldc = N; p.err = error_word();
     p.a_scale = pa.scale(); p.b_scale = pb.scale();
-    if (p.atomic) { if (cudaMemsetAsync(C, 0, sizeof(float) * M * N, s) != cudaSuccess) rc = -1; }
-    if (!rc) rc = launch_gemm_bn(bn, p, s, 2.0 * M * N * K, "DLGpuMatrixMultiply");
+    rc = launch_gemm_bn(bn, ar, p, s, 2.0 * M * N * K, "DLGpuMatrixMultiply", oom);
   }
   pack_release(pa); pack_release(pb);       // stream order keeps the blocks valid until the kernel is done
-  return rc ? -1 : 1;
+  return rc < 0 ? -1 : (rc > 0 ? 0 : 1);    // a missing workspace sends the call to the CUDA-core kernel
 }
 
 // ---- convolution -------------------------------------------------------------------------------------
@@ -1051,29 +1270,35 @@ static int launch_pack_nchw(Pack& pk, const ScaleRef& sr, const float* src, int 
   const int tc = cover > 64 ? 128 : cover > 32 ? 64 : 32;
   dim3 grid(N * ((cover + tc - 1) / tc), (st->frame_h * st->frame_w + 31) / 32);
   TF_REQUIRE(grid.y <= 65535, "pack: frame of %d x %d positions is too large", st->frame_h, st->frame_w);
-  KernelTimer kt("pack_nchw", s, 0, 4.0 * N * chans * H * W / (sh * sw) + 4.0 * pk.rows * cover);
-  if (tc == 128) launch_dep(pack_nchw_kernel<128>, grid, dim3(256), 0, s, src, pk.hi, pk.lo, g, sr);
-  else if (tc == 64) launch_dep(pack_nchw_kernel<64>, grid, dim3(256), 0, s, src, pk.hi, pk.lo, g, sr);
-  else launch_dep(pack_nchw_kernel<32>, grid, dim3(256), 0, s, src, pk.hi, pk.lo, g, sr);
+  KernelTimer kt("pack_nchw", s, 0, 4.0 * N * chans * H * W / (sh * sw) + 2.0 * elem_of(pk.arith) * pk.rows * cover);
+  with_elems(pk, [&](auto* hi, auto* lo) {
+    using E = std::remove_pointer_t<decltype(hi)>;
+    if (tc == 128) launch_dep(pack_nchw_kernel<128, E>, grid, dim3(256), 0, s, src, hi, lo, g, sr);
+    else if (tc == 64) launch_dep(pack_nchw_kernel<64, E>, grid, dim3(256), 0, s, src, hi, lo, g, sr);
+    else launch_dep(pack_nchw_kernel<32, E>, grid, dim3(256), 0, s, src, hi, lo, g, sr);
+  });
   TF_AFTER(s, "pack_nchw");
   return 0;
 }
-static bool pack_valid(const Pack& pk, const void* src, uint64_t ver, int tag, long long rows, long long cols) {
-  return pk.hi && pk.src == src && pk.version == ver && pk.tag == tag && pk.rows == rows && pk.cols == cols;
+static bool pack_valid(const Pack& pk, int ar, const void* src, uint64_t ver, int tag, long long rows, long long cols) {
+  return pk.hi && pk.arith == ar && pk.src == src && pk.version == ver && pk.tag == tag && pk.rows == rows && pk.cols == cols;
 }
 // the x operand of a plan: frame pack (classes A, B), patch matrix (class C) or one frame per stride phase (class D)
-static int pack_x(ConvTc* st, const ConvPlan* p, const float* x, cudaStream_t s, int* oom) {
+static int pack_x(ConvTc* st, int ar, const ConvPlan* p, const float* x, cudaStream_t s, int* oom) {
   Pack& pk = st->x;
   const uint64_t ver = version_of(x);
   const long long n_src = (long long)p->N * p->C * p->H * p->W;
   if (st->cls == 3) {
     long long rows = (long long)p->N * p->P * p->Q;
-    if (pack_valid(pk, x, ver, 3, rows, st->eC)) return 0;
-    if (pack_alloc(pk, rows, st->eC, s, oom)) return 1;
+    if (pack_valid(pk, ar, x, ver, 3, rows, st->eC)) return 0;
+    if (pack_alloc(pk, ar, rows, st->eC, s, oom)) return 1;
     ScaleRef sr = begin_pack(pk, x, n_src, s);
     PatchGeom g{p->N, p->C, p->H, p->W, p->R, p->S, p->P, p->Q, p->stride_h, p->stride_w, p->pad_h, p->pad_w, st->eC, (int)pk.pitch};
-    KernelTimer kt("pack_patches", s, 0, 4.0 * rows * pk.pitch);
-    launch_dep(pack_patches_kernel, dim3(grid_for(rows * 32, 256, 4)), dim3(256), 0, s, x, pk.hi, pk.lo, g, sr);
+    KernelTimer kt("pack_patches", s, 0, 2.0 * elem_of(ar) * rows * pk.pitch);
+    with_elems(pk, [&](auto* hi, auto* lo) {
+      using E = std::remove_pointer_t<decltype(hi)>;
+      launch_dep(pack_patches_kernel<E>, dim3(grid_for(rows * 32, 256, 4)), dim3(256), 0, s, x, hi, lo, g, sr);
+    });
     TF_AFTER(s, "pack_patches");
     pk.src = x; pk.version = ver; pk.tag = 3;
     return 0;
@@ -1081,8 +1306,8 @@ static int pack_x(ConvTc* st, const ConvPlan* p, const float* x, cudaStream_t s,
   const long long rows = (long long)p->N * st->frame_h * st->frame_w;
   const int phases = st->cls == 4 ? p->stride_h * p->stride_w : 1;
   const long long cols = st->cls == 4 ? (long long)phases * st->cp : p->C;
-  if (pack_valid(pk, x, ver, st->cls, rows, cols)) return 0;
-  if (pack_alloc(pk, rows, cols, s, oom)) return 1;
+  if (pack_valid(pk, ar, x, ver, st->cls, rows, cols)) return 0;
+  if (pack_alloc(pk, ar, rows, cols, s, oom)) return 1;
   ScaleRef sr = begin_pack(pk, x, n_src, s);
   int rc = 0;
   if (st->cls == 4) {
@@ -1099,12 +1324,12 @@ static int pack_x(ConvTc* st, const ConvPlan* p, const float* x, cudaStream_t s,
   pk.src = x; pk.version = ver; pk.tag = st->cls;
   return 0;
 }
-static int pack_dy(ConvTc* st, const ConvPlan* p, const float* dy, cudaStream_t s, int* oom) {
+static int pack_dy(ConvTc* st, int ar, const ConvPlan* p, const float* dy, cudaStream_t s, int* oom) {
   Pack& pk = st->dy;
   const uint64_t ver = version_of(dy);
   const long long rows = (long long)p->N * st->frame_h * st->frame_w;
-  if (pack_valid(pk, dy, ver, 2, rows, p->K)) return 0;
-  if (pack_alloc(pk, rows, p->K, s, oom)) return 1;
+  if (pack_valid(pk, ar, dy, ver, 2, rows, p->K)) return 0;
+  if (pack_alloc(pk, ar, rows, p->K, s, oom)) return 1;
   ScaleRef sr = begin_pack(pk, dy, (long long)p->N * p->K * p->P * p->Q, s);
   if (launch_pack_nchw(pk, sr, dy, p->N, p->K, p->P, p->Q, st, st->dy_off_h, st->dy_off_w, 1, 1, 0, (int)pk.pitch, s)) return -1;
   pk.src = dy; pk.version = ver; pk.tag = 2;
@@ -1112,25 +1337,28 @@ static int pack_dy(ConvTc* st, const ConvPlan* p, const float* dy, cudaStream_t 
 }
 // Filter packs are keyed like the activation packs (pointer, write version): an optimiser step bumps the version.
 // `with_other` makes the forward call produce the backward-data pack in the same launch.
-static int pack_filter(ConvTc* st, const float* w, const ConvPlan* p, int flip, bool with_other, cudaStream_t s, int* oom) {
+static int pack_filter(ConvTc* st, int ar, const float* w, const ConvPlan* p, int flip, bool with_other, cudaStream_t s, int* oom) {
   Pack& pk = flip ? st->wd : st->wf;
   const uint64_t ver = version_of(w);
   const int taps = st->eR * st->eS;
-  auto dims = [&](int f, int& rows, int& pad) { rows = f ? st->eC : p->K; pad = (int)round_up(f ? p->K : st->eC, BK); };
+  auto dims = [&](int f, int& rows, int& pad) { rows = f ? st->eC : p->K; pad = (int)round_up(f ? p->K : st->eC, 64); };
   int rows, pad;
   dims(flip, rows, pad);
-  if (pack_valid(pk, w, ver, 10 + flip, rows, (long long)taps * pad)) return 0;
-  if (pack_alloc(pk, rows, (long long)taps * pad, s, oom)) return 1;
+  if (pack_valid(pk, ar, w, ver, 10 + flip, rows, (long long)taps * pad)) return 0;
+  if (pack_alloc(pk, ar, rows, (long long)taps * pad, s, oom)) return 1;
   const long long nw = (long long)p->K * p->C * p->R * p->S;
   if (with_other && !flip) {
     Pack& pd = st->wd;
     int rows_d, pad_d;
     dims(1, rows_d, pad_d);
-    if (pack_alloc(pd, rows_d, (long long)taps * pad_d, s, oom)) return 1;
+    if (pack_alloc(pd, ar, rows_d, (long long)taps * pad_d, s, oom)) return 1;
     ScaleRef sr = begin_pack(pk, w, nw, s);
     long long total = std::max((long long)rows * taps * pad, (long long)rows_d * taps * pad_d);
-    launch_dep(pack_filter_pair_kernel, dim3(grid_for(total, 256)), dim3(256), 0, s, w, pk.hi, pk.lo, pd.hi, pd.lo, p->K, st->eC, st->eR, st->eS, pad, pad_d, sr,
-               reinterpret_cast<float*>(pd.words + 2));
+    with_elems(pk, [&](auto* hi, auto* lo) {
+      using E = std::remove_pointer_t<decltype(hi)>;
+      launch_dep(pack_filter_pair_kernel<E>, dim3(grid_for(total, 256)), dim3(256), 0, s, w, hi, lo, (E*)pd.hi, (E*)pd.lo, p->K, st->eC, st->eR, st->eS, pad, pad_d, sr,
+                 reinterpret_cast<float*>(pd.words + 2));
+    });
     TF_AFTER(s, "pack_filter");
     pk.src = w; pk.version = ver; pk.tag = 10;
     pd.src = w; pd.version = ver; pd.tag = 11;
@@ -1138,75 +1366,55 @@ static int pack_filter(ConvTc* st, const float* w, const ConvPlan* p, int flip, 
   }
   ScaleRef sr = begin_pack(pk, w, nw, s);
   long long total = (long long)rows * taps * pad;
-  launch_dep(pack_filter_kernel, dim3(grid_for(total, 256)), dim3(256), 0, s, w, pk.hi, pk.lo, p->K, st->eC, st->eR, st->eS, flip, pad, sr);
+  with_elems(pk, [&](auto* hi, auto* lo) {
+    using E = std::remove_pointer_t<decltype(hi)>;
+    launch_dep(pack_filter_kernel<E>, dim3(grid_for(total, 256)), dim3(256), 0, s, w, hi, lo, p->K, st->eC, st->eR, st->eS, flip, pad, sr);
+  });
   TF_AFTER(s, "pack_filter");
   pk.src = w; pk.version = ver; pk.tag = 10 + flip;
   return 0;
 }
 
-// Picks how many ways to split a reduction of k_total stages over `tiles` output tiles: minimises
-// waves * (stages per tile + fixed per-tile cost), everything in units of one stage; a split costs extra
-// (pre-zeroed output and atomic adds) so ties go to fewer splits.
-static int choose_splits(int tiles, int k_total, int min_iters, int max_splits, bool free_split) {
-  const int sms = device_sm_count();
-  double best_cost = 1e30; int best = 1;
-  for (int sp = 1; sp <= max_splits; ++sp) {
-    int it = (k_total + sp - 1) / sp;
-    if (sp > 1 && it < min_iters) break;
-    int real = (k_total + it - 1) / it;
-    long long total = (long long)tiles * real;
-    long long waves = (total + sms - 1) / sms;
-    double cost = (double)waves * (it + 8.0 + ((real > 1 && !free_split) ? 4.0 : 0.0));
-    if (cost < best_cost * 0.97) { best_cost = cost; best = real; }
-  }
-  return best;
-}
-
 // forward and backward-data share one launcher: out[pixel][ch_out] = sum_{tap, ch_in} act[pixel + off(tap)][col(tap) + ch_in] * filt[ch_out][b(tap)][ch_in]
 struct TapList { int n = 0; int off[kMaxTaps]; int col[kMaxTaps]; int b[kMaxTaps]; void add(int o, int c, int bb) { off[n] = o; col[n] = c; b[n] = bb; ++n; } };
 struct OutGeom { int valid_h, valid_w, out_h, out_w, out_sh, out_sw, out_off_h, out_off_w; };
-static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, const ConvPlan* p, const ConvTc* st, float* out, const TapList& taps,
-                     const OutGeom& og, bool out_is_zero, double flops, cudaStream_t s, const char* what) {
+// returns 0 on success, -1 on error, 1 when scratch memory was short (*oom set)
+static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, const ConvTc* st, float* out, const TapList& taps,
+                     const OutGeom& og, double flops, cudaStream_t s, const char* what, int* oom) {
   GemmParams g;
   memset(&g, 0, sizeof(g));
+  const int ar = act.arith, bk = bk_of(ar);
   const int bn = pick_bn(ch_out, true);
   g.mode = kModeConv; g.epi = kEpiNchw;
-  int rc = make_map(&g.a_hi, act.hi, act.rows, act.cols, act.pitch, BM);
-  if (!rc) rc = make_map(&g.a_lo, act.lo, act.rows, act.cols, act.pitch, BM);
-  if (!rc) rc = make_map(&g.b_hi, filt.hi, filt.rows, filt.cols, filt.pitch, bn);
-  if (!rc) rc = make_map(&g.b_lo, filt.lo, filt.rows, filt.cols, filt.pitch, bn);
+  int rc = make_map(&g.a_hi, ar, act.hi, act.rows, act.cols, act.pitch, BM);
+  if (!rc) rc = make_map(&g.a_lo, ar, act.lo, act.rows, act.cols, act.pitch, BM);
+  if (!rc) rc = make_map(&g.b_hi, ar, filt.hi, filt.rows, filt.cols, filt.pitch, bn);
+  if (!rc) rc = make_map(&g.b_lo, ar, filt.lo, filt.rows, filt.cols, filt.pitch, bn);
   if (rc) return -1;
   g.M = (int)act.rows; g.N = ch_out;
-  g.m_tiles = (int)((act.rows + BM - 1) / BM); g.n_tiles = (ch_out + bn - 1) / bn; g.tap_tiles = 1; g.splits = 1;
+  g.m_tiles = (int)((act.rows + BM - 1) / BM); g.n_tiles = (ch_out + bn - 1) / bn; g.tap_tiles = 1;
   g.ntaps = taps.n;
-  g.chunks_per_tap = (ch_in + BK - 1) / BK;
-  g.b_tap_pitch = (int)round_up(ch_in, BK);
+  g.chunks_per_tap = (ch_in + bk - 1) / bk;
+  g.b_tap_pitch = (int)round_up(ch_in, 64);
   g.k_total = g.ntaps * g.chunks_per_tap;
-  g.k_iters = g.k_total;
-  {   // Split the reduction when the tile count quantises badly onto the SMs and the reduction is long enough.
-    int best = g.k_total >= 24 ? choose_splits(g.m_tiles * g.n_tiles, g.k_total, 8, 16, false) : 1;
-    if (best > 1) {
-      g.k_iters = (g.k_total + best - 1) / best;
-      g.splits = (g.k_total + g.k_iters - 1) / g.k_iters;
-      g.atomic = g.splits > 1;
-    }
-  }
   for (int t = 0; t < taps.n; ++t) { g.tap_off[t] = taps.off[t]; g.tap_col[t] = (short)taps.col[t]; g.tap_b[t] = (short)taps.b[t]; }
   g.out = out; g.err = error_word();
   g.a_scale = act.scale(); g.b_scale = filt.scale();
   g.frame_h = st->frame_h; g.frame_w = st->frame_w; g.valid_h = og.valid_h; g.valid_w = og.valid_w;
   g.out_c = ch_out; g.out_h = og.out_h; g.out_w = og.out_w; g.out_sh = og.out_sh; g.out_sw = og.out_sw; g.out_off_h = og.out_off_h; g.out_off_w = og.out_off_w;
-  if (g.atomic && !out_is_zero) TF_CUDA(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)p->N * ch_out * og.out_h * og.out_w, s));
-  return launch_gemm_bn(bn, g, s, flops, what);
+  return launch_gemm_bn(bn, ar, g, s, flops, what, oom);
 }
 static double conv_flops(const ConvPlan* p) { return 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S; }
+// result of a tensor-path entry point from the launcher's code
+static inline int tc_result(int rc) { return rc < 0 ? -1 : (rc > 0 ? 1 : 1); }
 
 int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStream_t s, int* oom) {
   ConvTc* st = conv_state(p);
   if (!st->cls || !encode_fn()) return 0;
+  const int ar = tensor_arithmetic();
   std::lock_guard<std::mutex> lk(st->mu);
-  if (pack_x(st, p, x, s, oom)) return *oom ? 1 : -1;
-  if (pack_filter(st, w, p, 0, st->dgrad_seen, s, oom)) return *oom ? 1 : -1;
+  if (pack_x(st, ar, p, x, s, oom)) return *oom ? 1 : -1;
+  if (pack_filter(st, ar, w, p, 0, st->dgrad_seen, s, oom)) return *oom ? 1 : -1;
   TapList taps;
   for (int r = 0; r < st->eR; ++r)
     for (int q = 0; q < st->eS; ++q) {
@@ -1214,33 +1422,35 @@ int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStrea
       else taps.add(r * st->frame_w + q, 0, r * st->eS + q);
     }
   OutGeom og{p->P, p->Q, p->P, p->Q, 1, 1, 0, 0};
-  int rc = conv_like(st->x, st->wf, st->eC, p->K, p, st, y, taps, og, false, conv_flops(p), s, "DLGpuConvolution2DForward");
-  return rc ? -1 : 1;
+  return tc_result(conv_like(st->x, st->wf, st->eC, p->K, st, y, taps, og, conv_flops(p), s, "DLGpuConvolution2DForward", oom));
 }
 
 int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaStream_t s, int* oom) {
   ConvTc* st = conv_state(p);
   if (!st->cls || st->cls == 3 || !encode_fn()) return 0;
+  const int ar = tensor_arithmetic();
   std::lock_guard<std::mutex> lk(st->mu);
-  if (pack_dy(st, p, dy, s, oom)) return *oom ? 1 : -1;
+  if (pack_dy(st, ar, p, dy, s, oom)) return *oom ? 1 : -1;
   st->dgrad_seen = true;                                           // from now on forward packs both layouts in one launch
-  if (pack_filter(st, w, p, 1, false, s, oom)) return *oom ? 1 : -1;     // [C][flipped tap][K]; a no-op when forward made it
+  if (pack_filter(st, ar, w, p, 1, false, s, oom)) return *oom ? 1 : -1;     // [C][flipped tap][K]; a no-op when forward made it
   const int ntap = p->R * p->S;
   int rc = 0;
   if (st->cls == 1) {
+    // a strided 1x1 window reaches only every stride-th input position: the rest of dx is zero
     bool strided = p->stride_h > 1 || p->stride_w > 1;
     if (strided && cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)p->N * p->C * p->H * p->W, s) != cudaSuccess) return -1;
     TapList taps; taps.add(0, 0, 0);
     OutGeom og{p->P, p->Q, p->H, p->W, p->stride_h, p->stride_w, 0, 0};
-    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, taps, og, strided, conv_flops(p), s, "DLGpuConvolutionBackwardData");
+    rc = conv_like(st->dy, st->wd, p->K, p->C, st, dx, taps, og, conv_flops(p), s, "DLGpuConvolutionBackwardData", oom);
   } else if (st->cls == 2) {
     TapList taps;
     for (int r = 0; r < p->R; ++r) for (int q = 0; q < p->S; ++q) taps.add(r * st->frame_w + q, 0, r * p->S + q);
     OutGeom og{p->H, p->W, p->H, p->W, 1, 1, 0, 0};
-    rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, taps, og, false, conv_flops(p), s, "DLGpuConvolutionBackwardData");
+    rc = conv_like(st->dy, st->wd, p->K, p->C, st, dx, taps, og, conv_flops(p), s, "DLGpuConvolutionBackwardData", oom);
   } else {
     // One launch per stride phase (a, b): dx_padded(sh*u + a, sw*v + b) = sum over the taps r = sh*r' + a, s = sw*s' + b of
     // dy(u - r', v - s') * w(r, s); dy sits at frame offset (hh, hw), so the shift is (hh - r') rows and (hw - s') columns.
+    // The phases write disjoint positions of dx; positions no phase reaches stay zero.
     if (cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)p->N * p->C * p->H * p->W, s) != cudaSuccess) return -1;
     for (int a = 0; a < p->stride_h && !rc; ++a)
       for (int b = 0; b < p->stride_w && !rc; ++b) {
@@ -1250,20 +1460,23 @@ int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaS
             taps.add((st->dy_off_h - r / p->stride_h) * st->frame_w + (st->dy_off_w - q / p->stride_w), 0, ntap - 1 - (r * p->S + q));
         if (!taps.n) continue;      // no tap lands on this phase: it stays zero
         OutGeom og{st->frame_h, st->frame_w, p->H, p->W, p->stride_h, p->stride_w, a - p->pad_h, b - p->pad_w};
-        rc = conv_like(st->dy, st->wd, p->K, p->C, p, st, dx, taps, og, true, conv_flops(p) * taps.n / ntap, s, "DLGpuConvolutionBackwardData");
+        rc = conv_like(st->dy, st->wd, p->K, p->C, st, dx, taps, og, conv_flops(p) * taps.n / ntap, s, "DLGpuConvolutionBackwardData", oom);
       }
   }
-  return rc ? -1 : 1;
+  return tc_result(rc);
 }
 
 int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaStream_t s, int* oom) {
   ConvTc* st = conv_state(p);
   if (!st->cls || !encode_fn()) return 0;
+  const int ar = tensor_arithmetic(), bk = bk_of(ar);
   std::lock_guard<std::mutex> lk(st->mu);
-  if (pack_x(st, p, x, s, oom)) return *oom ? 1 : -1;
-  if (pack_dy(st, p, dy, s, oom)) return *oom ? 1 : -1;
+  if (pack_x(st, ar, p, x, s, oom)) return *oom ? 1 : -1;
+  if (pack_dy(st, ar, p, dy, s, oom)) return *oom ? 1 : -1;
   GemmParams g;
   memset(&g, 0, sizeof(g));
+  g.err = error_word(); g.out = dw;
+  const int kit = (int)((st->dy.rows + bk - 1) / bk);       // the reduction runs over the frame's pixel rows
   if (st->eR * st->eS == 1 && st->dy_off_h == 0 && st->dy_off_w == 0) {
     // One tap: dW[k][c] = dy^T x is a plain GEMM over the two packs, and either operand may take the M side.
     // Take the orientation whose padded tile grid is smaller (64 input channels would fill half of a 128-row tile).
@@ -1273,38 +1486,31 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
     const long long as_is = slot_rows * ((p->K + bn_x - 1) / bn_x * bn_x);
     if (padded(p->K, st->eC) < as_is) {
       const int bn = pick_bn(st->eC);
-      g.mode = kModeGemm; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiRowMajor; g.atomic = 1;
-      int rc = make_map_mn(&g.a_hi, st->dy.hi, st->dy.rows, st->dy.pitch, BM / 64);
-      if (!rc) rc = make_map_mn(&g.a_lo, st->dy.lo, st->dy.rows, st->dy.pitch, BM / 64);
-      if (!rc) rc = make_map_mn(&g.b_hi, st->x.hi, st->x.rows, st->x.pitch, bn / 64);
-      if (!rc) rc = make_map_mn(&g.b_lo, st->x.lo, st->x.rows, st->x.pitch, bn / 64);
+      g.mode = kModeGemm; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiRowMajor;
+      int rc = make_map_mn(&g.a_hi, ar, st->dy.hi, st->dy.rows, st->dy.pitch, BM);
+      if (!rc) rc = make_map_mn(&g.a_lo, ar, st->dy.lo, st->dy.rows, st->dy.pitch, BM);
+      if (!rc) rc = make_map_mn(&g.b_hi, ar, st->x.hi, st->x.rows, st->x.pitch, bn);
+      if (!rc) rc = make_map_mn(&g.b_lo, ar, st->x.lo, st->x.rows, st->x.pitch, bn);
       if (rc) return -1;
       g.a_scale = st->dy.scale(); g.b_scale = st->x.scale();
       g.M = p->K; g.N = st->eC; g.ldc = st->eC;
       g.m_tiles = (p->K + BM - 1) / BM; g.n_tiles = (st->eC + bn - 1) / bn; g.tap_tiles = 1; g.ntaps = 1;
-      const int kit = (int)((st->dy.rows + BK - 1) / BK);
-      const int splits = choose_splits(g.m_tiles * g.n_tiles, kit, 4, 1024, true);
       g.k_total = kit;
-      g.k_iters = (kit + splits - 1) / splits;
-      g.splits = (kit + g.k_iters - 1) / g.k_iters;
-      g.out = dw; g.err = error_word();
-      if (cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)p->K * p->C * p->R * p->S, s) != cudaSuccess) return -1;
-      rc = launch_gemm_bn(bn, g, s, conv_flops(p), "DLGpuConvolutionBackwardFilter");
-      return rc ? -1 : 1;
+      return tc_result(launch_gemm_bn(bn, ar, g, s, conv_flops(p), "DLGpuConvolutionBackwardFilter", oom));
     }
   }
   // A = x (M = tap slots x input channels), B = dy (N = output channels); both M/N-major, reduction over pixel rows.
   const int bn = pick_bn(p->K);
-  g.mode = kModeWgrad; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiWgrad; g.atomic = 1;
+  g.mode = kModeWgrad; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiWgrad;
   g.M = st->eC; g.N = p->K; g.ntaps = st->eR * st->eS;
   // Few input channels: two filter taps share one 128-row tile (slots of 64 channels), so that the tensor core's
   // M dimension is full and dy is read once for both.
   g.slot = st->eC > 64 ? BM : 64;
   g.taps_per_tile = BM / g.slot;
-  int rc = make_map_mn(&g.a_hi, st->x.hi, st->x.rows, st->x.pitch, g.slot / 64);
-  if (!rc) rc = make_map_mn(&g.a_lo, st->x.lo, st->x.rows, st->x.pitch, g.slot / 64);
-  if (!rc) rc = make_map_mn(&g.b_hi, st->dy.hi, st->dy.rows, st->dy.pitch, bn / 64);
-  if (!rc) rc = make_map_mn(&g.b_lo, st->dy.lo, st->dy.rows, st->dy.pitch, bn / 64);
+  int rc = make_map_mn(&g.a_hi, ar, st->x.hi, st->x.rows, st->x.pitch, g.slot);
+  if (!rc) rc = make_map_mn(&g.a_lo, ar, st->x.lo, st->x.rows, st->x.pitch, g.slot);
+  if (!rc) rc = make_map_mn(&g.b_hi, ar, st->dy.hi, st->dy.rows, st->dy.pitch, bn);
+  if (!rc) rc = make_map_mn(&g.b_lo, ar, st->dy.lo, st->dy.rows, st->dy.pitch, bn);
   if (rc) return -1;
   g.a_scale = st->x.scale(); g.b_scale = st->dy.scale();
   g.m_tiles = (st->eC + g.slot - 1) / g.slot;
@@ -1322,17 +1528,8 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
         g.tap_off[t] = (r - st->dy_off_h) * st->frame_w + (q - st->dy_off_w);
       }
     }
-  long long rows = st->dy.rows;
-  int kit = (int)((rows + BK - 1) / BK);
-  int splits = choose_splits(g.m_tiles * g.n_tiles * g.tap_tiles, kit, 4, 1024, true);
   g.k_total = kit;
-  g.k_iters = (kit + splits - 1) / splits;
-  g.splits = (kit + g.k_iters - 1) / g.k_iters;
-  g.out = dw; g.err = error_word();
-  if (cudaMemsetAsync(dw, 0, sizeof(float) * (size_t)p->K * p->C * p->R * p->S, s) != cudaSuccess) return -1;
-  double flops = 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S;
-  rc = launch_gemm_bn(bn, g, s, flops, "DLGpuConvolutionBackwardFilter");
-  return rc ? -1 : 1;
+  return tc_result(launch_gemm_bn(bn, ar, g, s, conv_flops(p), "DLGpuConvolutionBackwardFilter", oom));
 }
 
 }  // namespace tf

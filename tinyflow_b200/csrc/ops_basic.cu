@@ -917,17 +917,19 @@ int DLGpuAdam(DLArrayHandle output, const DLArrayHandle m, const DLArrayHandle v
 
 // Pointer tables for the multi-tensor optimisers.  `result` receives a 1- or 2-slot host array:
 // slot 0 = device table, slot 1 = host copy of the sizes.  indexlist slot 0 = device prefix sums.
-struct PtrTable { int n; int groups; void** dev; };
+// The host keeps its own copy of the table: the tensors a multi-tensor update writes (the parameters, and Adam's
+// moments) have to get a new write version at every update, or packed copies of the old weights would be reused.
+struct PtrTable { int n; int groups; void** dev; void** host; };
 static int build_table(void** const* cols, int ncols, int number, void**** result) {
   TF_REQUIRE(result && number > 0, "pointer table: bad arguments");
-  PtrTable* t = new PtrTable{number, ncols, nullptr};
+  PtrTable* t = new PtrTable{number, ncols, nullptr, nullptr};
   void** host = (void**)malloc(sizeof(void*) * number * ncols);
   for (int c = 0; c < ncols; ++c) for (int i = 0; i < number; ++i) host[c * number + i] = cols[c][i];
   t->dev = (void**)pool_alloc(sizeof(void*) * number * ncols);
   if (!t->dev) { free(host); delete t; TF_FAIL("pointer table: allocation failed"); }
   cudaError_t e = cudaMemcpy(t->dev, host, sizeof(void*) * number * ncols, cudaMemcpyHostToDevice);
-  free(host);
-  if (e != cudaSuccess) { delete t; TF_FAIL("pointer table: copy failed"); }
+  t->host = host;
+  if (e != cudaSuccess) { free(host); pool_free(t->dev); delete t; TF_FAIL("pointer table: copy failed"); }
   void*** arr = (void***)malloc(sizeof(void**));
   arr[0] = (void**)t;
   *result = arr;
@@ -956,6 +958,7 @@ int DLGpuSgd_o(void**** n2list, const void*** indexlist, const int count, const 
   IndexInfo* info = (IndexInfo*)((*indexlist)[0]);
   TF_REQUIRE(t && info && t->groups == 2 && t->n == info->count && (count == t->n || count == (int)info->total), "DLGpuSgd_o: tables do not match");
   cudaStream_t s = last_compute_stream();
+  for (int i = 0; i < t->n; ++i) note_write(t->host[i]);                      // column 0: the parameters
   sgd_table_kernel<<<grid_for(info->total, kBlock), kBlock, 0, s>>>((float* const*)t->dev, (float* const*)(t->dev + t->n), info->dev_prefix, t->n, info->total, learning_rate);
   TF_AFTER(s, "DLGpuSgd_o");
   return 0;
@@ -966,6 +969,7 @@ int DLGpuAdam_o(void**** n4list, const void*** indexlist, const int count, const
   IndexInfo* info = (IndexInfo*)((*indexlist)[0]);
   TF_REQUIRE(t && info && t->groups == 4 && t->n == info->count && (count == t->n || count == (int)info->total), "DLGpuAdam_o: tables do not match");
   cudaStream_t s = last_compute_stream();
+  for (int i = 0; i < 3 * t->n; ++i) note_write(t->host[i]);                  // columns 0-2: parameters and both moments
   adam_table_kernel<<<grid_for(info->total, kBlock), kBlock, 0, s>>>((float* const*)t->dev, (float* const*)(t->dev + t->n), (float* const*)(t->dev + 2 * t->n), (float* const*)(t->dev + 3 * t->n),
                                                                      info->dev_prefix, t->n, info->total, b1, b2, 1.f - b1t, 1.f - b2t, e, learning_rate);
   TF_AFTER(s, "DLGpuAdam_o");

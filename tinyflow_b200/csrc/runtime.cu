@@ -112,7 +112,6 @@ struct Pool {
   std::unordered_map<void*, size_t> size_of;   // every block we own, in use or cached
   long long in_use = 0, cached = 0;
   bool host;
-  bool failed_hard = false;      // an allocation failed for a reason other than running out of memory
   explicit Pool(bool h) : host(h) {}
 
   static size_t round(size_t b) {
@@ -132,7 +131,11 @@ struct Pool {
     }
     cached = 0;
   }
-  void* alloc(size_t bytes) {
+  // *hard (optional) is set when the allocation failed for a reason other than running out of memory (the context is
+  // unusable, e.g. after a kernel fault): the caller reports an error instead of the out-of-memory protocol.  The
+  // flag describes this call only.
+  void* alloc(size_t bytes, bool* hard = nullptr) {
+    if (hard) *hard = false;
     size_t b = round(bytes);
     std::lock_guard<std::mutex> lk(mu);
     auto it = free_by_size.find(b);
@@ -147,7 +150,7 @@ struct Pool {
     cudaError_t e = raw_alloc(&p, b);
     if (e != cudaSuccess && e != cudaErrorMemoryAllocation) {
       // not an out-of-memory condition: the context is unusable (an earlier kernel faulted)
-      failed_hard = true;
+      if (hard) *hard = true;
       set_error("device allocation failed: %s", cudaGetErrorString(e));
       return nullptr;
     }
@@ -174,11 +177,31 @@ struct Pool {
   }
 };
 
-static Pool& device_pool() { static Pool* p = new Pool(false); return *p; }
+// One device pool per GPU (a cached block is only ever handed out on the device it was allocated on); pinned host
+// memory is not tied to a device.
+constexpr int kMaxDevices = 64;
+static Pool* g_device_pools[kMaxDevices] = {nullptr};
+static std::mutex g_device_pools_mu;
+static Pool& device_pool(int dev) {
+  std::lock_guard<std::mutex> lk(g_device_pools_mu);
+  if (dev < 0 || dev >= kMaxDevices) dev = 0;
+  if (!g_device_pools[dev]) g_device_pools[dev] = new Pool(false);
+  return *g_device_pools[dev];
+}
+static int current_device() { int dev = 0; if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = 0; } return dev; }
+static Pool& device_pool() { return device_pool(current_device()); }
 static Pool& host_pool() { static Pool* p = new Pool(true); return *p; }
 
 void* pool_alloc(size_t bytes) { return device_pool().alloc(bytes); }
-void pool_free(void* p) { if (p) device_pool().free(p); }
+void pool_free(void* p) {
+  if (!p) return;
+  if (device_pool().free(p)) return;
+  for (int d = 0; d < kMaxDevices; ++d) {                                      // freed while another device is current
+    Pool* other;
+    { std::lock_guard<std::mutex> lk(g_device_pools_mu); other = g_device_pools[d]; }
+    if (other && other->free(p)) return;
+  }
+}
 
 void* persistent_scratch(int slot, size_t bytes) {
   static std::mutex mu;
@@ -214,19 +237,22 @@ int DLArrayAlloc(const index_t* shape, index_t ndim_in, DLContext ctx, DLArrayHa
   size_t n = 1;
   for (int i = 0; i < ndim; ++i) {
     TF_REQUIRE(shape[i] >= 0, "DLArrayAlloc: negative extent");
+    TF_REQUIRE(shape[i] == 0 || n <= (SIZE_MAX / 4) / (size_t)shape[i], "DLArrayAlloc: the array's byte size overflows");
     n *= (size_t)shape[i];
   }
   size_t bytes = n * 4;
   void* data = nullptr;
+  bool hard = false;
   if (ctx.device_type == kGPU) {
+    TF_REQUIRE(ctx.device_id >= 0 && ctx.device_id < kMaxDevices, "DLArrayAlloc: device id %d out of range", ctx.device_id);
     if (cudaSetDevice(ctx.device_id) != cudaSuccess) { cudaGetLastError(); TF_FAIL("DLArrayAlloc: cudaSetDevice(%d) failed", ctx.device_id); }
-    data = device_pool().alloc(bytes);
+    data = device_pool(ctx.device_id).alloc(bytes, &hard);
   } else if (ctx.device_type == kCPU) {
-    data = host_pool().alloc(bytes);     // pinned, as src/cpu_device_api.cc:18
+    data = host_pool().alloc(bytes, &hard);     // pinned, as src/cpu_device_api.cc:18
   } else {
     TF_FAIL("DLArrayAlloc: unknown device type %d", (int)ctx.device_type);
   }
-  if (!data && (device_pool().failed_hard || host_pool().failed_hard)) return -1;   // message already set
+  if (!data && hard) return -1;          // not out of memory: this call hit an unusable context (message already set)
   if (!data) {
     if (memorytoSaving) *memorytoSaving = bytes > 0x7fffffffu ? 0x7fffffff : (int)bytes;
     return 0;
@@ -246,7 +272,7 @@ int DLArrayFree(DLArrayHandle handle) {
   if (!handle) return 0;
   if (handle->data) {
     if (handle->ctx.device_type == kGPU) note_write(handle->data);   // a recycled block is new data
-    bool ok = (handle->ctx.device_type == kGPU) ? device_pool().free(handle->data)
+    bool ok = (handle->ctx.device_type == kGPU) ? device_pool(handle->ctx.device_id).free(handle->data)
                                                 : host_pool().free(handle->data);
     if (!ok) TF_FAIL("DLArrayFree: array was not allocated by DLArrayAlloc");
   }
@@ -352,6 +378,7 @@ int testPcie(void) {
   double a = run(dev, pageable, cudaMemcpyHostToDevice), b = run(pageable, dev, cudaMemcpyDeviceToHost);
   double c = run(dev, pinned, cudaMemcpyHostToDevice), d = run(pinned, dev, cudaMemcpyDeviceToHost);
   printf("host link GB/s: pageable H2D %.2f D2H %.2f | pinned H2D %.2f D2H %.2f\n", a, b, c, d);
+  fflush(stdout);
   cudaFree(dev); cudaFreeHost(pinned); free(pageable);
   return 0;
 }

@@ -430,8 +430,36 @@ def set_contraction_path(path: int):
     check_call(_LIB.TfSetContractionPath(int(path)))
 
 
+def last_contraction_path() -> int:
+    """Engine that served this thread's most recent matmul / convolution: 1 = CUDA cores, 2 = tensor cores."""
+    return int(_LIB.TfLastContractionPath())
+
+
+def set_tensor_arithmetic(name: str):
+    """"3xfp16" (default) or "3xtf32": how the tensor-core path represents fp32 operands."""
+    check_call(_LIB.TfSetArithmetic({"3xfp16": 0, "3xtf32": 1}[name]))
+
+
+def tensor_arithmetic() -> str:
+    return {0: "3xfp16", 1: "3xtf32"}[int(_LIB.TfGetArithmetic())]
+
+
 def allocator_stats():
     """(bytes handed out and not yet freed, bytes cached in the pools) of the device allocator."""
     used, cached = ctypes.c_longlong(0), ctypes.c_longlong(0)
     check_call(_LIB.TfAllocatorStats(ctypes.byref(used), ctypes.byref(cached)))
     return used.value, cached.value
+
+
+def release_cached_memory():
+    """Returns every cached (free) block of the device and pinned-host pools to the driver."""
+    check_call(_LIB.TfReleaseCachedMemory())
+
+
+def tensor_path_error() -> int:
+    """Non-zero after a tensor-core kernel gave up on a barrier wait (sticky until cleared)."""
+    return int(_LIB.TfTensorPathError())
+
+
+def clear_tensor_path_error():
+    check_call(_LIB.TfClearTensorPathError())

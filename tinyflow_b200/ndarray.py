@@ -35,10 +35,8 @@ class DLArray(ctypes.Structure):
 
 DLArrayHandle = ctypes.POINTER(DLArray)
 
-_LIB.DLArrayAlloc.argtypes = [ctypes.POINTER(ctypes.c_int64), ctypes.c_int64, DLContext,
-                              ctypes.POINTER(DLArrayHandle), ctypes.POINTER(ctypes.c_int)]
-_LIB.DLArrayFree.argtypes = [DLArrayHandle]
-_LIB.DLArrayCopyFromTo.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+# No argtypes are declared, as in the reference (ndarray.py:96-259): integers travel as C ints, the
+# context by value, everything else as the ctypes pointer object the caller built.
 
 
 def cpu(dev_id=0):
@@ -115,13 +113,13 @@ class NDArray(object):
         if source_array.shape != self.shape:
             raise ValueError("array shape do not match the shape of NDArray")
         src, keep = _borrow_numpy(source_array)
-        check_call(_LIB.DLArrayCopyFromTo(ctypes.addressof(src), ctypes.cast(self.handle, ctypes.c_void_p), None))
+        check_call(_LIB.DLArrayCopyFromTo(ctypes.byref(src), self.handle, None))
         del keep
 
     def asnumpy(self):
         out = np.empty(self.shape, dtype=np.float32)
         dst, keep = _borrow_numpy(out)
-        check_call(_LIB.DLArrayCopyFromTo(ctypes.cast(self.handle, ctypes.c_void_p), ctypes.addressof(dst), None))
+        check_call(_LIB.DLArrayCopyFromTo(self.handle, ctypes.byref(dst), None))
         del keep
         return out
 
@@ -133,9 +131,7 @@ class NDArray(object):
                 return target
         if not isinstance(target, NDArray):
             raise ValueError("Unsupported target type %s" % str(type(target)))
-        stream = None if cudaStream is None else ctypes.cast(cudaStream, ctypes.c_void_p)
-        check_call(_LIB.DLArrayCopyFromTo(ctypes.cast(self.handle, ctypes.c_void_p),
-                                          ctypes.cast(target.handle, ctypes.c_void_p), stream))
+        check_call(_LIB.DLArrayCopyFromTo(self.handle, target.handle, cudaStream))
         return target
 
 
