@@ -264,19 +264,32 @@ int DLGpuAdam_o(void ****n4list, const void ***indexlist, const int count,
 /* ==== additions with no counterpart in the reference ====================== */
 
 /* Data-parallel training across the GPUs of one box (one process per GPU).
- * After TfDpInit, DLGpuSgdUpdate sums the gradient over all ranks (bucketed
- * NCCL all-reduce on a side stream, overlapped with the rest of the backward
- * pass) and applies  w -= (lr / world) * sum_r g_r.  `nccl_id_path` names a file
- * rank 0 creates; the other ranks wait for it.  Returns 0 on success. */
+ * After TfDpInit the optimiser entry points exchange gradients: DLGpuSgdUpdate, and
+ * the DLGpuAdam_mv + DLGpuAdam pair, sum the gradient over all ranks (bucketed NCCL
+ * all-reduce on a side stream, overlapped with the rest of the backward pass) and
+ * apply the update with the mean gradient (SGD: w -= (lr / world) * sum_r g_r).
+ * `nccl_id_path` names a file rank 0 creates; the other ranks wait for it, at most
+ * TINYFLOW_DP_INIT_TIMEOUT_S seconds (default 120).  Returns 0 on success. */
 int TfDpInit(int rank, int world_size, const char *nccl_id_path);
-/* Flush every pending bucket and wait for the updates to land (call at the
- * end of a step, before parameters are read back). */
+/* Flush every pending bucket and make the stream wait for the updates (end of a
+ * step).  A blocking host<->device DLArrayCopyFromTo does the same, so a training
+ * loop that knows nothing of this layer stays correct.  Returns -1 if NCCL reported
+ * an asynchronous error (the communicator is then aborted). */
 int TfDpFlush(void **cudaStream);
+/* Waits (at most TINYFLOW_DP_TIMEOUT_S seconds, default 300) for the communication
+ * stream, then releases the communicator; -1 if the wait ran out (communicator aborted). */
 int TfDpShutdown(void);
 int TfDpStats(long long *bytes_reduced, long long *allreduces);   /* totals since TfDpInit */
+int TfDpStats2(long long *bytes_reduced, long long *allreduces, long long *apply_launches,
+               long long *early_closes);                          /* + update launches, early bucket closes */
 /* Host-only: the bucket each gradient tensor lands in, given tensor sizes (floats) in arrival order and the
  * bucket capacity; a tensor larger than the capacity gets -(id+1).  Returns the number of buckets. */
 int TfDpPlanBuckets(const long long *counts, int n, long long capacity_floats, int *bucket_of);
+/* The same walk with the early close the exchange applies from its second step on: once all but `tail_floats`
+ * of the step's `step_total_floats` have arrived, the open bucket is closed (once per step), so that the last,
+ * un-overlapped all-reduce is small.  step_total_floats = 0 plans a first step. */
+int TfDpPlanBucketsTail(const long long *counts, int n, long long capacity_floats, long long step_total_floats,
+                        long long tail_floats, int *bucket_of);
 
 /* Allocation-free twin of DLGpuReduceSumAll (no counterpart in the reference): output[0] = sum of all
  * elements of input, with the per-block partial sums kept in a fixed 16 KiB array inside the library
@@ -303,6 +316,10 @@ int TfGetArithmetic(void);
  * TfTensorPathError reads it, TfClearTensorPathError resets it once the cause has been dealt with. */
 int TfTensorPathError(void);
 int TfClearTensorPathError(void);
+/* Launches a one-thread kernel that waits, with the tensor path's bounded-wait helper and a limit of
+ * `limit_cycles` GPU clock cycles, on a barrier nothing ever arms: the wait gives up and raises the error word.
+ * Lets a test see the time-out path end to end without a stuck kernel. */
+int TfTensorPathTimeoutProbe(long long limit_cycles, void **cudaStream);
 int TfLastError(char *buf, int buflen);   /* message of the last -1 return on this thread */
 int TfAllocatorStats(long long *bytes_in_use, long long *bytes_cached);
 int TfReleaseCachedMemory(void);

@@ -30,6 +30,17 @@ def test_bucket_planner(lib_path):
     n = lib.TfDpPlanBuckets(counts, len(sizes), ctypes.c_longlong(32 * 1024 * 1024 // 4), out)
     assert 4 <= n <= 8 and min(out) >= 0
     assert sum(sizes) == 29700264
+    # from the second step on the open bucket is closed once all but ~2 MiB of the step's gradients have arrived, so
+    # that the step's last all-reduce (which nothing overlaps) is small
+    total, tail = sum(sizes), 2 * 1024 * 1024 // 4
+    out_tail = (ctypes.c_int * len(sizes))()
+    n_tail = lib.TfDpPlanBucketsTail(counts, len(sizes), ctypes.c_longlong(32 * 1024 * 1024 // 4), ctypes.c_longlong(total), ctypes.c_longlong(tail), out_tail)
+    assert n_tail == n + 1
+    last = [sz for sz, b in zip(sizes, out_tail) if b == n_tail - 1]
+    assert 0 < sum(last) <= tail
+    first_step = (ctypes.c_int * len(sizes))()
+    assert lib.TfDpPlanBucketsTail(counts, len(sizes), ctypes.c_longlong(32 * 1024 * 1024 // 4), ctypes.c_longlong(0), ctypes.c_longlong(tail), first_step) == n
+    assert list(first_step) == list(out)
 
 
 def _gloo_rank(rank, world, port, q):
@@ -93,9 +104,11 @@ def test_two_rank_exchange_equals_large_batch_step():
 
 
 @pytest.mark.gpu
-def test_nccl_data_parallel_step_matches_oracle(lib_path):
-    """Two ranks on two GPUs: weights after two data-parallel SGD steps equal the oracle's step with the
-    rank-averaged gradient, and are identical on both ranks."""
+@pytest.mark.parametrize("opt,flush", [("sgd", "explicit"), ("adam", "explicit"), ("adam", "implicit")])
+def test_nccl_data_parallel_step_matches_oracle(lib_path, opt, flush):
+    """Two ranks on two GPUs: weights after two data-parallel steps equal the oracle's steps with the rank-averaged
+    gradient, and are identical on both ranks - for SGD, for Adam (the reference executor's optimiser), and for a
+    training loop that never calls TfDpFlush."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -104,7 +117,7 @@ def test_nccl_data_parallel_step_matches_oracle(lib_path):
         procs = []
         for r in range(world):
             env = dict(os.environ, RANK=str(r), WORLD=str(world), ID_FILE=os.path.join(d, "nccl_id"), OUT=os.path.join(d, "w%d.npz" % r),
-                       CUDA_VISIBLE_DEVICES=str(r), STEPS="2", NCCL_NVLS_ENABLE="0")
+                       CUDA_VISIBLE_DEVICES=str(r), STEPS="2", NCCL_NVLS_ENABLE="0", OPT=opt, FLUSH=flush)
             procs.append(subprocess.Popen([sys.executable, os.path.join(REPO, "tests", "dp_worker.py")], env=env))
         for p in procs:
             assert p.wait(timeout=300) == 0
@@ -113,6 +126,7 @@ def test_nccl_data_parallel_step_matches_oracle(lib_path):
         np.testing.assert_array_equal(w[0][k], w[1][k])
     # oracle: two steps with the averaged gradient
     sys.path.insert(0, REPO)
+    import oracle.ops as ops
     from oracle.graph_eval import OracleExecutor
     from tinyflow_b200 import autodiff as ad, models
     sys.path.insert(0, os.path.join(REPO, "tests"))
@@ -122,6 +136,9 @@ def test_nccl_data_parallel_step_matches_oracle(lib_path):
     grads = ad.gradients(model.loss, params)
     topo = ad.find_topo_sort([model.loss] + grads)
     cur = {p: v.astype(np.float64) for p, v in model.init_params(seed=5).items()}
+    mom = {p: (np.zeros_like(cur[p]), np.zeros_like(cur[p])) for p in params}
+    lr = dp_worker.LR[opt]
+    b1t, b2t = 0.9, 0.999
     for _ in range(2):
         acc = {p: 0.0 for p in params}
         for r in range(world):
@@ -131,8 +148,65 @@ def test_nccl_data_parallel_step_matches_oracle(lib_path):
             vals = OracleExecutor(topo, np.float64).run(feed)
             for p, g in zip(params, grads):
                 acc[p] = acc[p] + vals[g]
-        cur = {p: cur[p] - 0.05 / world * acc[p] for p in params}
+        if opt == "sgd":
+            cur = {p: cur[p] - lr / world * acc[p] for p in params}
+        else:
+            for p in params:
+                w2, m2, v2 = ops.adam(cur[p], mom[p][0], mom[p][1], acc[p] / world, 0.9, 0.999, b1t, b2t, 1e-8, lr)
+                cur[p], mom[p] = w2, (m2, v2)
+            b1t, b2t = b1t * 0.9, b2t * 0.999
     for p in params:
         want = cur[p]
-        scale = np.maximum(np.abs(want), 0.05 * np.abs(want).max())
+        if opt == "adam":
+            # an Adam step is lr * m / sqrt(v): compare the two-step displacement, which is what the exchange affects
+            start = model.init_params(seed=5)[p].astype(np.float64)
+            got_step, want_step = w[0][p.name] - start, want - start
+            clear = np.abs(want_step) > 0.5 * lr                      # entries whose gradient sign is not rounding noise
+            assert np.abs(got_step[clear] - want_step[clear]).max() <= 2e-2 * lr * 2, p.name
+            continue
+        scale = np.maximum(np.abs(want), 1e-2 * np.abs(want).max())
         assert (np.abs(w[0][p.name] - want) / scale).max() <= 1e-4, p.name
+
+
+# ---- failure handling on the host (no GPU is touched: the waits run out before NCCL is loaded) -----------------------
+def _init_in_child(rank, world, path, timeout_s, q):
+    os.environ["TINYFLOW_DP_INIT_TIMEOUT_S"] = str(timeout_s)
+    import time
+    lib = ctypes.CDLL(os.path.join(REPO, "build", "lib", "libc_runtime_api.so"))
+    t0 = time.time()
+    rc = lib.TfDpInit(rank, world, path.encode())
+    buf = ctypes.create_string_buffer(512)
+    lib.TfLastError(buf, 512)
+    q.put((rc, time.time() - t0, buf.value.decode()))
+
+
+def _run_init(path, timeout_s=0.6):
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_init_in_child, args=(1, 2, path, timeout_s, q))
+    p.start()
+    rc, took, msg = q.get(timeout=60)
+    p.join(timeout=30)
+    return rc, took, msg
+
+
+def test_rendezvous_wait_is_bounded_when_rank_zero_never_arrives(lib_path, tmp_path):
+    """Rank 1 of 2 waits for the id file of a rank 0 that never starts: TfDpInit returns -1 after the configured
+    limit instead of blocking for good."""
+    rc, took, msg = _run_init(str(tmp_path / "never_written"))
+    assert rc == -1 and 0.5 <= took < 10 and "timed out" in msg
+
+
+def test_rendezvous_rejects_a_stale_id_file(lib_path, tmp_path):
+    """An id file left by a crashed run (right magic, an hour old) is not accepted: the other ranks keep waiting for
+    rank 0 to publish a fresh one, within the limit."""
+    import struct
+    import time
+    path = tmp_path / "stale"
+    path.write_bytes(struct.pack("<QQ", 0x746664706E63636C, int(time.time()) - 3600) + bytes(128))
+    rc, took, msg = _run_init(str(path))
+    assert rc == -1 and "timed out" in msg
+    path.write_bytes(b"short")                 # a truncated file is ignored as well
+    rc, took, msg = _run_init(str(path))
+    assert rc == -1 and "timed out" in msg

@@ -6,7 +6,7 @@ inputs.  Two checks per graph:
   (elementwise |got - want| <= 1e-4 * max(|want|, 1e-2 * max|want|));
 * node by node: every node's GPU output against the oracle applied to that node's GPU inputs,
   which localises any disagreement to one kernel.  Matmul and convolution nodes are held to
-  |got - want| <= 1e-4 * |want| + 4 * 2^-24 * sum|a||b| (relative 1e-4, or four units of fp32 roundoff of
+  |got - want| <= 1e-4 * |want| + 8 * 2^-24 * sum|a||b| (relative 1e-4, or eight units of fp32 roundoff of
   the dot product's own magnitude where its terms cancel); the other nodes to the floor rule above plus
   1e-6 of the largest input (outputs that are differences of O(max input) quantities).
 """
@@ -26,9 +26,9 @@ CONTRACTIONS = ("MatMulOp", "Convolution2DForwardOp", "Convolution2DBackwardOp")
 
 
 def dot_err(got, want, mag):
-    """max of |got - want| / (|want| + 4 * 2^-24 * mag / 1e-4): <= 1e-4 means the contraction criterion holds."""
+    """max of |got - want| / (|want| + 8 * 2^-24 * mag / 1e-4): <= 1e-4 means the contraction criterion holds."""
     want, got, mag = np.asarray(want, np.float64), np.asarray(got, np.float64), np.asarray(mag, np.float64)
-    return float((np.abs(got - want) / np.maximum(np.abs(want) + 4 * 2.0 ** -24 * mag * 1e4, 1e-300)).max())
+    return float((np.abs(got - want) / np.maximum(np.abs(want) + 8 * 2.0 ** -24 * mag * 1e4, 1e-300)).max())
 
 
 def rel_err(got, want, floor=1e-2, atol=0.0):
@@ -76,8 +76,9 @@ def check_end_to_end(ex, model, feed_np, loss, next_feed, lr, rel=1e-4, fp32_env
     where sixteen or more chained fp32 layers leave more than 1e-4 of rounding noise on the first layers'
     gradients whatever executes them) a gradient may instead be within 5x of the error that the float32
     numpy execution of the same graph shows against the float64 oracle.  (Both sides of that comparison are maxima
-    over millions of elements of chaotic rounding noise, and the split reductions add with atomics in a different
-    order every run: over 30 runs the ratio ranged from 0.9x to 2.5x.)"""
+    over millions of elements of chaotic rounding noise; the GPU side is bit-reproducible from run to run - no kernel
+    adds floating-point values with atomics - but the two executions round differently, and the ratio of their maxima
+    moves between about 0.9x and 2.5x with the seed.)"""
     orc, vals = oracle_step(ex, feed_np)
     vals32 = oracle_step(ex, feed_np, dtype=np.float32)[1] if fp32_envelope else None
     assert rel_err(loss.asnumpy(), vals[model.loss]) <= rel, "loss"

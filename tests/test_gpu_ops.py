@@ -2,9 +2,10 @@
 CPU oracle (float64) on the same seeded inputs.  Tolerances for floating point:
 
 * dense contractions (matmul, the three convolution passes): per element
-  |got - want| <= 1e-4 * |want| + 4 * 2^-24 * sum_i |a_i| |b_i|, i.e. relative 1e-4, or four units of
+  |got - want| <= 1e-4 * |want| + 8 * 2^-24 * sum_i |a_i| |b_i|, i.e. relative 1e-4, or eight units of
   fp32 roundoff of the dot product's own magnitude where the terms cancel (an fp32 accumulation - the
-  reference's cuBLAS / cuDNN arithmetic - cannot do better on such an element; there is no floor tied to the
+  reference's cuBLAS / cuDNN arithmetic - lands 2.5 to 4 such units from the exact value on the worst of a
+  few million elements, see the exact-fp32 CUDA-core path in these tests; there is no floor tied to the
   tensor's largest value), plus ||got - want||_2 <= 5e-5 * ||want||_2;
 * everything else: |got - want| <= 1e-4 * max(|want|, 1e-2 * max|want|) (the floor is 16 units of fp32
   roundoff of the tensor's largest element: outputs that are differences of O(max) quantities);
@@ -22,7 +23,7 @@ RNG = np.random.RandomState(42)
 ULP = 2.0 ** -24          # unit roundoff of fp32
 
 
-def close_dot(got, want, mag, rel=1e-4, ulps=4.0, what=""):
+def close_dot(got, want, mag, rel=1e-4, ulps=8.0, what=""):
     """Parity of a dense contraction: `mag` is the same contraction evaluated on the absolute values of the operands."""
     want, got, mag = np.asarray(want, np.float64), np.asarray(got, np.float64), np.asarray(mag, np.float64)
     assert got.shape == want.shape == mag.shape, (what, got.shape, want.shape)
@@ -605,6 +606,35 @@ def test_host_link_probe_runs(env, capfd):
     import re
     nums = [float(v) for v in re.findall(r"(\d+\.\d+)", out)]
     assert len(nums) >= 4 and all(v > 0.1 for v in nums[:4]), out
+
+
+# ---- failure reporting of the tensor path -----------------------------------------------------------------------------
+def test_bounded_barrier_wait_reports_refuses_and_recovers(env):
+    """Every barrier wait of the tensor-core kernels has a cycle limit.  The probe kernel waits, with a 20,000-cycle
+    limit, on a barrier nothing arms: it returns by itself, the library's error word is raised, tensor-core launches are
+    refused (return -1) until the word is cleared, and after that the path works again."""
+    from tinyflow_b200._base import _LIB, TinyflowError
+    assert env.gpu_op.tensor_path_error() == 0
+    A, B = f32(256, 512), f32(512, 128)
+    C = env.empty((256, 128))
+    try:
+        assert _LIB.TfTensorPathTimeoutProbe(ctypes.c_longlong(20000), env.stream) == 0
+        assert _LIB.TfDeviceSynchronize() == -1               # the synchronising call reports the time-out
+        assert env.gpu_op.tensor_path_error() == 1
+        env.gpu_op.set_contraction_path(2)
+        with pytest.raises(TinyflowError):
+            env.gpu_op.matrix_multiply(env.dev(A), False, env.dev(B), False, C, env.cublas, env.stream)
+    finally:
+        env.gpu_op.clear_tensor_path_error()
+        env.gpu_op.set_contraction_path(0)
+    assert env.gpu_op.tensor_path_error() == 0
+    env.gpu_op.set_contraction_path(2)
+    try:
+        env.gpu_op.matrix_multiply(env.dev(A), False, env.dev(B), False, C, env.cublas, env.stream)
+    finally:
+        env.gpu_op.set_contraction_path(0)
+    a64, b64 = A.astype(np.float64), B.astype(np.float64)
+    close_dot(C.asnumpy(), a64 @ b64, np.abs(a64) @ np.abs(b64), what="matmul after the error word was cleared")
 
 
 # ---- size-independent properties at benchmark sizes ---------------------------------------------------------------------

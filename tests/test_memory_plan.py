@@ -93,14 +93,9 @@ def test_step_under_a_swap_and_release_plan_matches_the_plain_step(lib_path, opt
     loss0, w0, used0, _p0, _h0 = one_step(False)
     loss1, w1, used1, passive, swapped = one_step(True)
     assert swapped > 20 and passive == 0
-    assert abs(loss1 - loss0) <= 1e-5 * abs(loss0)
+    assert loss1 == loss0
     for k in w0:
         scale = max(np.abs(w0[k]).max(), 1e-12)
         diff = np.abs(w1[k] - w0[k])
-        if optimizer == "sgd":
-            assert diff.max() <= 2e-5 * scale, k      # atomics reorder the split reductions: not bit-exact
-        else:
-            # Adam's first step is lr * sign(g): reordering noise can flip the sign of a gradient that is zero up to
-            # rounding, nothing else may move
-            assert np.mean(diff > 1e-6 * scale) < 0.01, k
+        assert diff.max() == 0.0, k                   # every kernel is bit-reproducible: the plan changes nothing
     assert used1 < 0.85 * used0          # parameters, optimiser state and the packed operands of the conv plans stay

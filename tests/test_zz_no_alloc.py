@@ -5,7 +5,9 @@ launch sequence, or an executor inside a memory plan that has given away every b
 that even the pool's occasional cudaMalloc could fail or stall.  The variant keeps its per-block partial
 sums in a fixed array inside the library; this test checks, through the C-ABI, that it returns what
 DLGpuReduceSumAll returns, on two calls in a row (the second smaller, so stale partials from the first
-would show), and that it refuses inputs beyond its stated capacity.  Collected last on purpose."""
+would show), that the device allocator's books (bytes handed out, bytes cached) do not move across a call -
+the property the entry point exists for - and that it refuses inputs beyond its stated capacity.
+Collected last on purpose."""
 import ctypes
 
 import numpy as np
@@ -16,11 +18,21 @@ pytestmark = pytest.mark.gpu
 MAX_ELEMS = 4096 * 8192
 
 
+def _stats(lib):
+    used, cached = ctypes.c_longlong(0), ctypes.c_longlong(0)
+    assert lib.TfAllocatorStats(ctypes.byref(used), ctypes.byref(cached)) == 0
+    return used.value, cached.value
+
+
 def _sum_both(lib, nd, ctx, stream, x):
     dx = nd.array(x, ctx)
-    a, b = nd.empty((1,), ctx), nd.empty((1,), ctx)
+    a, b, c = nd.empty((1,), ctx), nd.empty((1,), ctx), nd.empty((1,), ctx)
     assert lib.DLGpuReduceSumAll(dx.handle, a.handle) == 0
+    before = _stats(lib)
     assert lib.DLGpuReduceSumAllStatic(dx.handle, b.handle, stream) == 0
+    assert lib.DLGpuReduceSumAllStatic(dx.handle, c.handle, stream) == 0
+    assert _stats(lib) == before, "the allocation-free entry point touched the device allocator"
+    assert float(b.asnumpy()[0]) == float(c.asnumpy()[0])           # same stream, same input: same bits
     return float(a.asnumpy()[0]), float(b.asnumpy()[0])
 
 

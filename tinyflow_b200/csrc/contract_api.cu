@@ -22,6 +22,7 @@ int tensor_arithmetic();
 void set_tensor_arithmetic(int a);
 int tensor_path_error();
 void tensor_path_error_clear();
+int tensor_path_timeout_probe(long long limit_cycles, cudaStream_t s);
 // which engine served this thread's most recent contraction: 1 = CUDA cores, 2 = tensor cores (0 = none yet)
 static thread_local int t_last_path = 0;
 
@@ -42,6 +43,7 @@ int TfGetArithmetic(void) { return tensor_arithmetic(); }
 
 int TfTensorPathError(void) { return tensor_path_error(); }
 int TfClearTensorPathError(void) { tensor_path_error_clear(); return 0; }
+int TfTensorPathTimeoutProbe(long long limit_cycles, void** cudaStream) { return tensor_path_timeout_probe(limit_cycles, stream_of(cudaStream)); }
 
 int TfSetContractionPath(int path) {
   TF_REQUIRE(path >= 0 && path <= 2, "TfSetContractionPath: path must be 0, 1 or 2");

@@ -86,8 +86,10 @@ struct NchwOut {            // rows = channel, cols = (image, pixel)
 };
 
 // B_KFAST: consecutive loader threads walk K (for operands contiguous along K) instead of N.
-template <class AV, class BV, class OV, bool B_KFAST, bool ATOMIC>
-__global__ void __launch_bounds__(256) contract_kernel(AV A, BV B, OV O, int64_t M, int64_t N, int64_t K, int64_t k_per_split) {
+// SPLIT: the reduction is cut over blockIdx.z; every cut writes its partial [M x N] result to `part` and
+// contract_reduce_kernel adds the cuts in order (bit-reproducible, unlike atomic adds).
+template <class AV, class BV, class OV, bool B_KFAST, bool SPLIT>
+__global__ void __launch_bounds__(256) contract_kernel(AV A, BV B, OV O, int64_t M, int64_t N, int64_t K, int64_t k_per_split, float* __restrict__ part) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
   int tid = threadIdx.x;
@@ -137,9 +139,19 @@ __global__ void __launch_bounds__(256) contract_kernel(AV A, BV B, OV O, int64_t
     for (int j = 0; j < TN; ++j) {
       int64_t gn = n0 + tx * TN + j;
       if (gn >= N) continue;
-      float* o = O.ptr(gm, gn);
-      if (ATOMIC) atomicAdd(o, acc[i][j]); else *o = acc[i][j];
+      if (SPLIT) part[((int64_t)blockIdx.z * M + gm) * N + gn] = acc[i][j];
+      else *O.ptr(gm, gn) = acc[i][j];
     }
+  }
+}
+
+template <class OV>
+__global__ void __launch_bounds__(256) contract_reduce_kernel(const float* __restrict__ part, OV O, int64_t M, int64_t N, int splits) {
+  const int64_t total = M * N, stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    float v = 0.f;
+    for (int z = 0; z < splits; ++z) v += part[(int64_t)z * total + i];
+    *O.ptr(i / N, i % N) = v;
   }
 }
 
@@ -163,12 +175,18 @@ static int launch_contract(AV A, BV B, OV O, int64_t M, int64_t N, int64_t K, fl
   note_compute_stream(s);
   KernelTimer kt("contract_cudacore", s, 2.0 * (double)M * (double)N * (double)K, 0, 1);
   dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)splits);
+  (void)out_base; (void)out_bytes;
   if (splits > 1) {
-    TF_CUDA(cudaMemsetAsync(out_base, 0, out_bytes, s));
-    contract_kernel<AV, BV, OV, B_KFAST, true><<<grid, 256, 0, s>>>(A, B, O, M, N, K, kps);
-  } else {
-    contract_kernel<AV, BV, OV, B_KFAST, false><<<grid, 256, 0, s>>>(A, B, O, M, N, K, kps);
+    float* part = (float*)persistent_scratch(3, sizeof(float) * (size_t)splits * (size_t)M * (size_t)N);
+    if (!part) { splits = 1; kps = (K + BK - 1) / BK * BK; grid.z = 1; }       // no scratch: run unsplit
+    else {
+      contract_kernel<AV, BV, OV, B_KFAST, true><<<grid, 256, 0, s>>>(A, B, O, M, N, K, kps, part);
+      contract_reduce_kernel<OV><<<grid_for(M * N, 256), 256, 0, s>>>(part, O, M, N, splits);
+      if (after_launch(s, what, 2) != 0) return -1;
+      return 0;
+    }
   }
+  contract_kernel<AV, BV, OV, B_KFAST, false><<<grid, 256, 0, s>>>(A, B, O, M, N, K, kps, nullptr);
   TF_AFTER(s, what);
   return 0;
 }

@@ -147,13 +147,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises *abort_flag) if the barrier does not flip in time or another
 // role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, long long limit_cycles = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   for (;;) {
     for (int i = 0; i < 64; ++i) if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; return false; }
+    if (clock64() - t0 > limit_cycles) { *abort_flag = 1; return false; }
   }
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -163,6 +163,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
                ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+// im2col-mode load over a [N][H][W][C] tensor: `pixels` consecutive base pixels starting at (w, h, n) - walking w, then h,
+// then n inside the map's bounding box - each displaced by the window offset (off_w, off_h); positions outside the
+// tensor read as zero.  Lands [pixels][channels of one 128-byte row], swizzled like a tiled load.
+__device__ __forceinline__ void tma_load_im2col(void* dst, const CUtensorMap* map, int c, int w, int h, int n, int off_w, int off_h, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
+                 "h"((unsigned short)off_w), "h"((unsigned short)off_h) : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -250,8 +258,17 @@ struct alignas(64) GemmParams {
   // rows with i >= valid_h, j >= valid_w or (oi, oj) outside the plane are dropped
   int frame_h, frame_w, valid_h, valid_w, out_c, out_h, out_w, out_sh, out_sw, out_off_h, out_off_w;
   int* err;                       // device-visible error word (mapped host memory)
+  // im2col != 0: the activation operand A is a halo-free [N][im_h'][im_w'][C] pack read through an im2col tensor map;
+  // rows of the GEMM are the im_h x im_w base pixels per image (the output positions), the map's lower corner is
+  // (im_lo_w, im_lo_h) and tap t adds the window offset (tap_off[t] & 0xffff, tap_off[t] >> 16)
+  int im2col, im_w, im_h, im_lo_w, im_lo_h;
   int slot, taps_per_tile;        // kModeWgrad: M-tile rows are taps_per_tile slots of `slot` input channels, one filter tap per slot
   int group_iters;                // stages accumulated in TMEM before the epilogue promotes them to registers
+  // Where the two small cross terms accumulate.  0: A_lo*B_hi joins A_hi*B_hi (block 0), A_hi*B_lo alone in block 1.
+  // 1: both cross terms in block 1.  2: the B stage is laid out [B_lo ; B_hi], so the wide MMA leaves A_hi*B_lo in block 0
+  // and A_hi*B_hi in block 1, and A_lo*B_hi joins block 0.  In 1 and 2 the large accumulator sees one truncating
+  // accumulation per K step instead of two; in 2 the narrow MMA depends on the first half of the wide one, not the last.
+  int acc_layout;
   int tap_off[kMaxTaps];          // row shift per tap (applied to the activation operand A)
   short tap_col[kMaxTaps];        // first column of the tap's channels in A (space-to-depth packs keep one phase per column block)
   short tap_b[kMaxTaps];          // kModeConv: which tap block of the packed filter the tap multiplies
@@ -377,10 +394,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3x_kernel(const __grid_consta
         int mt, nt, tap;
         decode_tile(p, w.tile, mt, nt, tap);
         const int m0 = mt * BM, n0 = nt * BN;
+        // im2col convolution: base pixel (image, row, column) of the tile's first GEMM row
+        int im_n = 0, im_y = 0, im_x = 0;
+        if (p.im2col && p.mode == kModeConv) {
+          const int per_img = p.im_w * p.im_h;
+          im_n = m0 / per_img;
+          const int rem = m0 - im_n * per_img;
+          im_y = rem / p.im_w; im_x = rem - im_y * p.im_w;
+        }
         for (int it = 0; it < w.kcount; ++it) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* st = smem + stage * L::kStageBytes;
-          uint8_t *a_hi = st, *a_lo = st + L::kABytes, *b_hi = st + 2 * L::kABytes, *b_lo = b_hi + L::kBBytes;
+          uint8_t *a_hi = st, *a_lo = st + L::kABytes;
+          uint8_t *b_hi = st + 2 * L::kABytes + (p.acc_layout == 2 ? L::kBBytes : 0), *b_lo = st + 2 * L::kABytes + (p.acc_layout == 2 ? 0 : L::kBBytes);
           mbar_expect_tx(&full[stage], L::kStageBytes);
           armed[stage] = true; armed_phase[stage] = phase;
           const int git = w.k0 + it;                  // stage index within the tile's reduction
@@ -400,7 +426,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3x_kernel(const __grid_consta
           }
           // M/N-major operands come through a 3-D view {group width, rows, column groups}: one copy lands
           // [groups][BK rows][128 B], the layout the M/N-major descriptor expects.
-          if (p.mode == kModeWgrad) {
+          if (p.mode == kModeConv && p.im2col) {
+            const int t = git / p.chunks_per_tap;
+            const int ow = p.tap_off[t] & 0xffff, oh = p.tap_off[t] >> 16;
+            tma_load_im2col(a_hi, &p.a_hi, a_col, im_x + p.im_lo_w, im_y + p.im_lo_h, im_n, ow, oh, &full[stage]);
+            tma_load_im2col(a_lo, &p.a_lo, a_col, im_x + p.im_lo_w, im_y + p.im_lo_h, im_n, ow, oh, &full[stage]);
+          } else if (p.mode == kModeWgrad && p.im2col) {
+            // the K rows of this stage are BK consecutive output pixels; every tap slot reads the input pixels they
+            // touch through the im2col map, one 128-byte channel group per copy.  A slot past the last tap asks for
+            // an image index beyond the batch and receives zeros.
+            const int per_img = p.im_w * p.im_h;
+            const int pn = a_row / per_img, prem = a_row - pn * per_img, py = prem / p.im_w, px = prem - py * p.im_w;
+            const int gps = p.slot / T::kGW;
+            for (int sl = 0; sl < p.taps_per_tile; ++sl) {
+              const int t = tap * p.taps_per_tile + sl;
+              const bool live = t < p.ntaps;
+              const int ow = live ? (p.tap_off[t] & 0xffff) : 0, oh = live ? (p.tap_off[t] >> 16) : 0;
+              const int bn_img = live ? pn : 0x00400000;
+              for (int gq = 0; gq < gps; ++gq) {
+                const int c = a_col + gq * T::kGW;
+                tma_load_im2col(a_hi + (sl * gps + gq) * kGroupStride, &p.a_hi, c, px + p.im_lo_w, py + p.im_lo_h, bn_img, ow, oh, &full[stage]);
+                tma_load_im2col(a_lo + (sl * gps + gq) * kGroupStride, &p.a_lo, c, px + p.im_lo_w, py + p.im_lo_h, bn_img, ow, oh, &full[stage]);
+              }
+            }
+          } else if (p.mode == kModeWgrad) {
             // One copy per tap slot; a slot past the last tap reads rows beyond the pack (the copy still completes
             // with its full byte count and fills zeros).
             const int gps = p.slot / T::kGW;
@@ -472,13 +521,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3x_kernel(const __grid_consta
             if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
             tcgen05_fence_after();
             const uint32_t st = smem_u32(smem + stage * L::kStageBytes);
-            const uint32_t a_hi = st, a_lo = st + L::kABytes, b_hi = st + 2 * L::kABytes;
+            const uint32_t a_hi = st, a_lo = st + L::kABytes, b_pair = st + 2 * L::kABytes;     // [B_hi ; B_lo], or [B_lo ; B_hi] in layout 2
+            const uint32_t b_hi = b_pair + (p.acc_layout == 2 ? L::kBBytes : 0);
+            const uint32_t d_narrow = d_tmem + (p.acc_layout == 1 ? BN : 0);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               const uint64_t ah = umma_desc(a_hi + k * a_kstep, a_lbo, a_sbo, a_lt), al = umma_desc(a_lo + k * a_kstep, a_lbo, a_sbo, a_lt);
-              const uint64_t bh = umma_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lt);      // N = 2*BN runs on into B_lo
-              umma<AR>(d_tmem, ah, bh, idesc_wide, (it > it0 || k > 0) ? 1u : 0u);
-              umma<AR>(d_tmem + BN, al, bh, idesc_narrow, 1u);
+              const uint64_t bw = umma_desc(b_pair + k * b_kstep, b_lbo, b_sbo, b_lt);    // N = 2*BN runs on into the second B tile
+              const uint64_t bh = umma_desc(b_hi + k * b_kstep, b_lbo, b_sbo, b_lt);
+              umma<AR>(d_tmem, ah, bw, idesc_wide, (it > it0 || k > 0) ? 1u : 0u);
+              umma<AR>(d_narrow, al, bh, idesc_narrow, 1u);
             }
             tcgen05_commit(&empty[stage]);       // frees the stage once the MMAs above have read it
             if (++stage == L::kStages) { stage = 0; phase ^= 1; }
@@ -577,8 +629,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3x_kernel(const __grid_consta
 #pragma unroll
         for (int c0 = 0; c0 < HC; c0 += 16) {
           float v1[16], v2[16];
-          tmem_ld16(t_base + c0, v1);              // A_hi*B_hi
-          tmem_ld16(t_base + BN + c0, v2);         // A_hi*B_lo + A_lo*B_hi
+          tmem_ld16(t_base + c0, v1);              // the two accumulator blocks (which terms sit where: acc_layout)
+          tmem_ld16(t_base + BN + c0, v2);
           tmem_ld_wait();
 #pragma unroll
           for (int q = 0; q < 16; ++q) accv[c0 + q] += v1[q] + v2[q];
@@ -613,9 +665,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3x_kernel(const __grid_consta
 
 // Adds up the pieces of every split tile (the tail of the schedule) in a fixed order and writes the result where the
 // GEMM's own epilogue would have.  grid (tail_tiles, BN / kReduceCols), block (128 rows, kReduceWays): the pieces of a
-// tile are dealt round robin to the kReduceWays row groups, each adds its share in piece order, and the row group 0
-// adds the kReduceWays subtotals in order - the same order every run, so the result is bit-reproducible.
-constexpr int kReduceCols = 4, kReduceWays = 8;
+// tile are dealt round robin to the kReduceWays row groups, each adds its share in piece order, and the subtotals are
+// added in row-group order - the same order every run, so the result is bit-reproducible.
+constexpr int kReduceCols = 8, kReduceWays = 4;
 template <int BN>
 __global__ void __launch_bounds__(BM * kReduceWays) reduce_partials_kernel(const __grid_constant__ GemmParams p) {
   __shared__ float part[kReduceWays][kReduceCols][BM];
@@ -632,26 +684,56 @@ __global__ void __launch_bounds__(BM * kReduceWays) reduce_partials_kernel(const
   float sum[kReduceCols];
 #pragma unroll
   for (int q = 0; q < kReduceCols; ++q) sum[q] = 0.f;
-  for (int g = g_first + way; g <= g_last; g += kReduceWays) {
+  // four pieces per trip: their loads are independent and all in flight before the first add (a tile of a long
+  // reduction has dozens of pieces, and the loop would otherwise pay the memory latency once per piece)
+  auto piece = [&](int g) -> const float* {
     const int slot = g * p.slots_per_cta + (t - (int)(((long long)g * p.tail_share) / p.k_total));
-    const float* ws = p.workspace + ((size_t)slot * BN + c_begin) * BM + row;
+    return p.workspace + ((size_t)slot * BN + c_begin) * BM + row;
+  };
+  int g = g_first + way;
+  for (; g + 3 * kReduceWays <= g_last; g += 4 * kReduceWays) {
+    const float *w0 = piece(g), *w1 = piece(g + kReduceWays), *w2 = piece(g + 2 * kReduceWays), *w3 = piece(g + 3 * kReduceWays);
+    float v0[kReduceCols], v1[kReduceCols], v2[kReduceCols], v3[kReduceCols];
 #pragma unroll
-    for (int q = 0; q < kReduceCols; ++q) sum[q] += ws[(size_t)q * BM];
+    for (int q = 0; q < kReduceCols; ++q) { v0[q] = __ldcg(w0 + (size_t)q * BM); v1[q] = __ldcg(w1 + (size_t)q * BM); v2[q] = __ldcg(w2 + (size_t)q * BM); v3[q] = __ldcg(w3 + (size_t)q * BM); }
+#pragma unroll
+    for (int q = 0; q < kReduceCols; ++q) sum[q] = (((sum[q] + v0[q]) + v1[q]) + v2[q]) + v3[q];
+  }
+  for (; g <= g_last; g += kReduceWays) {
+    const float* ws = piece(g);
+#pragma unroll
+    for (int q = 0; q < kReduceCols; ++q) sum[q] += __ldcg(ws + (size_t)q * BM);
   }
 #pragma unroll
   for (int q = 0; q < kReduceCols; ++q) part[way][q][row] = sum[q];
   __syncthreads();
-  if (way != 0) return;
+  // every row group finishes a quarter of the block's columns: subtotals added in row-group order
   const RowAddr ra = row_address(p, mt, tap, row);
   if (!ra.ok) return;
   const float inv_scale = (1.f / __ldg(p.a_scale)) * (1.f / __ldg(p.b_scale));
+  constexpr int kPer = kReduceCols / kReduceWays;
 #pragma unroll
-  for (int q = 0; q < kReduceCols; ++q) {
-    float v = sum[q];
+  for (int j = 0; j < kPer; ++j) {
+    const int q = way * kPer + j;
+    float v = part[0][q][row];
 #pragma unroll
     for (int w2 = 1; w2 < kReduceWays; ++w2) v += part[w2][q][row];
     const int n = nt * BN + c_begin + q;
     if (n < p.N) p.out[ra.base + (long long)n * ra.col_stride] = v * inv_scale;
+  }
+}
+
+// Exercises the bounded wait on its own: one thread waits, with a short limit, on a barrier that nothing arms; the wait
+// gives up, raises the CTA's abort flag and the kernel reports it through the error word exactly as the GEMM does.
+__global__ void barrier_timeout_probe_kernel(long long limit_cycles, int* err) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const bool flipped = mbar_wait(&bar, 0, &abort_flag, limit_cycles);
+    if (!flipped && abort_flag && err) atomicExch(err, 1);
   }
 }
 
@@ -997,6 +1079,39 @@ static int make_map_mn(CUtensorMap* m, int ar, const void* base, long long rows,
   return 0;
 }
 
+// im2col-mode map over a halo-free pixel-major pack [N][H][W][pitch]: base pixels range over the box
+// [-lo_w, W - lo_w' ) x [-lo_h, ...) that holds one base pixel per output position of a stride-1 window of
+// win_w x win_h with lo_w / lo_h zero columns / rows in front (and as many behind as the output extent needs);
+// a copy brings `pixels` base pixels x `chans` channels (128 bytes).
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+static EncodeIm2colFn encode_im2col_fn() {
+  static EncodeIm2colFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+    return (EncodeIm2colFn)p;
+  }();
+  return fn;
+}
+static int make_map_im2col(CUtensorMap* m, int ar, const void* base, int N, int H, int W, long long pitch, int lo_w, int lo_h, int win_w, int win_h,
+                           int pixels, int chans) {
+  EncodeIm2colFn fn = encode_im2col_fn();
+  TF_REQUIRE(fn, "cuTensorMapEncodeIm2col is not available from this driver");
+  const int es = elem_of(ar);
+  cuuint64_t dims[4] = {(cuuint64_t)pitch, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
+  cuuint64_t strides[3] = {(cuuint64_t)pitch * es, (cuuint64_t)W * pitch * es, (cuuint64_t)H * W * pitch * es};
+  int lower[2] = {-lo_w, -lo_h};
+  int upper[2] = {lo_w - (win_w - 1), lo_h - (win_h - 1)};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, map_type(ar), 4, (void*)base, dims, strides, lower, upper, (cuuint32_t)chans, (cuuint32_t)pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeIm2col failed with %d (N %d H %d W %d pitch %lld lower %d,%d upper %d,%d)", (int)r, N, H, W, pitch, lower[0],
+             lower[1], upper[0], upper[1]);
+  return 0;
+}
+
 static std::mutex g_tc_mu;      // guards the lazily created process-wide state below
 static int* error_word() {      // mapped pinned word: the kernels raise it, the host polls it for free
   static int* host = nullptr;
@@ -1022,6 +1137,14 @@ static int* error_word_host() {
 }
 int tensor_path_error() { int* h = error_word_host(); return h ? *(volatile int*)h : 0; }
 void tensor_path_error_clear() { int* h = error_word_host(); if (h) *(volatile int*)h = 0; }
+
+int tensor_path_timeout_probe(long long limit_cycles, cudaStream_t s) {
+  int* err = error_word();
+  TF_REQUIRE(err, "the error word could not be mapped");
+  TF_REQUIRE(limit_cycles > 0 && limit_cycles <= 2000000000ll, "limit must be between 1 and 2e9 cycles");
+  barrier_timeout_probe_kernel<<<1, 32, 0, s>>>(limit_cycles, err);
+  return after_launch(s, "barrier_timeout_probe", 1);
+}
 
 // Arithmetic of the tensor path: 0 = 3xFP16 (scaled fp16 hi/lo pairs, kind::f16), 1 = 3xTF32 (tf32 hi/lo pairs, kind::tf32).
 static std::atomic<int> g_arith{[] { const char* e = getenv("TINYFLOW_ARITH"); return (e && (!strcmp(e, "3xtf32") || !strcmp(e, "1"))) ? 1 : 0; }()};
@@ -1070,6 +1193,8 @@ template <int BN, int AR> static int launch_gemm(const GemmParams& p, cudaStream
   TF_REQUIRE(tensor_path_error() == 0, "%s: an earlier tensor-core kernel timed out on a barrier; refusing to launch", what);
   static const int group_iters = getenv("TINYFLOW_GROUP_ITERS") ? atoi(getenv("TINYFLOW_GROUP_ITERS")) : kGroupIters;
   const_cast<GemmParams&>(p).group_iters = group_iters > 0 ? group_iters : kGroupIters;
+  static const int acc_layout = getenv("TINYFLOW_ACC_LAYOUT") ? atoi(getenv("TINYFLOW_ACC_LAYOUT")) : 2;
+  const_cast<GemmParams&>(p).acc_layout = acc_layout;
   const int sms = device_sm_count();
   const int tiles = p.full_tiles + p.tail_tiles;
   int grid = tiles < sms ? tiles : sms;
@@ -1240,8 +1365,20 @@ static ConvTc* conv_state(ConvPlan* p) {
     if (ok && p->R == 1 && p->S == 1 && p->pad_h == 0 && p->pad_w == 0) {
       st->cls = 1; st->frame_h = p->P; st->frame_w = p->Q;
     } else if (ok && p->stride_h == 1 && p->stride_w == 1 && p->pad_h <= p->R - 1 && p->pad_w <= p->S - 1) {
-      st->cls = 2; st->frame_h = p->H + p->R - 1; st->frame_w = p->W + p->S - 1;
-      st->x_off_h = p->pad_h; st->x_off_w = p->pad_w; st->dy_off_h = p->R - 1 - p->pad_h; st->dy_off_w = p->S - 1 - p->pad_w;
+      st->cls = 2;
+      static const bool shared_halo = [] { const char* e = getenv("TINYFLOW_SHARED_HALO"); return e ? atoi(e) != 0 : true; }();
+      if (shared_halo) {
+        // x and dy both sit at the frame's origin and the frame is only max(pad, window-1-pad) wider / taller than the
+        // input: a tap that reaches left of column 0 lands in the zero gap that ends the previous frame row (right of
+        // the last column: the gap of its own row), above row 0 in the zero rows that end the previous image (or before
+        // the pack: zero fill).  The gap is shared by both sides, so the frame has (H+g)(W+g) positions instead of
+        // (H+R-1)(W+S-1): 1.31x the outputs instead of 1.65x at 7x7 with a 3x3 window.
+        const int gh = std::max(p->pad_h, p->R - 1 - p->pad_h), gw = std::max(p->pad_w, p->S - 1 - p->pad_w);
+        st->frame_h = p->H + gh; st->frame_w = p->W + gw;
+      } else {
+        st->frame_h = p->H + p->R - 1; st->frame_w = p->W + p->S - 1;
+        st->x_off_h = p->pad_h; st->x_off_w = p->pad_w; st->dy_off_h = p->R - 1 - p->pad_h; st->dy_off_w = p->S - 1 - p->pad_w;
+      }
     } else if (ok && p->stride_h * p->stride_w <= 16 && p->pad_h <= p->R - 1 && p->pad_w <= p->S - 1 &&
                (long long)p->stride_h * p->stride_w * round_up(p->C, 64) < 32768) {
       // strided window: x is split into stride_h*stride_w phases (space to depth), each tap reads one phase at a
@@ -1264,12 +1401,12 @@ static ConvTc* conv_state(ConvPlan* p) {
 
 // One launch of the frame pack: `chans` channels of an NCHW tensor (spatial dims H x W) into columns dst_c0 .. dst_c0 + cover
 // of pk (zeros past `chans`)
-static int launch_pack_nchw(Pack& pk, const ScaleRef& sr, const float* src, int N, int chans, int H, int W, const ConvTc* st, int off_h, int off_w,
+static int launch_pack_nchw(Pack& pk, const ScaleRef& sr, const float* src, int N, int chans, int H, int W, int frame_h, int frame_w, int off_h, int off_w,
                             int sh, int sw, int dst_c0, int cover, cudaStream_t s) {
-  PackGeom g{N, chans, H, W, st->frame_h, st->frame_w, off_h, off_w, sh, sw, (int)pk.pitch, dst_c0, cover};
+  PackGeom g{N, chans, H, W, frame_h, frame_w, off_h, off_w, sh, sw, (int)pk.pitch, dst_c0, cover};
   const int tc = cover > 64 ? 128 : cover > 32 ? 64 : 32;
-  dim3 grid(N * ((cover + tc - 1) / tc), (st->frame_h * st->frame_w + 31) / 32);
-  TF_REQUIRE(grid.y <= 65535, "pack: frame of %d x %d positions is too large", st->frame_h, st->frame_w);
+  dim3 grid(N * ((cover + tc - 1) / tc), (frame_h * frame_w + 31) / 32);
+  TF_REQUIRE(grid.y <= 65535, "pack: frame of %d x %d positions is too large", frame_h, frame_w);
   KernelTimer kt("pack_nchw", s, 0, 4.0 * N * chans * H * W / (sh * sw) + 2.0 * elem_of(pk.arith) * pk.rows * cover);
   with_elems(pk, [&](auto* hi, auto* lo) {
     using E = std::remove_pointer_t<decltype(hi)>;
@@ -1315,10 +1452,10 @@ static int pack_x(ConvTc* st, int ar, const ConvPlan* p, const float* x, cudaStr
     for (int a = 0; a < p->stride_h && !rc; ++a)
       for (int b = 0; b < p->stride_w && !rc; ++b) {
         int ph = a * p->stride_w + b;
-        rc = launch_pack_nchw(pk, sr, x, p->N, p->C, p->H, p->W, st, p->pad_h - a, p->pad_w - b, p->stride_h, p->stride_w, ph * st->cp, st->cp, s);
+        rc = launch_pack_nchw(pk, sr, x, p->N, p->C, p->H, p->W, st->frame_h, st->frame_w, p->pad_h - a, p->pad_w - b, p->stride_h, p->stride_w, ph * st->cp, st->cp, s);
       }
   } else {
-    rc = launch_pack_nchw(pk, sr, x, p->N, p->C, p->H, p->W, st, st->x_off_h, st->x_off_w, p->stride_h, p->stride_w, 0, (int)pk.pitch, s);
+    rc = launch_pack_nchw(pk, sr, x, p->N, p->C, p->H, p->W, st->frame_h, st->frame_w, st->x_off_h, st->x_off_w, p->stride_h, p->stride_w, 0, (int)pk.pitch, s);
   }
   if (rc) return -1;
   pk.src = x; pk.version = ver; pk.tag = st->cls;
@@ -1331,8 +1468,19 @@ static int pack_dy(ConvTc* st, int ar, const ConvPlan* p, const float* dy, cudaS
   if (pack_valid(pk, ar, dy, ver, 2, rows, p->K)) return 0;
   if (pack_alloc(pk, ar, rows, p->K, s, oom)) return 1;
   ScaleRef sr = begin_pack(pk, dy, (long long)p->N * p->K * p->P * p->Q, s);
-  if (launch_pack_nchw(pk, sr, dy, p->N, p->K, p->P, p->Q, st, st->dy_off_h, st->dy_off_w, 1, 1, 0, (int)pk.pitch, s)) return -1;
+  if (launch_pack_nchw(pk, sr, dy, p->N, p->K, p->P, p->Q, st->frame_h, st->frame_w, st->dy_off_h, st->dy_off_w, 1, 1, 0, (int)pk.pitch, s)) return -1;
   pk.src = dy; pk.version = ver; pk.tag = 2;
+  return 0;
+}
+// Halo-free pixel-major packs [N][H][W][C] of x and [N][P][Q][K] of dy for the im2col route (tags 20 / 21)
+static int pack_plain(Pack& pk, int ar, int tag, const float* src, int N, int chans, int H, int W, cudaStream_t s, int* oom) {
+  const uint64_t ver = version_of(src);
+  const long long rows = (long long)N * H * W;
+  if (pack_valid(pk, ar, src, ver, tag, rows, chans)) return 0;
+  if (pack_alloc(pk, ar, rows, chans, s, oom)) return 1;
+  ScaleRef sr = begin_pack(pk, src, rows * chans, s);
+  if (launch_pack_nchw(pk, sr, src, N, chans, H, W, H, W, 0, 0, 1, 1, 0, (int)pk.pitch, s)) return -1;
+  pk.src = src; pk.version = ver; pk.tag = tag;
   return 0;
 }
 // Filter packs are keyed like the activation packs (pointer, write version): an optimiser step bumps the version.
@@ -1379,20 +1527,31 @@ static int pack_filter(ConvTc* st, int ar, const float* w, const ConvPlan* p, in
 struct TapList { int n = 0; int off[kMaxTaps]; int col[kMaxTaps]; int b[kMaxTaps]; void add(int o, int c, int bb) { off[n] = o; col[n] = c; b[n] = bb; ++n; } };
 struct OutGeom { int valid_h, valid_w, out_h, out_w, out_sh, out_sw, out_off_h, out_off_w; };
 // returns 0 on success, -1 on error, 1 when scratch memory was short (*oom set)
-static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, const ConvTc* st, float* out, const TapList& taps,
-                     const OutGeom& og, double flops, cudaStream_t s, const char* what, int* oom) {
+// Geometry of an im2col read of the activation pack: the pack is [N][H][W][pitch]; a stride-1 window of win_w x win_h
+// with lo_w / lo_h zero columns / rows in front gives box_w x box_h base pixels (= output positions) per image.
+struct Im2colGeom { int N, H, W, lo_w, lo_h, win_w, win_h, box_w, box_h; };
+static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, int frame_h, int frame_w, float* out, const TapList& taps,
+                     const OutGeom& og, double flops, cudaStream_t s, const char* what, int* oom, const Im2colGeom* im = nullptr) {
   GemmParams g;
   memset(&g, 0, sizeof(g));
   const int ar = act.arith, bk = bk_of(ar);
   const int bn = pick_bn(ch_out, true);
   g.mode = kModeConv; g.epi = kEpiNchw;
-  int rc = make_map(&g.a_hi, ar, act.hi, act.rows, act.cols, act.pitch, BM);
-  if (!rc) rc = make_map(&g.a_lo, ar, act.lo, act.rows, act.cols, act.pitch, BM);
+  int rc;
+  if (im) {
+    rc = make_map_im2col(&g.a_hi, ar, act.hi, im->N, im->H, im->W, act.pitch, im->lo_w, im->lo_h, im->win_w, im->win_h, BM, bk);
+    if (!rc) rc = make_map_im2col(&g.a_lo, ar, act.lo, im->N, im->H, im->W, act.pitch, im->lo_w, im->lo_h, im->win_w, im->win_h, BM, bk);
+    g.im2col = 1; g.im_w = im->box_w; g.im_h = im->box_h; g.im_lo_w = -im->lo_w; g.im_lo_h = -im->lo_h;
+  } else {
+    rc = make_map(&g.a_hi, ar, act.hi, act.rows, act.cols, act.pitch, BM);
+    if (!rc) rc = make_map(&g.a_lo, ar, act.lo, act.rows, act.cols, act.pitch, BM);
+  }
   if (!rc) rc = make_map(&g.b_hi, ar, filt.hi, filt.rows, filt.cols, filt.pitch, bn);
   if (!rc) rc = make_map(&g.b_lo, ar, filt.lo, filt.rows, filt.cols, filt.pitch, bn);
   if (rc) return -1;
-  g.M = (int)act.rows; g.N = ch_out;
-  g.m_tiles = (int)((act.rows + BM - 1) / BM); g.n_tiles = (ch_out + bn - 1) / bn; g.tap_tiles = 1;
+  const long long m_rows = im ? (long long)im->N * im->box_w * im->box_h : act.rows;      // one GEMM row per output position
+  g.M = (int)m_rows; g.N = ch_out;
+  g.m_tiles = (int)((m_rows + BM - 1) / BM); g.n_tiles = (ch_out + bn - 1) / bn; g.tap_tiles = 1;
   g.ntaps = taps.n;
   g.chunks_per_tap = (ch_in + bk - 1) / bk;
   g.b_tap_pitch = (int)round_up(ch_in, 64);
@@ -1400,11 +1559,22 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, c
   for (int t = 0; t < taps.n; ++t) { g.tap_off[t] = taps.off[t]; g.tap_col[t] = (short)taps.col[t]; g.tap_b[t] = (short)taps.b[t]; }
   g.out = out; g.err = error_word();
   g.a_scale = act.scale(); g.b_scale = filt.scale();
-  g.frame_h = st->frame_h; g.frame_w = st->frame_w; g.valid_h = og.valid_h; g.valid_w = og.valid_w;
+  g.frame_h = frame_h; g.frame_w = frame_w; g.valid_h = og.valid_h; g.valid_w = og.valid_w;
   g.out_c = ch_out; g.out_h = og.out_h; g.out_w = og.out_w; g.out_sh = og.out_sh; g.out_sw = og.out_sw; g.out_off_h = og.out_off_h; g.out_off_w = og.out_off_w;
   return launch_gemm_bn(bn, ar, g, s, flops, what, oom);
 }
 static double conv_flops(const ConvPlan* p) { return 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S; }
+// Stride-1 windows (class B) in the fp16 arithmetic read halo-free packs through im2col tensor maps: the GEMM's rows are
+// the real output positions only (a halo frame spends (H+R-1)(W+S-1)/(HW) times the multiplies, 1.65x at 7x7), and the
+// packs are smaller.  TINYFLOW_IM2COL=0 keeps the halo frames.
+static bool use_im2col(const ConvTc* st, int ar) {
+  static const bool on = [] { const char* e = getenv("TINYFLOW_IM2COL"); return e ? atoi(e) != 0 : false; }();
+  return on && st->cls == 2 && ar == kArithF16 && encode_im2col_fn() != nullptr;
+}
+// window offsets of every tap, packed as (r << 16) | s
+static void im2col_taps(TapList& taps, int R, int S) {
+  for (int r = 0; r < R; ++r) for (int q = 0; q < S; ++q) taps.add((r << 16) | q, 0, r * S + q);
+}
 // result of a tensor-path entry point from the launcher's code
 static inline int tc_result(int rc) { return rc < 0 ? -1 : (rc > 0 ? 1 : 1); }
 
@@ -1413,16 +1583,26 @@ int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStrea
   if (!st->cls || !encode_fn()) return 0;
   const int ar = tensor_arithmetic();
   std::lock_guard<std::mutex> lk(st->mu);
+  if (use_im2col(st, ar)) {
+    if (pack_plain(st->x, ar, 20, x, p->N, p->C, p->H, p->W, s, oom)) return *oom ? 1 : -1;
+    if (pack_filter(st, ar, w, p, 0, st->dgrad_seen, s, oom)) return *oom ? 1 : -1;
+    TapList taps;
+    im2col_taps(taps, p->R, p->S);
+    Im2colGeom im{p->N, p->H, p->W, p->pad_w, p->pad_h, p->S, p->R, p->Q, p->P};
+    OutGeom og{p->P, p->Q, p->P, p->Q, 1, 1, 0, 0};
+    return tc_result(conv_like(st->x, st->wf, st->eC, p->K, p->P, p->Q, y, taps, og, conv_flops(p), s, "DLGpuConvolution2DForward", oom, &im));
+  }
   if (pack_x(st, ar, p, x, s, oom)) return *oom ? 1 : -1;
   if (pack_filter(st, ar, w, p, 0, st->dgrad_seen, s, oom)) return *oom ? 1 : -1;
   TapList taps;
   for (int r = 0; r < st->eR; ++r)
     for (int q = 0; q < st->eS; ++q) {
       if (st->cls == 4) taps.add((r / p->stride_h) * st->frame_w + q / p->stride_w, ((r % p->stride_h) * p->stride_w + q % p->stride_w) * st->cp, r * st->eS + q);
+      else if (st->cls == 2) taps.add((r - p->pad_h + st->x_off_h) * st->frame_w + (q - p->pad_w + st->x_off_w), 0, r * st->eS + q);   // output (p, q) is anchored at frame position (p, q)
       else taps.add(r * st->frame_w + q, 0, r * st->eS + q);
     }
   OutGeom og{p->P, p->Q, p->P, p->Q, 1, 1, 0, 0};
-  return tc_result(conv_like(st->x, st->wf, st->eC, p->K, st, y, taps, og, conv_flops(p), s, "DLGpuConvolution2DForward", oom));
+  return tc_result(conv_like(st->x, st->wf, st->eC, p->K, st->frame_h, st->frame_w, y, taps, og, conv_flops(p), s, "DLGpuConvolution2DForward", oom));
 }
 
 int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaStream_t s, int* oom) {
@@ -1430,6 +1610,17 @@ int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaS
   if (!st->cls || st->cls == 3 || !encode_fn()) return 0;
   const int ar = tensor_arithmetic();
   std::lock_guard<std::mutex> lk(st->mu);
+  if (use_im2col(st, ar)) {
+    // dx = correlation of dy with the flipped filter, R-1-pad zero rows / columns in front
+    if (pack_plain(st->dy, ar, 21, dy, p->N, p->K, p->P, p->Q, s, oom)) return *oom ? 1 : -1;
+    st->dgrad_seen = true;
+    if (pack_filter(st, ar, w, p, 1, false, s, oom)) return *oom ? 1 : -1;
+    TapList taps;
+    im2col_taps(taps, p->R, p->S);
+    Im2colGeom im{p->N, p->P, p->Q, p->S - 1 - p->pad_w, p->R - 1 - p->pad_h, p->S, p->R, p->W, p->H};
+    OutGeom og{p->H, p->W, p->H, p->W, 1, 1, 0, 0};
+    return tc_result(conv_like(st->dy, st->wd, p->K, p->C, p->H, p->W, dx, taps, og, conv_flops(p), s, "DLGpuConvolutionBackwardData", oom, &im));
+  }
   if (pack_dy(st, ar, p, dy, s, oom)) return *oom ? 1 : -1;
   st->dgrad_seen = true;                                           // from now on forward packs both layouts in one launch
   if (pack_filter(st, ar, w, p, 1, false, s, oom)) return *oom ? 1 : -1;     // [C][flipped tap][K]; a no-op when forward made it
@@ -1441,12 +1632,15 @@ int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaS
     if (strided && cudaMemsetAsync(dx, 0, sizeof(float) * (size_t)p->N * p->C * p->H * p->W, s) != cudaSuccess) return -1;
     TapList taps; taps.add(0, 0, 0);
     OutGeom og{p->P, p->Q, p->H, p->W, p->stride_h, p->stride_w, 0, 0};
-    rc = conv_like(st->dy, st->wd, p->K, p->C, st, dx, taps, og, conv_flops(p), s, "DLGpuConvolutionBackwardData", oom);
+    rc = conv_like(st->dy, st->wd, p->K, p->C, st->frame_h, st->frame_w, dx, taps, og, conv_flops(p), s, "DLGpuConvolutionBackwardData", oom);
   } else if (st->cls == 2) {
     TapList taps;
-    for (int r = 0; r < p->R; ++r) for (int q = 0; q < p->S; ++q) taps.add(r * st->frame_w + q, 0, r * p->S + q);
+    // dx(h, w), anchored at frame position (h, w), reads dy(h - lo_h + r, w - lo_w + s) with lo = window - 1 - pad
+    for (int r = 0; r < p->R; ++r)
+      for (int q = 0; q < p->S; ++q)
+        taps.add((r - (p->R - 1 - p->pad_h) + st->dy_off_h) * st->frame_w + (q - (p->S - 1 - p->pad_w) + st->dy_off_w), 0, r * p->S + q);
     OutGeom og{p->H, p->W, p->H, p->W, 1, 1, 0, 0};
-    rc = conv_like(st->dy, st->wd, p->K, p->C, st, dx, taps, og, conv_flops(p), s, "DLGpuConvolutionBackwardData", oom);
+    rc = conv_like(st->dy, st->wd, p->K, p->C, st->frame_h, st->frame_w, dx, taps, og, conv_flops(p), s, "DLGpuConvolutionBackwardData", oom);
   } else {
     // One launch per stride phase (a, b): dx_padded(sh*u + a, sw*v + b) = sum over the taps r = sh*r' + a, s = sw*s' + b of
     // dy(u - r', v - s') * w(r, s); dy sits at frame offset (hh, hw), so the shift is (hh - r') rows and (hw - s') columns.
@@ -1460,7 +1654,7 @@ int tc_conv_dgrad(ConvPlan* p, const float* dy, const float* w, float* dx, cudaS
             taps.add((st->dy_off_h - r / p->stride_h) * st->frame_w + (st->dy_off_w - q / p->stride_w), 0, ntap - 1 - (r * p->S + q));
         if (!taps.n) continue;      // no tap lands on this phase: it stays zero
         OutGeom og{st->frame_h, st->frame_w, p->H, p->W, p->stride_h, p->stride_w, a - p->pad_h, b - p->pad_w};
-        rc = conv_like(st->dy, st->wd, p->K, p->C, st, dx, taps, og, conv_flops(p) * taps.n / ntap, s, "DLGpuConvolutionBackwardData", oom);
+        rc = conv_like(st->dy, st->wd, p->K, p->C, st->frame_h, st->frame_w, dx, taps, og, conv_flops(p) * taps.n / ntap, s, "DLGpuConvolutionBackwardData", oom);
       }
   }
   return tc_result(rc);
@@ -1471,6 +1665,33 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
   if (!st->cls || !encode_fn()) return 0;
   const int ar = tensor_arithmetic(), bk = bk_of(ar);
   std::lock_guard<std::mutex> lk(st->mu);
+  if (use_im2col(st, ar)) {
+    // dW[k][c][r][s] = sum over output pixels of dy[pixel][k] * x[pixel + (r, s) - pad][c]: the reduction runs over the
+    // real output pixels; x comes through an im2col map (BK pixels x one 128-byte channel group per copy), dy as it lies
+    if (pack_plain(st->x, ar, 20, x, p->N, p->C, p->H, p->W, s, oom)) return *oom ? 1 : -1;
+    if (pack_plain(st->dy, ar, 21, dy, p->N, p->K, p->P, p->Q, s, oom)) return *oom ? 1 : -1;
+    GemmParams g;
+    memset(&g, 0, sizeof(g));
+    g.err = error_word(); g.out = dw;
+    const int bn = pick_bn(p->K);
+    g.mode = kModeWgrad; g.a_mn = 1; g.b_mn = 1; g.epi = kEpiWgrad;
+    g.M = p->C; g.N = p->K; g.ntaps = p->R * p->S;
+    g.slot = p->C > 64 ? BM : 64;
+    g.taps_per_tile = BM / g.slot;
+    int rc = make_map_im2col(&g.a_hi, ar, st->x.hi, p->N, p->H, p->W, st->x.pitch, p->pad_w, p->pad_h, p->S, p->R, bk, gw_of(ar));
+    if (!rc) rc = make_map_im2col(&g.a_lo, ar, st->x.lo, p->N, p->H, p->W, st->x.pitch, p->pad_w, p->pad_h, p->S, p->R, bk, gw_of(ar));
+    if (!rc) rc = make_map_mn(&g.b_hi, ar, st->dy.hi, st->dy.rows, st->dy.pitch, bn);
+    if (!rc) rc = make_map_mn(&g.b_lo, ar, st->dy.lo, st->dy.rows, st->dy.pitch, bn);
+    if (rc) return -1;
+    g.a_scale = st->x.scale(); g.b_scale = st->dy.scale();
+    g.m_tiles = (p->C + g.slot - 1) / g.slot;
+    g.tap_tiles = (g.ntaps + g.taps_per_tile - 1) / g.taps_per_tile;
+    g.n_tiles = (p->K + bn - 1) / bn;
+    g.im2col = 1; g.im_w = p->Q; g.im_h = p->P; g.im_lo_w = -p->pad_w; g.im_lo_h = -p->pad_h;
+    for (int r = 0; r < p->R; ++r) for (int q = 0; q < p->S; ++q) g.tap_off[r * p->S + q] = (r << 16) | q;
+    g.k_total = (int)((st->dy.rows + bk - 1) / bk);
+    return tc_result(launch_gemm_bn(bn, ar, g, s, conv_flops(p), "DLGpuConvolutionBackwardFilter", oom));
+  }
   if (pack_x(st, ar, p, x, s, oom)) return *oom ? 1 : -1;
   if (pack_dy(st, ar, p, dy, s, oom)) return *oom ? 1 : -1;
   GemmParams g;
@@ -1525,7 +1746,8 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
         g.tap_off[t] = (r / p->stride_h - st->dy_off_h) * st->frame_w + (q / p->stride_w - st->dy_off_w);
         g.tap_col[t] = (short)(((r % p->stride_h) * p->stride_w + q % p->stride_w) * st->cp);
       } else {
-        g.tap_off[t] = (r - st->dy_off_h) * st->frame_w + (q - st->dy_off_w);
+        const int ph = st->cls == 2 ? p->pad_h : st->x_off_h, pw = st->cls == 2 ? p->pad_w : st->x_off_w;    // classes A / C: no padding, offsets 0
+        g.tap_off[t] = (r - ph + st->x_off_h - st->dy_off_h) * st->frame_w + (q - pw + st->x_off_w - st->dy_off_w);
       }
     }
   g.k_total = kit;

@@ -169,9 +169,9 @@ __global__ void __launch_bounds__(kBlock) bcast_channel_kernel(const float* __re
 
 // ---- reductions --------------------------------------------------------------------
 // Column sums of a row-major [rows x cols] matrix, out[c] = sum_r in[r, c].
-// Block = 32 columns x 8 row lanes; grid.x tiles the columns, grid.y splits the rows; partial
-// sums from the row splits are combined with one atomicAdd per column (out pre-zeroed when
-// gridDim.y > 1).
+// Block = 32 columns x 8 row lanes; grid.x tiles the columns, grid.y splits the rows; with several row
+// splits each writes its partial sums to out[split * cols + c] (a scratch array) and colsum_final_kernel
+// adds the splits in order, so the result does not depend on scheduling.
 __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ in, float* __restrict__ out, int64_t rows, int64_t cols, int64_t rows_per_split) {
   __shared__ float sm[8][33];
   int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -185,8 +185,15 @@ __global__ void __launch_bounds__(256) colsum_kernel(const float* __restrict__ i
     float t = 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) t += sm[j][tx];
-    if (gridDim.y > 1) atomicAdd(out + c, t); else out[c] = t;
+    out[(int64_t)blockIdx.y * cols + c] = t;
   }
+}
+__global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ part, float* __restrict__ out, int64_t cols, int splits) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float t = 0.f;
+  for (int z = 0; z < splits; ++z) t += part[(int64_t)z * cols + c];
+  out[c] = t;
 }
 // Sum of n contiguous floats into out[0]; two launches: per-block partials then one block.
 __global__ void __launch_bounds__(kBlock) partial_sum_kernel(const float* __restrict__ in, float* __restrict__ part, int64_t n) {
@@ -408,7 +415,11 @@ __global__ void __launch_bounds__(kBlock) adam_table_kernel(float* const* __rest
 using namespace tf;
 
 // Data-parallel hook implemented in dp_nccl.cu: returns 1 when it took ownership of the update.
-namespace tf { int dp_sgd_update(float* w, const float* g, int64_t n, float lr, cudaStream_t s); }
+namespace tf {
+int dp_sgd_update(float* w, const float* g, int64_t n, float lr, cudaStream_t s);
+int dp_adam_moments(float* m, float* v, const float* g, int64_t n, float b1, float b2, cudaStream_t s);
+int dp_adam_step(float* w, const float* m, const float* v, float c1, float c2, float eps, float lr, cudaStream_t s);
+}
 
 static inline const float* F(const DLArrayHandle a) { return (const float*)a->data; }
 static inline float* FM(DLArrayHandle a) { return out_f32(a); }
@@ -468,10 +479,17 @@ static int column_sums(const float* in, float* out, int64_t rows, int64_t cols, 
   int64_t rps = (rows + splits - 1) / splits;
   splits = (int)((rows + rps - 1) / rps);
   note_compute_stream(s);
-  int launches = 1;
-  if (splits > 1) { cudaMemsetAsync(out, 0, sizeof(float) * cols, s); }
-  colsum_kernel<<<dim3(gx, splits), 256, 0, s>>>(in, out, rows, cols, rps);
-  if (after_launch(s, what, launches) != 0) return -1;
+  if (splits > 1) {
+    float* part = (float*)persistent_scratch(2, sizeof(float) * (size_t)splits * (size_t)cols);
+    if (part) {
+      colsum_kernel<<<dim3(gx, splits), 256, 0, s>>>(in, part, rows, cols, rps);
+      colsum_final_kernel<<<(unsigned)((cols + 255) / 256), 256, 0, s>>>(part, out, cols, splits);
+      return after_launch(s, what, 2) != 0 ? -1 : 0;
+    }
+    rps = rows;                                  // no scratch: one split
+  }
+  colsum_kernel<<<dim3(gx, 1), 256, 0, s>>>(in, out, rows, cols, rps);
+  if (after_launch(s, what, 1) != 0) return -1;
   return 0;
 }
 
@@ -601,17 +619,19 @@ static __device__ __align__(256) float g_static_partials[kStaticPartials];
 
 // In host code `g_static_partials` is only a handle for the symbol, not a device address; the address a
 // kernel can use comes from cudaGetSymbolAddress, once per device, with that device current.
+// The per-device cache needs no lock: two threads that race on the first call both look the address up and store the
+// same value (the write is idempotent), and the slots are atomics so neither can see a torn pointer.
 static float* static_partials_ptr() {
-  static float* ptr[64] = {nullptr};
+  static std::atomic<float*> ptr[64];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); set_error("DLGpuReduceSumAllStatic: no current device"); return nullptr; }
-  if (!ptr[dev]) {
-    float* p = nullptr;
+  float* p = ptr[dev].load(std::memory_order_acquire);
+  if (!p) {
     cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_partials);
     if (e != cudaSuccess) { cudaGetLastError(); set_error("DLGpuReduceSumAllStatic: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); return nullptr; }
-    ptr[dev] = p;
+    ptr[dev].store(p, std::memory_order_release);
   }
-  return ptr[dev];
+  return p;
 }
 
 extern "C" {
@@ -906,12 +926,20 @@ int DLGpuAdam_mv(DLArrayHandle m, DLArrayHandle v, const DLArrayHandle g, float 
   cudaStream_t s = stream_of(cudaStream);
   int64_t n = numel(g);
   note_compute_stream(s);
+  // data-parallel mode: the moments are computed from the gradient averaged over the ranks, after its all-reduce
+  int took = dp_adam_moments(FM(m), FM(v), F(g), n, b1, b2, s);
+  if (took < 0) return -1;
+  if (took) return 0;
   adam_moments_kernel<<<grid_for(n, kBlock), kBlock, 0, s>>>(FM(m), FM(v), F(g), n, b1, b2);
   TF_AFTER(s, "DLGpuAdam_mv");
   return 0;
 }
 int DLGpuAdam(DLArrayHandle output, const DLArrayHandle m, const DLArrayHandle v, float b1t, float b2t, float e, float learning_rate, void** cudaStream) {
   TF_SAME(output, m, "DLGpuAdam"); TF_SAME(output, v, "DLGpuAdam");
+  // data-parallel mode: the step joins the pending record of (m, v) and runs behind the all-reduce
+  int took = dp_adam_step(FM(output), F(m), F(v), 1.f - b1t, 1.f - b2t, e, learning_rate, stream_of(cudaStream));
+  if (took < 0) return -1;
+  if (took) return 0;
   return run_map3(F(output), F(m), F(v), FM(output), numel(output), stream_of(cudaStream), "DLGpuAdam", FAdamStep{1.f - b1t, 1.f - b2t, e, learning_rate});
 }
 

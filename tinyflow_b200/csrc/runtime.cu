@@ -223,7 +223,7 @@ static inline size_t data_bytes(const DLArray* a) { return (size_t)numel(a) * 4;
 
 }  // namespace tf
 
-namespace tf { int tensor_path_error(); }
+namespace tf { int tensor_path_error(); int dp_flush_if_pending(); }
 using namespace tf;
 
 extern "C" {
@@ -294,6 +294,9 @@ int DLArrayCopyFromTo(DLArrayHandle from, DLArrayHandle to, DLStreamHandle strea
   if (bytes == 0) return 0;
   if (tg) note_write(to->data);
   if (stream == nullptr) {
+    // A blocking copy between host and device is how a training loop uploads its next batch and reads its loss: in
+    // data-parallel mode that is the step boundary, so pending gradient buckets are sent and waited for (on the device).
+    if (fg != tg && dp_flush_if_pending() != 0) return -1;
     // Blocking copy on the legacy default stream: ordered after everything already
     // enqueued on the (blocking) compute streams, and complete on return.
     TF_CUDA(cudaMemcpy(to->data, from->data, bytes, kind));
