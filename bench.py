@@ -2,7 +2,8 @@
 """Benchmark: train images/s for one forward + backward + SGD step of ResNet-50 (batch 64 per GPU,
 3x224x224 synthetic inputs, 1000 classes) through the mirrored executor and the C-ABI library.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload resnet50|vgg16|inceptionv3|lenet5|mlp]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload resnet50|vgg16|inceptionv3|densenet121|inceptionv4|lenet5|mlp]
+    python bench.py --layer N,C,H,W,K,R,S,PADDING,STRIDE [--steps K]      one convolution layer on its own (profiling aid)
 
 With N > 1 launch under torchrun (one rank per GPU); rank 0 prints one JSON line.
 `--impl reference` times the CPU arm instead: the same graph evaluated by the numpy restatement of
@@ -27,6 +28,8 @@ WORKLOADS = {
     "resnet50": dict(batch=64, image=224, classes=1000, lr=0.01, dist="normal"),
     "vgg16": dict(batch=64, image=224, classes=1000, lr=0.01, dist="normal"),
     "inceptionv3": dict(batch=32, image=299, classes=1000, lr=0.01, dist="normal"),
+    "densenet121": dict(batch=32, image=224, classes=1000, lr=0.01, dist="normal"),
+    "inceptionv4": dict(batch=32, image=299, classes=1000, lr=0.01, dist="normal"),
     "lenet5": dict(batch=256, lr=0.05, dist="uniform"),
     "mlp": dict(batch=1000, lr=0.1, dist="uniform"),
 }
@@ -37,7 +40,7 @@ def build_model(name, batch=None):
     cfg = dict(WORKLOADS[name])
     if batch is not None:
         cfg["batch"] = batch
-    if name in ("resnet50", "vgg16", "inceptionv3"):
+    if name in ("resnet50", "vgg16", "inceptionv3", "densenet121", "inceptionv4"):
         return models.BUILDERS[name](batch=cfg["batch"], classes=cfg["classes"], image=cfg["image"]), cfg
     return models.BUILDERS[name](batch=cfg["batch"]), cfg
 
@@ -167,7 +170,7 @@ def run_reference_arm(args):
     import numpy as np  # noqa: F401  (loads the BLAS whose thread count is reported)
     workload = args.workload
     cfg = WORKLOADS[workload]
-    sample = {"resnet50": 4, "vgg16": 2, "inceptionv3": 2}.get(workload, cfg["batch"])
+    sample = {"resnet50": 4, "vgg16": 2, "inceptionv3": 2, "densenet121": 2, "inceptionv4": 2}.get(workload, cfg["batch"])
     blas_threads, cores = cpu_threads()
     for _ in range(args.warmup if workload in ("mlp", "lenet5") else min(args.warmup, 1)):
         cpu_step_time(workload, sample)
@@ -193,6 +196,90 @@ def run_reference_arm(args):
 
 
 # ---------------------------------------------------------------------------------------------------
+# one layer on its own (profiling aid)
+# ---------------------------------------------------------------------------------------------------
+def run_layer(args):
+    import ctypes
+    import numpy as np
+    from tinyflow_b200 import gpu_op, ndarray
+    from tinyflow_b200._base import _LIB
+    f = args.layer.split(",")
+    N, C, H, W, K, R, S = (int(v) for v in f[:7])
+    padding, stride = f[7], int(f[8])
+    ctx = ndarray.gpu(0)
+    stream = gpu_op.create_cudaStream()
+    cudnn = gpu_op.create_cudnnHandle(stream)
+    rng = np.random.RandomState(0)
+    x = ndarray.array(rng.randn(N, C, H, W).astype(np.float32), ctx)
+    w = ndarray.array((rng.randn(K, C, R, S) * np.sqrt(2.0 / (C * R * S))).astype(np.float32), ctx)
+    out_shape, cell = gpu_op.convolution_2d_forward_get_out_shape((N, C, H, W), (K, C, R, S), "NCHW", padding, stride, stride)
+    y, dy = ndarray.empty(out_shape, ctx), ndarray.array(rng.randn(*out_shape).astype(np.float32), ctx)
+    dx, dw = ndarray.empty((N, C, H, W), ctx), ndarray.empty((K, C, R, S), ctx)
+
+    def passes():
+        gpu_op.convolution_2d_forward(x, w, y, cell, cudnn, stream)
+        if C >= 16:
+            gpu_op.convolution_backward_data(x, dy, w, dx, cell, cudnn, stream)
+        gpu_op.convolution_backward_filter(x, dy, w, dw, cell, cudnn, stream)
+
+    for _ in range(max(args.warmup, 1)):
+        passes()
+    gpu_op.device_synchronize()
+    _LIB.TfKernelTimingEnable(2)
+    for _ in range(args.steps):
+        passes()
+    gpu_op.device_synchronize()
+    report = ctypes.create_string_buffer(1 << 16)
+    _LIB.TfKernelTimingReport(report, len(report))
+    _LIB.TfKernelTimingEnable(0)
+    rows = json.loads(report.value.decode() or "[]")
+    for r in rows:
+        t = r["ms"] / max(r["launches"], 1)
+        r.update(us_per_launch=1000.0 * t, tflops=(r["flops"] / r["launches"] / t / 1e9 if t and r["flops"] else 0.0),
+                 gbs=(r["bytes"] / r["launches"] / t / 1e6 if t and r["bytes"] else 0.0))
+    print(json.dumps({"layer": args.layer, "arithmetic": gpu_op.tensor_arithmetic(), "steps": args.steps, "kernels": rows}))
+    return 0
+
+
+def run_matmul(args):
+    import ctypes
+    import numpy as np
+    from tinyflow_b200 import gpu_op, ndarray
+    from tinyflow_b200._base import _LIB
+    M, K, N = (int(v) for v in args.matmul.split(","))
+    ctx = ndarray.gpu(0)
+    stream = gpu_op.create_cudaStream()
+    cublas = gpu_op.create_cublasHandle(stream)
+    rng = np.random.RandomState(0)
+    A, B, C = ndarray.array(rng.randn(M, K).astype(np.float32), ctx), ndarray.array(rng.randn(K, N).astype(np.float32), ctx), ndarray.empty((M, N), ctx)
+    out = {"matmul": [M, K, N], "steps": args.steps, "modes": {}}
+    for name, path, arith in (("3xfp16", 2, "3xfp16"), ("3xtf32", 2, "3xtf32"), ("fp32 CUDA cores", 1, "3xfp16")):
+        gpu_op.set_contraction_path(path)
+        gpu_op.set_tensor_arithmetic(arith)
+        reps = args.steps if path == 2 else max(1, args.steps // 4)
+        try:
+            for _ in range(3):
+                gpu_op.matrix_multiply(A, False, B, False, C, cublas, stream)
+            gpu_op.device_synchronize()
+            _LIB.TfKernelTimingEnable(1)
+            for _ in range(reps):
+                gpu_op.matrix_multiply(A, False, B, False, C, cublas, stream)
+            gpu_op.device_synchronize()
+            report = ctypes.create_string_buffer(1 << 14)
+            _LIB.TfKernelTimingReport(report, len(report))
+            _LIB.TfKernelTimingEnable(0)
+        finally:
+            gpu_op.set_contraction_path(0)
+            gpu_op.set_tensor_arithmetic("3xfp16")
+        rows = [r for r in json.loads(report.value.decode() or "[]") if r["flops"] > 0]
+        ms = sum(r["ms"] for r in rows) / max(reps, 1)
+        alg = 2.0 * M * N * K / (ms / 1000.0) / 1e12 if ms else 0.0
+        out["modes"][name] = {"ms": ms, "algorithmic_tflops": alg, "issued_tflops": 3 * alg if path == 2 else alg}
+    print(json.dumps(out))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------
 def main():
@@ -206,7 +293,17 @@ def main():
     ap.add_argument("--memory-plan", default="none", choices=["none", "vdnn-conv", "vdnn-all"],
                     help="replay a swap/release plan (reference message format) during every step; not the headline configuration")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch override (profiling on a small case; not the headline configuration)")
+    ap.add_argument("--layer", default=None, metavar="N,C,H,W,K,R,S,PADDING,STRIDE",
+                    help="time the three passes of ONE convolution layer on its own (e.g. 64,256,14,14,256,3,3,SAME,1) and print a "
+                         "per-kernel JSON table: the small case profiler captures run on; not the headline configuration")
+    ap.add_argument("--matmul", default=None, metavar="M,K,N",
+                    help="time one M x K by K x N product in both arithmetic modes of the tensor path (3xFP16, 3xTF32) and on the "
+                         "exact-fp32 CUDA-core kernel; prints a JSON line (measures the issued tensor rate each mode reaches)")
     args = ap.parse_args()
+    if args.layer:
+        return run_layer(args)
+    if args.matmul:
+        return run_matmul(args)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
@@ -239,7 +336,7 @@ def main():
         check_call(_LIB.TfDpInit(rank, world, id_path.encode()))
 
     model, cfg = build_model(args.workload, batch=args.batch)
-    model.set_dropout({"resnet50": 0.5, "vgg16": 0.5, "inceptionv3": 0.8}.get(args.workload, 0.0))
+    model.set_dropout({"resnet50": 0.5, "vgg16": 0.5, "inceptionv3": 0.8, "densenet121": 0.2, "inceptionv4": 0.8}.get(args.workload, 0.0))
     import queue
     control = queue.Queue()
     ex = ad.Executor(model.loss, model.y, cfg["lr"], control, None, None, optimizer="sgd")
@@ -303,8 +400,23 @@ def main():
         if w == 1 and args.memory_plan != "none":          # shapes are known after the first step
             from tinyflow_b200 import memory_plan
             plan = memory_plan.vdnn_plan(ex, policy=args.memory_plan.split("-")[1])
+            out_bytes = sum(4 * int(np.prod(ex.node_to_shape_map[ex.topo_order[t]])) for t, _w, _s, to_gpu in plan[0] if not to_gpu)
+            # the swap traffic's own roofline: bytes each way over the measured pinned-memory link rate (the two directions
+            # run on separate copy engines, so the bound is one direction's bytes)
+            probe_h, probe_d = ndarray.empty((64 * 1024 * 1024,), ndarray.cpu(0)), ndarray.empty((64 * 1024 * 1024,), ctx)
+            probe_h.copyto(probe_d, copy_stream)
+            t0 = time.perf_counter()
+            for _ in range(4):
+                probe_h.copyto(probe_d, copy_stream)
+            h2d = 4 * 256 * 1024 * 1024 / (time.perf_counter() - t0) / 1e9
+            t0 = time.perf_counter()
+            for _ in range(4):
+                probe_d.copyto(probe_h, copy_stream)
+            d2h = 4 * 256 * 1024 * 1024 / (time.perf_counter() - t0) / 1e9
+            del probe_h, probe_d
             plan_info = {"policy": args.memory_plan, "swapped_tensors": len(plan[0]) // 2, "released_tensors": len(plan[1]),
-                         "bytes_away_at_peak": int(memory_plan.check_plan(ex, plan))}
+                         "bytes_away_at_peak": int(memory_plan.check_plan(ex, plan)), "bytes_each_way_per_step": int(out_bytes),
+                         "host_link_gbs": {"h2d": h2d, "d2h": d2h}, "host_link_bound_ms": out_bytes / 1e6 / min(h2d, d2h)}
             control.put(plan)
         loss, feed = step_resident(feed)
     if args.memory_plan != "none" and plan_info is None:
@@ -430,7 +542,7 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        sample = {"resnet50": 4, "vgg16": 2, "inceptionv3": 2}.get(args.workload, batch)
+        sample = {"resnet50": 4, "vgg16": 2, "inceptionv3": 2, "densenet121": 2, "inceptionv4": 2}.get(args.workload, batch)
         t = cpu_step_time(args.workload, sample)
         threads, cores = cpu_threads()
         cpu_baseline = {"value": sample / t, "unit": "images/s", "cores": threads, "kind": "port",

@@ -26,7 +26,8 @@ def _mirror_census(name, batch):
     return [[n.name, list(ex.node_to_shape_map[n])] for n in ex.topo_order]
 
 
-@pytest.mark.parametrize("name,batch", [("resnet50", 64), ("vgg16", 64), ("inceptionv3", 32)])
+@pytest.mark.parametrize("name,batch", [("resnet50", 64), ("vgg16", 64), ("inceptionv3", 32), ("densenet121", 32),
+                                        ("inceptionv4", 32)])
 def test_node_order_matches_reference(lib_path, name, batch):
     from tinyflow_b200 import models
     if not hasattr(models, name):

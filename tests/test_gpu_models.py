@@ -256,6 +256,30 @@ def test_inceptionv3_reduced_node_by_node(lib_path):
     assert np.isfinite(loss.asnumpy()).all()
 
 
+def test_densenet121_reduced_node_by_node(lib_path):
+    """DenseNet-121 graph (120 convolutions, 58 channel concats, 4-D dropout behind every convolution) at batch 4 on 64x64
+    images: a graph beyond the five benchmark configurations (DenseNet_test_leo.py)."""
+    from tinyflow_b200 import models
+    model = models.densenet121(batch=4, image=64, classes=100)
+    feed_np = _feed(model)
+    ex, loss, nxt = run_step(model, feed_np, 0.01, dropout=0.2)
+    worst = check_node_by_node(ex, feed_np)
+    print("worst node", worst)
+    assert np.isfinite(loss.asnumpy()).all()
+
+
+def test_inceptionv4_reduced_node_by_node(lib_path):
+    """Inception-v4 graph (149 convolutions, 7x1 / 1x7 and 3x1 / 1x3 filters, strided VALID reductions) at batch 4 on
+    107x107 images, which leaves a 2x2 map in front of the global pool (Inceptionv4_test_leo.py)."""
+    from tinyflow_b200 import models
+    model = models.inceptionv4(batch=4, image=107, classes=100)
+    feed_np = _feed(model)
+    ex, loss, nxt = run_step(model, feed_np, 0.01, dropout=0.8)
+    worst = check_node_by_node(ex, feed_np)
+    print("worst node", worst)
+    assert np.isfinite(loss.asnumpy()).all()
+
+
 def test_two_steps_reuse_pool_and_stay_finite(lib_path):
     from tinyflow_b200 import models, ndarray
     from tinyflow_b200._base import _LIB

@@ -608,6 +608,120 @@ def test_host_link_probe_runs(env, capfd):
     assert len(nums) >= 4 and all(v > 0.1 for v in nums[:4]), out
 
 
+# ---- 1-D and 3-D convolution (forward) and pooling --------------------------------------------------------------------
+@pytest.mark.parametrize("case", [(4, 8, 50, 16, 5, "SAME", 1), (3, 64, 400, 96, 7, "VALID", 2), (64, 128, 512, 128, 3, "SAME", 1)])
+def test_conv1d_forward(env, case):
+    """A 1-D convolution is the 2-D one on (N, C, 1, W) (the reference hands cuDNN exactly that, src/gpu_op.cu:1535-1606);
+    the last case is large enough for the tensor cores."""
+    N, C, W, K, S, padding, v = case
+    x, w = f32(N, C, W), f32(K, C, S, scale=0.2)
+    out_shape, cell = env.gpu_op.convolution_1d_forward_get_out_shape(x.shape, w.shape, "NCHW", padding, v)
+    g = env.ops.conv_geometry((N, C, 1, W), (K, C, 1, S), padding, 1, v)
+    assert out_shape == (N, K, g["Q"])
+    y = env.empty(out_shape)
+    assert env.gpu_op.convolution_1d_forward(env.dev(x), env.dev(w), y, cell, env.cudnn) == 0
+    x4, w4 = x.astype(np.float64).reshape(N, C, 1, W), w.astype(np.float64).reshape(K, C, 1, S)
+    close_dot(y.asnumpy().reshape(N, K, 1, g["Q"]), env.ops.conv2d_fwd(x4, w4, g), env.ops.conv2d_fwd(np.abs(x4), np.abs(w4), g), what="conv1d %s" % (case,))
+
+
+@pytest.mark.parametrize("mode", ["max", "mean"])
+def test_pool1d_forward_backward(env, mode):
+    N, C, W, pad, v, k = 3, 5, 37, 1, 2, 3
+    x = f32(N, C, W)
+    out_shape, cell = env.gpu_op.pooling_1d_forward_get_out_shape(x.shape, "NCHW", mode, pad, v, k)
+    g = env.ops.pool_geometry((N, C, 1, W), 0, pad, 1, v, 1, k)
+    assert out_shape == (N, C, g["Q"])
+    dy = f32(*out_shape)
+    xd, y, dx = env.dev(x), env.empty(out_shape), env.empty(x.shape)
+    env.gpu_op.pooling_1d_forward(xd, y, cell, env.cudnn)
+    env.gpu_op.pooling_1d_backward(xd, y, env.dev(dy), dx, cell, env.cudnn)
+    x4, dy4 = x.astype(np.float64).reshape(N, C, 1, W), dy.astype(np.float64).reshape(N, C, 1, -1)
+    if mode == "max":
+        np.testing.assert_array_equal(y.asnumpy().reshape(N, C, 1, -1), env.ops.maxpool_fwd(x.reshape(N, C, 1, W), g)[0])
+        close(dx.asnumpy().reshape(N, C, 1, W), env.ops.maxpool_bwd(x4, dy4, g), what="maxpool1d bwd")
+    else:
+        close(y.asnumpy().reshape(N, C, 1, -1), env.ops.avgpool_fwd(x4, g), what="avgpool1d fwd")
+        close(dx.asnumpy().reshape(N, C, 1, W), env.ops.avgpool_bwd(dy4, g), what="avgpool1d bwd")
+
+
+@pytest.mark.parametrize("case", [(2, 3, 6, 7, 8, 4, 3, 3, 3, "SAME", (1, 1, 1)), (2, 8, 9, 10, 11, 12, 3, 2, 3, "VALID", (2, 1, 2)), (1, 16, 8, 12, 12, 24, 3, 3, 3, "SAME", (1, 2, 2))])
+def test_conv3d_forward(env, case):
+    N, C, D, H, W, K, T, R, S, padding, strides = case
+    x, w = f32(N, C, D, H, W), f32(K, C, T, R, S, scale=0.2)
+    pads = (T // 2, R // 2, S // 2) if padding == "SAME" else (0, 0, 0)
+    out_shape, cell = env.gpu_op.convolution_3d_forward_get_out_shape(x.shape, w.shape, "NCHW", padding, *strides)
+    x64, w64 = x.astype(np.float64), w.astype(np.float64)
+    want = env.ops.conv3d_fwd(x64, w64, pads, strides)
+    assert out_shape == want.shape
+    y = env.empty(out_shape)
+    assert env.gpu_op.convolution_3d_forward(env.dev(x), env.dev(w), y, cell, env.cudnn) == 0
+    close_dot(y.asnumpy(), want, env.ops.conv3d_fwd(np.abs(x64), np.abs(w64), pads, strides), what="conv3d %s" % (case,))
+
+
+@pytest.mark.parametrize("mode", ["max", "mean"])
+@pytest.mark.parametrize("geom", [((0, 0, 0), (2, 2, 2), (2, 2, 2)), ((1, 1, 1), (2, 2, 2), (3, 3, 3)), ((0, 1, 0), (1, 2, 1), (2, 3, 2))])
+def test_pool3d_forward_backward(env, mode, geom):
+    pads, strides, win = geom
+    x = f32(2, 3, 6, 7, 8)
+    if mode == "max":
+        x[0, 0, :3, :3, :3] = 0.0            # a block of ties: the first maximum of a window takes the gradient
+    out_shape, cell = env.gpu_op.pooling_3d_forward_get_out_shape(x.shape, "NCHW", mode, *pads, *strides, *win)
+    want_y = env.ops.pool3d_fwd(x.astype(np.float64), mode, pads, strides, win)
+    assert out_shape == want_y.shape
+    dy = f32(*out_shape)
+    xd, y, dx = env.dev(x), env.empty(out_shape), env.empty(x.shape)
+    env.gpu_op.pooling_3d_forward(xd, y, cell, env.cudnn)
+    env.gpu_op.pooling_3d_backward(xd, y, env.dev(dy), dx, cell, env.cudnn)
+    if mode == "max":
+        np.testing.assert_array_equal(y.asnumpy(), want_y.astype(np.float32))        # a selection: exact
+    else:
+        close(y.asnumpy(), want_y, what="avgpool3d fwd")
+    close(dx.asnumpy(), env.ops.pool3d_bwd(x.astype(np.float64), dy.astype(np.float64), mode, pads, strides, win), what="pool3d bwd %s" % mode)
+
+
+# ---- cross-operator fusion: the ReLU in front of a convolution packs the convolution's operand ---------------------------
+@pytest.mark.parametrize("case", [(8, 64, 28, 28, 96, 3, 3, "SAME"), (8, 128, 14, 14, 256, 1, 1, "VALID"), (4, 40, 19, 17, 64, 5, 5, "SAME")])
+@pytest.mark.parametrize("arith", ["3xfp16", "3xtf32"])
+def test_relu_packs_the_next_convolutions_operand(env, case, arith):
+    """BN -> ReLU -> convolution as three separate calls, twice on the same arrays (as an executor does step after step).
+    The second time the ReLU writes y and the convolution's packed operand in one kernel; y must be the plain ReLU's,
+    bit for bit, and the convolution's result must not change."""
+    N, C, H, W, K, R, S, padding = case
+    x, w = f32(N, C, H, W, scale=2.0), f32(K, C, R, S, scale=0.2)
+    mean_p, var_p, bn_cell = env.gpu_op.bn_get_cudnnlist(x.shape, "NCHW", "pre_activation")
+    act_cell = env.gpu_op.activation_get_cudnnlist(x.shape, "NCHW", "relu")
+    g = env.ops.conv_geometry(x.shape, w.shape, padding, 1, 1)
+    out_shape, cell = env.gpu_op.convolution_2d_forward_get_out_shape(x.shape, w.shape, "NCHW", padding, 1, 1)
+    xd, wd = env.dev(x), env.dev(w)
+    bn_out, y, conv_out = env.empty(x.shape), env.empty(x.shape), env.empty(out_shape)
+    env.gpu_op.set_contraction_path(2)
+    env.gpu_op.set_tensor_arithmetic(arith)
+    try:
+        results = []
+        for step in range(3):
+            if step == 2:
+                xd._sync_copyfrom(x * np.float32(1.7) - np.float32(0.3))       # new data, same arrays: nothing stale may be reused
+            before = env.gpu_op.fused_relu_pack_count()
+            assert env.gpu_op.bn_forward(xd, bn_out, "pre_activation", 0, mean_p, var_p, bn_cell, env.cudnn, env.stream) == 0
+            env.gpu_op.activation_forward(bn_out, y, "relu", act_cell, env.cudnn, env.stream)
+            assert env.gpu_op.convolution_2d_forward(y, wd, conv_out, cell, env.cudnn, env.stream) == 0
+            assert env.gpu_op.last_contraction_path() == 2
+            results.append((env.gpu_op.fused_relu_pack_count() - before, bn_out.asnumpy(), y.asnumpy(), conv_out.asnumpy()))
+    finally:
+        env.gpu_op.set_contraction_path(0)
+        env.gpu_op.set_tensor_arithmetic("3xfp16")
+    assert results[0][0] == 0 and results[1][0] == 1 and results[2][0] == 1      # learned at the first pass, fused afterwards
+    for fused, b, yy, cc in results:
+        np.testing.assert_array_equal(yy, np.maximum(b, 0))
+        y64, w64 = yy.astype(np.float64), w.astype(np.float64)
+        close_dot(cc, env.ops.conv2d_fwd(y64, w64, g), env.ops.conv2d_fwd(np.abs(y64), np.abs(w64), g), what="conv behind the fused ReLU %s" % (case,))
+    if arith == "3xtf32":
+        # tf32 packs carry no scale, so the fused pass is the same arithmetic bit for bit; the fp16 pack's power-of-two
+        # scale comes from max|BN output| (an upper bound known before the pass) instead of max|y|, which may round
+        # the low halves differently
+        np.testing.assert_array_equal(results[0][3], results[1][3])
+
+
 # ---- failure reporting of the tensor path -----------------------------------------------------------------------------
 def test_bounded_barrier_wait_reports_refuses_and_recovers(env):
     """Every barrier wait of the tensor-core kernels has a cycle limit.  The probe kernel waits, with a 20,000-cycle

@@ -229,3 +229,22 @@ def test_sampled_convolution_oracle_equals_the_dense_one(case):
     np.testing.assert_allclose(ops.conv2d_fwd_at(x, w, g, n, k, p, q), ops.conv2d_fwd(x, w, g)[n, k, p, q], rtol=1e-12, atol=1e-12)
     np.testing.assert_allclose(ops.conv2d_dgrad_at(dy, w, g, n, c, h, wi), ops.conv2d_dgrad(dy, w, g)[n, c, h, wi], rtol=1e-12, atol=1e-12)
     np.testing.assert_allclose(ops.conv2d_wgrad_at(x, dy, g, k, c, r, s), ops.conv2d_wgrad(x, dy, g)[k, c, r, s], rtol=1e-12, atol=1e-12)
+
+
+def test_3d_convolution_and_pooling_oracle_against_torch():
+    """The 3-D restatements (cuDNN Nd descriptors in the reference, src/gpu_op.cu:2340-2530, 3029-3203) against torch-CPU
+    float64, including the gradient of both pooling modes."""
+    rng = np.random.RandomState(3)
+    x, w = rng.randn(2, 3, 6, 7, 8), rng.randn(4, 3, 3, 3, 3)
+    for pads, strides in [((1, 1, 1), (1, 1, 1)), ((0, 0, 0), (2, 1, 2)), ((1, 1, 1), (2, 2, 2))]:
+        want = Fn.conv3d(torch.tensor(x), torch.tensor(w), stride=strides, padding=pads).numpy()
+        np.testing.assert_allclose(ops.conv3d_fwd(x, w, pads, strides), want, rtol=1e-12, atol=1e-12)
+    for mode in ("max", "mean"):
+        for pads, strides, win in [((0, 0, 0), (2, 2, 2), (2, 2, 2)), ((1, 1, 1), (2, 2, 2), (3, 3, 3)), ((0, 1, 0), (1, 2, 1), (2, 3, 2))]:
+            xt = torch.tensor(x, requires_grad=True)
+            yt = Fn.max_pool3d(xt, win, strides, pads) if mode == "max" else Fn.avg_pool3d(xt, win, strides, pads, count_include_pad=True)
+            y = ops.pool3d_fwd(x, mode, pads, strides, win)
+            np.testing.assert_allclose(y, yt.detach().numpy(), rtol=1e-12, atol=1e-12)
+            dy = rng.randn(*y.shape)
+            yt.backward(torch.tensor(dy))
+            np.testing.assert_allclose(ops.pool3d_bwd(x, dy, mode, pads, strides, win), xt.grad.numpy(), rtol=1e-12, atol=1e-12)

@@ -83,6 +83,13 @@ __device__ __forceinline__ void amax_commit(const AmaxOut& am, uint32_t m) {
 }
 #endif
 
+// ---- producers that feed the tensor path ------------------------------------------------------------
+// y = relu(x) fused with the packing of y for the convolution expected to read it (see gemm_tcgen05.cu); 1 = done,
+// 0 = not applicable (run the plain kernel), -1 = error.
+int tc_fused_relu_pack(const void* node, const float* x, float* y, int64_t n, cudaStream_t s);
+void tc_note_relu_output(const void* node, const void* y);     // the plain ReLU of graph node `node` wrote y (after the version bump)
+bool contraction_path_is_cuda_cores();
+
 // ---- shapes -------------------------------------------------------------------
 inline int64_t numel(const DLArray* a) {
   int64_t n = 1;

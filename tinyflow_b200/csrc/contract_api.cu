@@ -18,11 +18,13 @@ int tc_conv_wgrad(ConvPlan* p, const float* x, const float* dy, float* dw, cudaS
 
 static int g_path = [] { const char* e = getenv("TINYFLOW_CONTRACTION"); return e ? atoi(e) : 0; }();   // 0 auto, 1 CUDA cores, 2 tensor cores
 int contraction_path() { return g_path; }
+bool contraction_path_is_cuda_cores() { return g_path == 1; }
 int tensor_arithmetic();
 void set_tensor_arithmetic(int a);
 int tensor_path_error();
 void tensor_path_error_clear();
 int tensor_path_timeout_probe(long long limit_cycles, cudaStream_t s);
+long long fused_relu_pack_count();
 // which engine served this thread's most recent contraction: 1 = CUDA cores, 2 = tensor cores (0 = none yet)
 static thread_local int t_last_path = 0;
 
@@ -43,6 +45,7 @@ int TfGetArithmetic(void) { return tensor_arithmetic(); }
 
 int TfTensorPathError(void) { return tensor_path_error(); }
 int TfClearTensorPathError(void) { tensor_path_error_clear(); return 0; }
+int TfFusedReluPackCount(long long* count) { if (count) *count = fused_relu_pack_count(); return 0; }
 int TfTensorPathTimeoutProbe(long long limit_cycles, void** cudaStream) { return tensor_path_timeout_probe(limit_cycles, stream_of(cudaStream)); }
 
 int TfSetContractionPath(int path) {
@@ -169,11 +172,5 @@ int DLGpuConvolutionBackwardFilter(const DLArrayHandle input, const DLArrayHandl
   t_last_path = 1;
   return cudacore_conv_wgrad(p, (const float*)input->data, (const float*)doutput->data, out_f32(dfilter), s);
 }
-
-// 1-D / 3-D convolution: symbols only.
-int DLGpuConvolution1DForwardGetOutShape(const int*, const int*, int*, int, const int, const int, void***) { TF_FAIL("1-D convolution is not implemented"); }
-int DLGpuConvolution3DForwardGetOutShape(const int*, const int*, int*, int, const int, const int, const int, const int, void***) { TF_FAIL("3-D convolution is not implemented"); }
-int DLGpuConvolution1DForward(const DLArrayHandle, const DLArrayHandle, DLArrayHandle, void***, void**, int*) { TF_FAIL("1-D convolution is not implemented"); }
-int DLGpuConvolution3DForward(const DLArrayHandle, const DLArrayHandle, DLArrayHandle, void***, void**, int*) { TF_FAIL("3-D convolution is not implemented"); }
 
 }  // extern "C"

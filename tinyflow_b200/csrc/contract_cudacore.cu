@@ -191,6 +191,24 @@ static int launch_contract(AV A, BV B, OV O, int64_t M, int64_t N, int64_t K, fl
   return 0;
 }
 
+// ---- 3-D convolution forward: A = filter [K x C*T*R*S], B = patches of x [C*T*R*S x N*Od*P*Q] ---------------------------
+struct Conv3Geom { int N, C, D, H, W, K, T, R, S, Od, P, Q, pd, ph, pw, sd, sh, sw; };
+struct Fwd3B {
+  const float* x; Conv3Geom g;
+  __device__ __forceinline__ float at(int64_t kk, int64_t j) const {
+    const int RS = g.R * g.S, TRS = g.T * RS, PQ = g.P * g.Q, OPQ = g.Od * PQ;
+    const int c = (int)(kk / TRS); int rem = (int)(kk % TRS);
+    const int t = rem / RS; rem -= t * RS;
+    const int r = rem / g.S, s = rem - r * g.S;
+    const int n = (int)(j / OPQ); int o = (int)(j % OPQ);
+    const int od = o / PQ; o -= od * PQ;
+    const int p = o / g.Q, q = o - p * g.Q;
+    const int z = od * g.sd + t - g.pd, h = p * g.sh + r - g.ph, w = q * g.sw + s - g.pw;
+    if (z < 0 || z >= g.D || h < 0 || h >= g.H || w < 0 || w >= g.W) return 0.f;
+    return x[((((int64_t)n * g.C + c) * g.D + z) * g.H + h) * g.W + w];
+  }
+};
+
 static ConvGeom geom_of(const ConvPlan* p) {
   ConvGeom g;
   g.N = p->N; g.C = p->C; g.H = p->H; g.W = p->W; g.K = p->K; g.R = p->R; g.S = p->S; g.P = p->P; g.Q = p->Q;
@@ -221,6 +239,15 @@ int cudacore_conv_wgrad(const ConvPlan* p, const float* x, const float* dy, floa
   ConvGeom g = geom_of(p);
   int64_t CRS = (int64_t)g.C * g.R * g.S, NPQ = (int64_t)g.N * g.P * g.Q;
   return launch_contract<WgradA, WgradB, MatOut, true>(WgradA{dy, g}, WgradB{x, g}, MatOut{dw, CRS}, g.K, CRS, NPQ, dw, sizeof(float) * g.K * CRS, true, s, "DLGpuConvolutionBackwardFilter");
+}
+
+// `d` points at the 18 ints N, C, D, H, W, K, T, R, S, Od, P, Q, pd, ph, pw, sd, sh, sw of the plan
+int cudacore_conv3d_fwd(const int* d, const float* x, const float* w, float* y, cudaStream_t s) {
+  Conv3Geom g;
+  memcpy(&g, d, sizeof(g));
+  const int64_t CTRS = (int64_t)g.C * g.T * g.R * g.S, vol = (int64_t)g.Od * g.P * g.Q, NV = (int64_t)g.N * vol;
+  return launch_contract<FwdA, Fwd3B, NchwOut, false>(FwdA{w, CTRS}, Fwd3B{x, g}, NchwOut{y, g.K, vol}, g.K, NV, CTRS, y, sizeof(float) * g.K * NV, false, s,
+                                                      "DLGpuConvolution3DForward");
 }
 
 }  // namespace tf

@@ -857,8 +857,12 @@ __global__ void __launch_bounds__(256) pack_matrix_kernel(const float* __restric
 // row through shared memory: reads run along w (TC/8 independent loads per thread in flight), writes along c as
 // 16-byte vectors (8 halves) of hi and of lo.
 struct PackGeom { int N, C, H, W, frame_h, frame_w, off_h, off_w, sh, sw, pitch, dst_c0, c_limit; };
-template <int TC, class E>
-__global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, E* __restrict__ hi, E* __restrict__ lo, PackGeom g, ScaleRef sr) {
+// RELU: the source is the input of a ReLU; the kernel applies it, writes the fp32 result to y_out (same layout as the
+// source), records max|y| like the stand-alone ReLU kernel does, and packs y.  The pack's scale then comes from max|x|, an
+// upper bound of max|y| that is known before the pass starts.
+template <int TC, class E, bool RELU>
+__global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict__ src, E* __restrict__ hi, E* __restrict__ lo, PackGeom g, ScaleRef sr,
+                                                        float* __restrict__ y_out, AmaxOut am) {
   grid_dep_sync();
   // tile[c][f ^ (c / 8)]: the XOR keeps both phases free of bank conflicts (stores: 32 lanes = 32 frame positions
   // of one channel; loads: lanes = 8-channel groups of a few positions that are TC/8 apart)
@@ -889,6 +893,20 @@ __global__ void __launch_bounds__(256) pack_nchw_kernel(const float* __restrict_
     } else {
 #pragma unroll
       for (int k = 0; k < TC / 8; ++k) v[k] = 0.f;
+    }
+    if (RELU) {
+      uint32_t m = 0;
+      if (ok) {
+        float* yp = y_out + (sp - src) - (long long)(TC / 8) * step;        // the element the first load read
+#pragma unroll
+        for (int k = 0; k < TC / 8; ++k) {
+          const float x = v[k];
+          v[k] = x > 0.f ? x : (x != x ? x : 0.f);                           // NaN propagates
+          if (8 * k < avail) { *yp = v[k]; m = max(m, amax_bits(v[k])); }
+          yp += step;
+        }
+      }
+      amax_commit(am, m);
     }
     float* trow = &tile[ty][0];
 #pragma unroll
@@ -1402,24 +1420,55 @@ static ConvTc* conv_state(ConvPlan* p) {
 // One launch of the frame pack: `chans` channels of an NCHW tensor (spatial dims H x W) into columns dst_c0 .. dst_c0 + cover
 // of pk (zeros past `chans`)
 static int launch_pack_nchw(Pack& pk, const ScaleRef& sr, const float* src, int N, int chans, int H, int W, int frame_h, int frame_w, int off_h, int off_w,
-                            int sh, int sw, int dst_c0, int cover, cudaStream_t s) {
+                            int sh, int sw, int dst_c0, int cover, cudaStream_t s, float* relu_out = nullptr, AmaxOut relu_am = AmaxOut{}) {
   PackGeom g{N, chans, H, W, frame_h, frame_w, off_h, off_w, sh, sw, (int)pk.pitch, dst_c0, cover};
   const int tc = cover > 64 ? 128 : cover > 32 ? 64 : 32;
   dim3 grid(N * ((cover + tc - 1) / tc), (frame_h * frame_w + 31) / 32);
   TF_REQUIRE(grid.y <= 65535, "pack: frame of %d x %d positions is too large", frame_h, frame_w);
-  KernelTimer kt("pack_nchw", s, 0, 4.0 * N * chans * H * W / (sh * sw) + 2.0 * elem_of(pk.arith) * pk.rows * cover);
+  KernelTimer kt(relu_out ? "relu_pack" : "pack_nchw", s, 0, (relu_out ? 8.0 : 4.0) * N * chans * H * W / (sh * sw) + 2.0 * elem_of(pk.arith) * pk.rows * cover);
   with_elems(pk, [&](auto* hi, auto* lo) {
     using E = std::remove_pointer_t<decltype(hi)>;
-    if (tc == 128) launch_dep(pack_nchw_kernel<128, E>, grid, dim3(256), 0, s, src, hi, lo, g, sr);
-    else if (tc == 64) launch_dep(pack_nchw_kernel<64, E>, grid, dim3(256), 0, s, src, hi, lo, g, sr);
-    else launch_dep(pack_nchw_kernel<32, E>, grid, dim3(256), 0, s, src, hi, lo, g, sr);
+    if (relu_out) {
+      if (tc == 128) launch_dep(pack_nchw_kernel<128, E, true>, grid, dim3(256), 0, s, src, hi, lo, g, sr, relu_out, relu_am);
+      else if (tc == 64) launch_dep(pack_nchw_kernel<64, E, true>, grid, dim3(256), 0, s, src, hi, lo, g, sr, relu_out, relu_am);
+      else launch_dep(pack_nchw_kernel<32, E, true>, grid, dim3(256), 0, s, src, hi, lo, g, sr, relu_out, relu_am);
+    } else {
+      if (tc == 128) launch_dep(pack_nchw_kernel<128, E, false>, grid, dim3(256), 0, s, src, hi, lo, g, sr, (float*)nullptr, AmaxOut{});
+      else if (tc == 64) launch_dep(pack_nchw_kernel<64, E, false>, grid, dim3(256), 0, s, src, hi, lo, g, sr, (float*)nullptr, AmaxOut{});
+      else launch_dep(pack_nchw_kernel<32, E, false>, grid, dim3(256), 0, s, src, hi, lo, g, sr, (float*)nullptr, AmaxOut{});
+    }
   });
-  TF_AFTER(s, "pack_nchw");
+  TF_AFTER(s, relu_out ? "relu_pack" : "pack_nchw");
   return 0;
 }
 static bool pack_valid(const Pack& pk, int ar, const void* src, uint64_t ver, int tag, long long rows, long long cols) {
   return pk.hi && pk.arith == ar && pk.src == src && pk.version == ver && pk.tag == tag && pk.rows == rows && pk.cols == cols;
 }
+// ---- producers that write a consumer's pack ---------------------------------------------------------------------------
+// The graph calls BN -> ReLU -> convolution as separate entry points, and the convolution then re-reads the ReLU's output
+// to pack it.  Every ReLU call that comes with a descriptor (one per graph node, stable from step to step) leaves a note
+// "this address was written by that node"; when a frame pack of x is made, the node that wrote x is looked up and the
+// plan is remembered under the node.  From the next step on that node's ReLU packs its output for the plan in the same
+// pass (relu_pack), whatever address the executor hands it, and the convolution finds the pack valid.  A wrong guess
+// costs one unused pack.
+struct PackTarget { ConvTc* st; int N, C, H, W; };
+static std::atomic<long long> g_fused_relu_packs{0};
+static std::mutex g_targets_mu;
+struct ReluNote { const void* node; uint64_t version; };
+static std::unordered_map<const void*, ReluNote> g_relu_writer;             // output address -> the ReLU node that wrote it, and the write version it left
+static std::unordered_map<const void*, PackTarget> g_pack_targets;          // ReLU descriptor -> plan that packs its output
+void tc_note_relu_output(const void* node, const void* y) {     // call after the output's write version was bumped
+  if (!node) return;
+  const uint64_t ver = version_of(y);
+  std::lock_guard<std::mutex> lk(g_targets_mu);
+  g_relu_writer[y] = ReluNote{node, ver};
+}
+static void remember_pack_target(const void* x, uint64_t ver, ConvTc* st, const ConvPlan* p) {
+  std::lock_guard<std::mutex> lk(g_targets_mu);
+  auto it = g_relu_writer.find(x);
+  if (it != g_relu_writer.end() && it->second.version == ver) g_pack_targets[it->second.node] = PackTarget{st, p->N, p->C, p->H, p->W};
+}
+
 // the x operand of a plan: frame pack (classes A, B), patch matrix (class C) or one frame per stride phase (class D)
 static int pack_x(ConvTc* st, int ar, const ConvPlan* p, const float* x, cudaStream_t s, int* oom) {
   Pack& pk = st->x;
@@ -1459,6 +1508,7 @@ static int pack_x(ConvTc* st, int ar, const ConvPlan* p, const float* x, cudaStr
   }
   if (rc) return -1;
   pk.src = x; pk.version = ver; pk.tag = st->cls;
+  if ((st->cls == 1 || st->cls == 2) && p->stride_h == 1 && p->stride_w == 1) remember_pack_target(x, ver, st, p);
   return 0;
 }
 static int pack_dy(ConvTc* st, int ar, const ConvPlan* p, const float* dy, cudaStream_t s, int* oom) {
@@ -1577,6 +1627,42 @@ static void im2col_taps(TapList& taps, int R, int S) {
 }
 // result of a tensor-path entry point from the launcher's code
 static inline int tc_result(int rc) { return rc < 0 ? -1 : (rc > 0 ? 1 : 1); }
+
+// ReLU forward (graph node `node`: the address of its descriptor) whose output the tensor path is expected to pack next:
+// y = relu(x) and the consumer plan's frame pack of y in one pass.  Returns 1 when it did that, 0 when the caller should run the plain ReLU (no known consumer, or in the
+// fp16 arithmetic no recorded max|x| to bound the scale with), -1 on error.
+int tc_fused_relu_pack(const void* node, const float* x, float* y, int64_t n, cudaStream_t s) {
+  static const bool on = [] { const char* e = getenv("TINYFLOW_FUSE_RELU_PACK"); return e ? atoi(e) != 0 : true; }();
+  if (!on || !node || contraction_path_is_cuda_cores()) return 0;
+  PackTarget t;
+  {
+    std::lock_guard<std::mutex> lk(g_targets_mu);
+    auto it = g_pack_targets.find(node);
+    if (it == g_pack_targets.end()) return 0;
+    t = it->second;
+  }
+  if ((int64_t)t.N * t.C * t.H * t.W != n || x == y) return 0;
+  const int ar = tensor_arithmetic();
+  ConvTc* st = t.st;
+  if (use_im2col(st, ar)) return 0;
+  const uint32_t* bound = ar == kArithF16 ? amax_tracked(x) : nullptr;
+  if (ar == kArithF16 && !bound) return 0;
+  std::lock_guard<std::mutex> lk(st->mu);
+  Pack& pk = st->x;
+  int oom = 0;
+  const long long rows = (long long)t.N * st->frame_h * st->frame_w;
+  if (pack_alloc(pk, ar, rows, t.C, s, &oom)) return 0;
+  note_write(y);
+  AmaxOut am = amax_track_begin(y);
+  ScaleRef sr{bound, nullptr, reinterpret_cast<float*>(pk.words + 2)};       // scale from max|x| >= max|relu(x)|; tf32: no scale
+  note_compute_stream(s);
+  if (launch_pack_nchw(pk, sr, x, t.N, t.C, t.H, t.W, st->frame_h, st->frame_w, st->x_off_h, st->x_off_w, 1, 1, 0, (int)pk.pitch, s, y, am)) return -1;
+  pk.src = y; pk.version = version_of(y); pk.tag = st->cls;
+  tc_note_relu_output(node, y);
+  g_fused_relu_packs.fetch_add(1, std::memory_order_relaxed);
+  return 1;
+}
+long long fused_relu_pack_count() { return g_fused_relu_packs.load(std::memory_order_relaxed); }
 
 int tc_conv_fwd(ConvPlan* p, const float* x, const float* w, float* y, cudaStream_t s, int* oom) {
   ConvTc* st = conv_state(p);

@@ -834,7 +834,16 @@ int DLGpuActivationForward(const DLArrayHandle input, DLArrayHandle output, int 
   int64_t n = numel(input);
   switch (activationMode) {
     case 0: return run_map1(F(input), FM(output), n, s, "DLGpuActivationForward(sigmoid)", FSigmoid{});
-    case 1: return run_map1(F(input), FM(output), n, s, "DLGpuActivationForward(relu)", FRelu{});
+    case 1: {
+      // when the tensor path is known to pack this output for a convolution next, one kernel writes y and the pack
+      const void* node = plan_of<TensorPlan>(cudnnlist, kPlanTensor);
+      int fused = tc_fused_relu_pack(node, F(input), (float*)output->data, n, s);
+      if (fused < 0) return -1;
+      if (fused) return 0;
+      int rc = run_map1(F(input), FM(output), n, s, "DLGpuActivationForward(relu)", FRelu{});
+      tc_note_relu_output(node, output->data);
+      return rc;
+    }
     case 2: return run_map1(F(input), FM(output), n, s, "DLGpuActivationForward(tanh)", FTanh{});
     case 3: {
       // softmax over all non-batch elements of each sample (src/gpu_op.cu:3238-3248)

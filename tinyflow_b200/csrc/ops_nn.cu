@@ -378,7 +378,7 @@ __device__ __forceinline__ void bn_group_sum(float (&part)[VEC], float (*red)[32
 }
 
 template <int VEC>
-__global__ void __launch_bounds__(32 * kBnGroups) bn_pa_fwd_regs_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ save_mean, float* __restrict__ save_inv, int N, int64_t F) {
+__global__ void __launch_bounds__(32 * kBnGroups) bn_pa_fwd_regs_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ save_mean, float* __restrict__ save_inv, int N, int64_t F, AmaxOut am) {
   grid_dep_sync();
   using V = typename VecT<VEC>::type;
   __shared__ float red[kBnGroups][32][VEC];
@@ -423,6 +423,7 @@ __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_fwd_regs_kernel(const fl
     float r = rsqrtf(a);
     inv[k] = r * (1.5f - 0.5f * a * r * r);       // one Newton step: full fp32 accuracy
   }
+  uint32_t amax = 0;
 #pragma unroll
   for (int i = 0; i < kBnPerThread; ++i) {
     int n = ty + i * kBnGroups;
@@ -430,7 +431,7 @@ __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_fwd_regs_kernel(const fl
       V t;
       float* tp = reinterpret_cast<float*>(&t);
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) tp[k] = (v[i][k] - mean[k]) * inv[k];
+      for (int k = 0; k < VEC; ++k) { tp[k] = (v[i][k] - mean[k]) * inv[k]; amax = max(amax, amax_bits(tp[k])); }
       yv[(int64_t)n * FV + fv] = t;
     }
   }
@@ -438,6 +439,7 @@ __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_fwd_regs_kernel(const fl
 #pragma unroll
     for (int k = 0; k < VEC; ++k) { save_mean[fv * VEC + k] = mean[k]; save_inv[fv * VEC + k] = inv[k]; }
   }
+  amax_commit(am, amax);        // max|y|: the activation that follows can pack its output for the next convolution in its own pass
 }
 
 template <int VEC>
@@ -552,8 +554,9 @@ __global__ void __launch_bounds__(512) bn_sp_bwd_kernel(const float* __restrict_
 }
 
 static void launch_bn_fwd_regs(const float* x, float* y, float* sm, float* si, int N, int64_t F, cudaStream_t s) {
-  if (F % 4 == 0 && aligned16(x) && aligned16(y)) launch_dep(bn_pa_fwd_regs_kernel<4>, dim3((unsigned)((F / 4 + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, y, sm, si, N, F);
-  else launch_dep(bn_pa_fwd_regs_kernel<1>, dim3((unsigned)((F + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, y, sm, si, N, F);
+  AmaxOut am = amax_track_begin(y);
+  if (F % 4 == 0 && aligned16(x) && aligned16(y)) launch_dep(bn_pa_fwd_regs_kernel<4>, dim3((unsigned)((F / 4 + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, y, sm, si, N, F, am);
+  else launch_dep(bn_pa_fwd_regs_kernel<1>, dim3((unsigned)((F + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, y, sm, si, N, F, am);
 }
 static void launch_bn_bwd_regs(const float* x, const float* dy, float* dx, const float* sm, const float* si, int N, int64_t F, cudaStream_t s) {
   AmaxOut am = amax_track_begin(dx);          // dx is the output gradient of the convolution in front of this layer
@@ -739,13 +742,5 @@ int DLGpuBatchNormalizationBackward(const DLArrayHandle input, const DLArrayHand
   TF_AFTER(s, "DLGpuBatchNormalizationBackward");
   return 0;
 }
-
-// ---- 1-D / 3-D pooling: symbols only ------------------------------------------------------------
-int DLGpuPooling1DForwardGetOutShape(const int*, int*, int, int, const int, const int, const int, void***) { TF_FAIL("1-D pooling is not implemented"); }
-int DLGpuPooling3DForwardGetOutShape(const int*, int*, int, int, const int, const int, const int, const int, const int, const int, const int, const int, const int, void***) { TF_FAIL("3-D pooling is not implemented"); }
-int DLGpuPooling1DForward(const DLArrayHandle, DLArrayHandle, void***, void**) { TF_FAIL("1-D pooling is not implemented"); }
-int DLGpuPooling3DForward(const DLArrayHandle, DLArrayHandle, void***, void**) { TF_FAIL("3-D pooling is not implemented"); }
-int DLGpuPooling1DBackward(const DLArrayHandle, const DLArrayHandle, const DLArrayHandle, DLArrayHandle, void***, void**) { TF_FAIL("1-D pooling is not implemented"); }
-int DLGpuPooling3DBackward(const DLArrayHandle, const DLArrayHandle, const DLArrayHandle, DLArrayHandle, void***, void**) { TF_FAIL("3-D pooling is not implemented"); }
 
 }  // extern "C"

@@ -463,3 +463,75 @@ def tensor_path_error() -> int:
 
 def clear_tensor_path_error():
     check_call(_LIB.TfClearTensorPathError())
+
+
+def fused_relu_pack_count() -> int:
+    """How many ReLU forward calls so far also wrote the packed operand of the convolution that reads their output."""
+    n = ctypes.c_longlong(0)
+    check_call(_LIB.TfFusedReluPackCount(ctypes.byref(n)))
+    return n.value
+
+
+# ---- 1-D / 3-D convolution (forward) and pooling (gpu_op.py:277-313, 368-404, 406-500, 577-660) ----------------------
+def convolution_1d_forward_get_out_shape(input_shapes, filter_shapes, dataformat, padding, v):
+    assert len(input_shapes) == 3 and len(filter_shapes) == 3
+    out = c_array(ctypes.c_int, [0, 0, 0])
+    cell = new_cell(3)
+    check_call(_LIB.DLGpuConvolution1DForwardGetOutShape(c_array(ctypes.c_int, list(input_shapes)), c_array(ctypes.c_int, list(filter_shapes)), out,
+                                                         _code(_DATAFORMAT, dataformat), _code(_PADDING, padding), int(v), cell))
+    return tuple(out), cell
+
+
+def convolution_1d_forward(in_arr, in_filter, out_arr, cudnnlist, cudnnHandle):
+    short = _short_cell()
+    check_call(_LIB.DLGpuConvolution1DForward(_h(in_arr), _h(in_filter), _h(out_arr), cudnnlist, cudnnHandle, short))
+    return _LIB.getInt(short)
+
+
+def convolution_3d_forward_get_out_shape(input_shapes, filter_shapes, dataformat, padding, s1, s2, s3):
+    assert len(input_shapes) == 5 and len(filter_shapes) == 5
+    out = c_array(ctypes.c_int, [0] * 5)
+    cell = new_cell(3)
+    check_call(_LIB.DLGpuConvolution3DForwardGetOutShape(c_array(ctypes.c_int, list(input_shapes)), c_array(ctypes.c_int, list(filter_shapes)), out,
+                                                         _code(_DATAFORMAT, dataformat), _code(_PADDING, padding), int(s1), int(s2), int(s3), cell))
+    return tuple(out), cell
+
+
+def convolution_3d_forward(in_arr, in_filter, out_arr, cudnnlist, cudnnHandle):
+    short = _short_cell()
+    check_call(_LIB.DLGpuConvolution3DForward(_h(in_arr), _h(in_filter), _h(out_arr), cudnnlist, cudnnHandle, short))
+    return _LIB.getInt(short)
+
+
+def pooling_1d_forward_get_out_shape(input_shapes, dataformat, poolingMode, padding_w, v, filter_w):
+    assert len(input_shapes) == 3
+    out = c_array(ctypes.c_int, [0, 0, 0])
+    cell = new_cell(3)
+    check_call(_LIB.DLGpuPooling1DForwardGetOutShape(c_array(ctypes.c_int, list(input_shapes)), out, _code(_DATAFORMAT, dataformat), _code(_POOLING, poolingMode),
+                                                     int(padding_w), int(v), int(filter_w), cell))
+    return tuple(out), cell
+
+
+def pooling_1d_forward(in_arr, out_arr, cudnnlist, cudnnHandle):
+    check_call(_LIB.DLGpuPooling1DForward(_h(in_arr), _h(out_arr), cudnnlist, cudnnHandle))
+
+
+def pooling_1d_backward(in_arr, out_arr, dout_arr, din_arr, cudnnlist, cudnnHandle):
+    check_call(_LIB.DLGpuPooling1DBackward(_h(in_arr), _h(out_arr), _h(dout_arr), _h(din_arr), cudnnlist, cudnnHandle))
+
+
+def pooling_3d_forward_get_out_shape(input_shapes, dataformat, poolingMode, padding1, padding2, padding3, s1, s2, s3, filter1, filter2, filter3):
+    assert len(input_shapes) == 5
+    out = c_array(ctypes.c_int, [0] * 5)
+    cell = new_cell(3)
+    check_call(_LIB.DLGpuPooling3DForwardGetOutShape(c_array(ctypes.c_int, list(input_shapes)), out, _code(_DATAFORMAT, dataformat), _code(_POOLING, poolingMode),
+                                                     int(padding1), int(padding2), int(padding3), int(s1), int(s2), int(s3), int(filter1), int(filter2), int(filter3), cell))
+    return tuple(out), cell
+
+
+def pooling_3d_forward(in_arr, out_arr, cudnnlist, cudnnHandle):
+    check_call(_LIB.DLGpuPooling3DForward(_h(in_arr), _h(out_arr), cudnnlist, cudnnHandle))
+
+
+def pooling_3d_backward(in_arr, out_arr, dout_arr, din_arr, cudnnlist, cudnnHandle):
+    check_call(_LIB.DLGpuPooling3DBackward(_h(in_arr), _h(out_arr), _h(dout_arr), _h(din_arr), cudnnlist, cudnnHandle))

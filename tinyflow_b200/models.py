@@ -9,6 +9,7 @@ network order).  The graphs follow the reference's model scripts node for node:
 * :func:`vgg16`      pycode/tinyflow/VGG16_test_leo.py:169-254
 * :func:`resnet50`   pycode/tinyflow/ResNet50_test_leo.py:27-261
 * :func:`inceptionv3` pycode/tinyflow/Inceptionv3_test_leo.py:558-1020
+* :func:`densenet121` pycode/tinyflow/DenseNet_test_leo.py:13-127 (beyond the five configurations)
 
 Initial values are synthetic: He-normal weights (std = sqrt(2 / fan_in)), zero biases, drawn from a
 seeded ``numpy.random.RandomState``.
@@ -285,7 +286,163 @@ def inceptionv3(batch=32, classes=1000, image=299, dropout=0.8):
     return Model("inceptionv3", X, y_, loss, y, params, (batch, 3, image, image), (batch, classes), [drop])
 
 
-BUILDERS = {"mlp": mlp, "lenet5": lenet5, "vgg16": vgg16, "resnet50": resnet50, "inceptionv3": inceptionv3}
+def densenet121(batch=32, classes=1000, image=224, dropout=0.2, growth=32):
+    """DenseNet-121 wired like DenseNet_test_leo.py:28-127: BN -> ReLU -> 1x1 conv -> dropout -> BN -> ReLU -> 3x3 conv ->
+    dropout bottlenecks whose outputs are concatenated onto their inputs (6 / 12 / 24 / 16 per block), transition layers
+    that halve channels (1x1 conv) and resolution (2x2 average pool), global average pool, one dense layer."""
+    X, y_ = ad.Placeholder("X"), ad.Placeholder("y_")
+    W0, W1, b1 = ad.Variable("W0"), ad.Variable("W1"), ad.Variable("b1")
+    params = {W0: (2 * growth, 3, 7, 7)}
+    tail = {}
+    drops = []
+
+    def bn_relu(x):
+        return ad.activation_forward_op(ad.bn_forward_op(x, "NCHW", "pre_activation"), "NCHW", "relu")
+
+    def drop(x):
+        d = ad.dropout_forward_op(x, "NCHW", dropout)
+        drops.append(d)
+        return d
+
+    def bottleneck(x, cin, name):
+        Wa, Wb = ad.Variable(name + "_W1"), ad.Variable(name + "_W2")
+        params[Wa], params[Wb] = (4 * growth, cin, 1, 1), (growth, 4 * growth, 3, 3)
+        h = drop(ad.convolution_2d_forward_op(bn_relu(x), Wa, "NCHW", "SAME", 1, 1))
+        return drop(ad.convolution_2d_forward_op(bn_relu(h), Wb, "NCHW", "SAME", 1, 1))
+
+    def dense_block(x, cin, layers, name):
+        for i in range(layers):
+            x = ad.concat_forward_op(x, bottleneck(x, cin, "%s_bottleneck%d" % (name, i)))
+            cin += growth
+        return x, cin
+
+    def transition(x, cin, name):
+        Wt = ad.Variable(name + "_W1")
+        params[Wt] = (cin // 2, cin, 1, 1)
+        h = drop(ad.convolution_2d_forward_op(bn_relu(x), Wt, "NCHW", "SAME", 1, 1))
+        return ad.pooling_2d_forward_op(h, "NCHW", "mean", 0, 0, 2, 2, 2, 2), cin // 2
+
+    h = ad.convolution_2d_forward_op(X, W0, "NCHW", "SAME", 2, 2)
+    h = ad.pooling_2d_forward_op(h, "NCHW", "max", 1, 1, 2, 2, 3, 3)
+    cin = 2 * growth
+    for bi, layers in enumerate((6, 12, 24, 16)):
+        h, cin = dense_block(h, cin, layers, "dense%d" % (bi + 1))
+        if bi < 3:
+            h, cin = transition(h, cin, "trans%d" % (bi + 1))
+    final = image // 32
+    h = ad.pooling_2d_forward_op(bn_relu(h), "NCHW", "mean", 0, 0, 1, 1, final, final)
+    y = ad.fullyactivation_forward_op(ad.dense(ad.flatten_op(h), W1, b1), "NCHW", "softmax")
+    loss = ad.crossEntropy_loss(y, y_)
+    # the reference feeds W0, W1, b1 first and the blocks' filters after them (DenseNet_test_leo.py:107-114)
+    ordered = {W0: params.pop(W0), W1: (cin, classes), b1: (classes,)}
+    ordered.update(params)
+    return Model("densenet121", X, y_, loss, y, ordered, (batch, 3, image, image), (batch, classes), drops)
+
+
+def inceptionv4(batch=32, classes=1000, image=299, dropout=0.8):
+    """Inception-v4 without batch norm, wired like Inceptionv4_test_leo.py:28-340: conv+ReLU units, chained two-input
+    channel concats; stem with two pooled/strided forks and a 7x1 / 1x7 fork, 4 A modules at 35x35x384, reduction to
+    17x17x1024, 7 B modules, reduction to 8x8x1536, 3 C modules with split 1x3 / 3x1 ends, global average pool,
+    squeeze, dropout, one dense layer."""
+    X, y_ = ad.Placeholder("X"), ad.Placeholder("y_")
+    params = {}
+
+    def unit(x, name, shape, padding="SAME", stride=1):
+        w = ad.Variable(name)
+        params[w] = shape
+        return _conv_relu(x, w, padding, stride, stride)
+
+    def chain(x, prefix, specs):
+        for suffix, shape in specs:
+            x = unit(x, prefix + suffix, shape)
+        return x
+
+    def cat(*xs):
+        out = xs[0]
+        for x in xs[1:]:
+            out = ad.concat_forward_op(out, x)
+        return out
+
+    def avg3(x):
+        return ad.pooling_2d_forward_op(x, "NCHW", "mean", 1, 1, 1, 1, 3, 3)
+
+    def pool_s2(x, mode):
+        return ad.pooling_2d_forward_op(x, "NCHW", mode, 0, 0, 2, 2, 3, 3)
+
+    # stem: 299 -> 35x35x384
+    h = unit(X, "f1", (32, 3, 3, 3), "VALID", 2)
+    h = unit(h, "f2", (32, 32, 3, 3), "VALID")
+    h = unit(h, "f3", (64, 32, 3, 3))
+    h = cat(pool_s2(h, "max"), unit(h, "f4", (96, 64, 3, 3), "VALID", 2))                     # 160 channels
+    left = unit(unit(h, "f5_1", (64, 160, 1, 1)), "f5_2", (96, 64, 3, 3), "VALID")
+    right = chain(h, "f6_", [("1", (64, 160, 1, 1)), ("2", (64, 64, 7, 1)), ("3", (64, 64, 1, 7))])
+    right = unit(right, "f6_4", (96, 64, 3, 3), "VALID")
+    h = cat(left, right)                                                                      # 192 channels
+    strided = unit(h, "f7", (192, 192, 3, 3), "VALID", 2)
+    h = cat(pool_s2(h, "max"), strided)                                                       # 384 channels
+    W, b = ad.Variable("W"), ad.Variable("b")
+    params[W], params[b] = (1536, classes), (classes,)
+
+    def module_a(x, name):
+        f = name + "filter1_1_"
+        b0 = unit(x, f + "0", (96, 384, 1, 1))
+        b1 = chain(x, f, [("1a", (64, 384, 1, 1)), ("1b", (96, 64, 3, 3))])
+        b2 = chain(x, f, [("2a", (64, 384, 1, 1)), ("2b", (96, 64, 3, 3)), ("2c", (96, 96, 3, 3))])
+        return cat(b0, b1, b2, unit(avg3(x), f + "3a", (96, 384, 1, 1)))
+
+    def reduce_a(x, cin, name):
+        f = name + "filter2_1_"
+        b0 = unit(x, f + "0", (384, cin, 3, 3), "VALID", 2)
+        b1 = chain(x, f, [("1a", (192, cin, 1, 1)), ("1b", (224, 192, 3, 3))])
+        b1 = unit(b1, f + "1c", (256, 224, 3, 3), "VALID", 2)
+        return cat(b0, b1, pool_s2(x, "mean"))
+
+    def module_b(x, cin, name):
+        f = name + "filter2_2_"
+        b0 = unit(x, f + "0", (384, cin, 1, 1))
+        b1 = chain(x, f, [("1a", (192, cin, 1, 1)), ("1b", (224, 192, 1, 7)), ("1c", (256, 224, 7, 1))])
+        b2 = chain(x, f, [("2a", (192, cin, 1, 1)), ("2b", (192, 192, 7, 1)), ("2c", (224, 192, 1, 7)),
+                          ("2d", (224, 224, 7, 1)), ("2e", (256, 224, 1, 7))])
+        return cat(b0, b1, b2, unit(avg3(x), f + "3a", (128, cin, 1, 1)))
+
+    def reduce_b(x, cin, name):
+        f = name + "filter3_1_"
+        b0 = unit(unit(x, f + "0a", (192, cin, 1, 1)), f + "0b", (192, 192, 3, 3), "VALID", 2)
+        b1 = chain(x, f, [("1a", (256, cin, 1, 1)), ("1b", (256, 256, 1, 7)), ("1c", (320, 256, 7, 1))])
+        b1 = unit(b1, f + "1d", (320, 320, 3, 3), "VALID", 2)
+        return cat(b0, b1, pool_s2(x, "mean"))
+
+    def module_c(x, cin, name):
+        f = name + "filter3_2_"
+        b0 = unit(x, f + "0", (256, cin, 1, 1))
+        b1a = unit(x, f + "1a", (384, cin, 1, 1))
+        b1 = ad.concat_forward_op(unit(b1a, f + "1b", (256, 384, 1, 3)), unit(b1a, f + "1c", (256, 384, 3, 1)))
+        b2c = chain(x, f, [("2a", (384, cin, 1, 1)), ("2b", (448, 384, 1, 3)), ("2c", (512, 448, 3, 1))])
+        b2 = ad.concat_forward_op(unit(b2c, f + "2d", (256, 512, 3, 1)), unit(b2c, f + "2e", (256, 512, 1, 3)))
+        return cat(b0, b1, b2, unit(avg3(x), f + "3a", (256, cin, 1, 1)))
+
+    for i in range(1, 5):
+        h = module_a(h, "a%d" % i)
+    h = reduce_a(h, 384, "ra")
+    for i in range(1, 8):
+        h = module_b(h, 1024, "b%d" % i)
+    h = reduce_b(h, 1024, "rb")
+    for i in range(1, 4):
+        h = module_c(h, 1536, "c%d" % i)
+
+    side = (image - 3) // 2 + 1 - 2          # 147 for 299
+    side = (side - 3) // 2 + 1 - 2           # 71
+    for _ in range(3):
+        side = (side - 3) // 2 + 1           # 35, 17, 8
+    h = ad.pooling_2d_forward_op(h, "NCHW", "mean", 0, 0, 1, 1, side, side)
+    drop = ad.fullydropout_forward_op(ad.squeeze_op(h), "NCHW", dropout)
+    y = ad.fullyactivation_forward_op(ad.dense(drop, W, b), "NCHW", "softmax")
+    loss = ad.crossEntropy_loss(y, y_)
+    return Model("inceptionv4", X, y_, loss, y, params, (batch, 3, image, image), (batch, classes), [drop])
+
+
+BUILDERS = {"mlp": mlp, "lenet5": lenet5, "vgg16": vgg16, "resnet50": resnet50, "inceptionv3": inceptionv3, "densenet121": densenet121,
+            "inceptionv4": inceptionv4}
 
 
 def synthetic_batch(model: Model, seed=1234, rank=0, input_dist="normal"):
