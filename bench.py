@@ -35,6 +35,14 @@ WORKLOADS = {
 }
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch of the contraction kernel, from one profiler
+# capture: every distinct convolution layer of the workload at its benchmark batch launched on its own (`--layer WORKLOAD`,
+# a few hundred MB on the device at a time), each layer's three launches weighted by how often the layer occurs in the graph.
+# The full step holds tens of GB and its counters need several replay passes, so it is not captured whole; a layer's
+# operands are the same size either way.  profiles/gemm3x_dram_traffic_resnet50_b64.md has the command and the table.
+CONTRACTION_DRAM_BYTES_PER_LAUNCH = {("resnet50", "3xfp16"): 89.2e6}
+
+
 def build_model(name, batch=None):
     from tinyflow_b200 import models
     cfg = dict(WORKLOADS[name])
@@ -198,46 +206,71 @@ def run_reference_arm(args):
 # ---------------------------------------------------------------------------------------------------
 # one layer on its own (profiling aid)
 # ---------------------------------------------------------------------------------------------------
+def conv_layers_of(workload):
+    """Distinct convolution layers of a workload's graph at its benchmark batch: [(N, C, H, W, K, R, S, padding, stride, count)]."""
+    from tinyflow_b200 import autodiff as ad
+    model, cfg = build_model(workload)
+    ex = ad.Executor(model.loss, model.y, cfg["lr"], None, None, None, optimizer="sgd")
+    shapes = {model.X: model.input_shape, model.y_: model.label_shape}
+    shapes.update({var: tuple(shape) for var, shape in model.param_shapes.items()})
+    ex.infer_shape(shapes)
+    found = {}
+    for node in ex.topo_order:
+        if type(node.op).__name__ == "Convolution2DForwardOp":
+            x, w = ex.node_to_shape_map[node.inputs[0]], ex.node_to_shape_map[node.inputs[1]]
+            key = (*x, w[0], w[2], w[3], node.padding, node.u)
+            found[key] = found.get(key, 0) + 1
+    return [(*k, c) for k, c in found.items()]
+
+
 def run_layer(args):
+    """One convolution layer (or, given a workload name, each distinct layer of that workload in turn) on its own."""
     import ctypes
     import numpy as np
     from tinyflow_b200 import gpu_op, ndarray
     from tinyflow_b200._base import _LIB
-    f = args.layer.split(",")
-    N, C, H, W, K, R, S = (int(v) for v in f[:7])
-    padding, stride = f[7], int(f[8])
+    if args.layer in WORKLOADS:
+        layers = conv_layers_of(args.layer)
+    else:
+        f = args.layer.split(",")
+        layers = [(*(int(v) for v in f[:7]), f[7], int(f[8]), 1)]
     ctx = ndarray.gpu(0)
     stream = gpu_op.create_cudaStream()
     cudnn = gpu_op.create_cudnnHandle(stream)
     rng = np.random.RandomState(0)
-    x = ndarray.array(rng.randn(N, C, H, W).astype(np.float32), ctx)
-    w = ndarray.array((rng.randn(K, C, R, S) * np.sqrt(2.0 / (C * R * S))).astype(np.float32), ctx)
-    out_shape, cell = gpu_op.convolution_2d_forward_get_out_shape((N, C, H, W), (K, C, R, S), "NCHW", padding, stride, stride)
-    y, dy = ndarray.empty(out_shape, ctx), ndarray.array(rng.randn(*out_shape).astype(np.float32), ctx)
-    dx, dw = ndarray.empty((N, C, H, W), ctx), ndarray.empty((K, C, R, S), ctx)
+    out = []
+    for (N, C, H, W, K, R, S, padding, stride, count) in layers:
+        x = ndarray.array(rng.randn(N, C, H, W).astype(np.float32), ctx)
+        w = ndarray.array((rng.randn(K, C, R, S) * np.sqrt(2.0 / (C * R * S))).astype(np.float32), ctx)
+        out_shape, cell = gpu_op.convolution_2d_forward_get_out_shape((N, C, H, W), (K, C, R, S), "NCHW", padding, stride, stride)
+        y, dy = ndarray.empty(out_shape, ctx), ndarray.array(rng.randn(*out_shape).astype(np.float32), ctx)
+        dx, dw = ndarray.empty((N, C, H, W), ctx), ndarray.empty((K, C, R, S), ctx)
 
-    def passes():
-        gpu_op.convolution_2d_forward(x, w, y, cell, cudnn, stream)
-        if C >= 16:
-            gpu_op.convolution_backward_data(x, dy, w, dx, cell, cudnn, stream)
-        gpu_op.convolution_backward_filter(x, dy, w, dw, cell, cudnn, stream)
+        def passes():
+            gpu_op.convolution_2d_forward(x, w, y, cell, cudnn, stream)
+            if C >= 16:
+                gpu_op.convolution_backward_data(x, dy, w, dx, cell, cudnn, stream)
+            gpu_op.convolution_backward_filter(x, dy, w, dw, cell, cudnn, stream)
 
-    for _ in range(max(args.warmup, 1)):
-        passes()
-    gpu_op.device_synchronize()
-    _LIB.TfKernelTimingEnable(2)
-    for _ in range(args.steps):
-        passes()
-    gpu_op.device_synchronize()
-    report = ctypes.create_string_buffer(1 << 16)
-    _LIB.TfKernelTimingReport(report, len(report))
-    _LIB.TfKernelTimingEnable(0)
-    rows = json.loads(report.value.decode() or "[]")
-    for r in rows:
-        t = r["ms"] / max(r["launches"], 1)
-        r.update(us_per_launch=1000.0 * t, tflops=(r["flops"] / r["launches"] / t / 1e9 if t and r["flops"] else 0.0),
-                 gbs=(r["bytes"] / r["launches"] / t / 1e6 if t and r["bytes"] else 0.0))
-    print(json.dumps({"layer": args.layer, "arithmetic": gpu_op.tensor_arithmetic(), "steps": args.steps, "kernels": rows}))
+        for _ in range(max(args.warmup, 1)):
+            passes()
+        gpu_op.device_synchronize()
+        _LIB.TfKernelTimingEnable(2)
+        for _ in range(args.steps):
+            passes()
+        gpu_op.device_synchronize()
+        report = ctypes.create_string_buffer(1 << 16)
+        _LIB.TfKernelTimingReport(report, len(report))
+        _LIB.TfKernelTimingEnable(0)
+        rows = json.loads(report.value.decode() or "[]")
+        for r in rows:
+            t = r["ms"] / max(r["launches"], 1)
+            r.update(us_per_launch=1000.0 * t, tflops=(r["flops"] / r["launches"] / t / 1e9 if t and r["flops"] else 0.0),
+                     gbs=(r["bytes"] / r["launches"] / t / 1e6 if t and r["bytes"] else 0.0))
+        out.append({"layer": "%d,%d,%d,%d,%d,%d,%d,%s,%d" % (N, C, H, W, K, R, S, padding, stride), "count_in_graph": count,
+                    "passes": 3 if C >= 16 else 2, "kernels": rows})
+        del x, w, y, dy, dx, dw
+    print(json.dumps({"layers": out, "arithmetic": gpu_op.tensor_arithmetic(), "steps": args.steps, "warmup": max(args.warmup, 1)}))
     return 0
 
 
@@ -293,9 +326,10 @@ def main():
     ap.add_argument("--memory-plan", default="none", choices=["none", "vdnn-conv", "vdnn-all"],
                     help="replay a swap/release plan (reference message format) during every step; not the headline configuration")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch override (profiling on a small case; not the headline configuration)")
-    ap.add_argument("--layer", default=None, metavar="N,C,H,W,K,R,S,PADDING,STRIDE",
-                    help="time the three passes of ONE convolution layer on its own (e.g. 64,256,14,14,256,3,3,SAME,1) and print a "
-                         "per-kernel JSON table: the small case profiler captures run on; not the headline configuration")
+    ap.add_argument("--layer", default=None, metavar="N,C,H,W,K,R,S,PADDING,STRIDE | WORKLOAD",
+                    help="time the three passes of ONE convolution layer on its own (e.g. 64,256,14,14,256,3,3,SAME,1), or of every "
+                         "distinct layer of a workload one after the other (e.g. resnet50), and print a per-kernel JSON table: the "
+                         "small cases profiler captures run on; not the headline configuration")
     ap.add_argument("--matmul", default=None, metavar="M,K,N",
                     help="time one M x K by K x N product in both arithmetic modes of the tensor path (3xFP16, 3xTF32) and on the "
                          "exact-fp32 CUDA-core kernel; prints a JSON line (measures the issued tensor rate each mode reaches)")
@@ -528,7 +562,9 @@ def main():
             peak = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
             ach = top["flops"] / (top["ms"] / 1000.0) / 1e12
             roofline = {"bound": "tensor", "kernel": top["name"], "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                        "traffic": None, "launches": top["launches"], "avg_us": 1000.0 * top["ms"] / max(top["launches"], 1),
+                        "traffic": CONTRACTION_DRAM_BYTES_PER_LAUNCH.get((args.workload, gpu_op.tensor_arithmetic())) if args.batch is None else None,
+                        "traffic_source": "DRAM read+write bytes per launch: profiler capture of each distinct convolution layer of this workload at this batch, launched on its own, weighted by its count in the graph (not captured in this run)",
+                        "launches": top["launches"], "avg_us": 1000.0 * top["ms"] / max(top["launches"], 1),
                         "issued": 3.0 * ach, "issued_frac": 3.0 * ach / peak,
                         "timed_over": "%d steps repeated right after the timed region with an event pair around each launch (%.3f ms per step there)" % (args.steps, instrumented_ms),
                         "peak_source": "%s bf16 sustained (fp16 inputs run at the same rate); achieved/frac count algorithmic flops, issued/issued_frac the three fp16 products 3xFP16 spends per multiply-add (what the tensor-pipe counter sees)" % peak_kind,

@@ -11,6 +11,7 @@ CPU oracle (float64) on the same seeded inputs.  Tolerances for floating point:
   roundoff of the tensor's largest element: outputs that are differences of O(max) quantities);
 * indices and masks bit-exact."""
 import ctypes
+import os
 
 import numpy as np
 import pytest
@@ -778,3 +779,53 @@ def test_batchnorm_output_statistics_at_full_size(env):
     yn = y.asnumpy().astype(np.float64)
     assert np.abs(yn.mean(axis=0)).max() < 1e-5
     assert np.abs(yn.var(axis=0) - 1.0).max() < 1e-3     # var/(var+eps) with eps 1e-5 and var ~ 9
+
+
+_SPLIT_WORKER = r"""
+import sys, numpy as np
+from tinyflow_b200 import gpu_op, ndarray
+ctx = ndarray.gpu(0)
+stream = gpu_op.create_cudaStream(); cudnn = gpu_op.create_cudnnHandle(stream)
+rng = np.random.RandomState(5)
+out = {}
+for i, (N, C, H, W, K, R, S, pad) in enumerate([(64, 256, 14, 14, 256, 3, 3, "SAME"), (64, 64, 28, 28, 96, 3, 3, "SAME"), (32, 512, 7, 7, 2048, 1, 1, "VALID"), (16, 192, 17, 17, 224, 1, 7, "SAME")]):
+    x = rng.randn(N, C, H, W).astype(np.float32); w = (0.1 * rng.randn(K, C, R, S)).astype(np.float32)
+    shape, cell = gpu_op.convolution_2d_forward_get_out_shape(x.shape, w.shape, "NCHW", pad, 1, 1)
+    dy = rng.randn(*shape).astype(np.float32)
+    xd, wd, dyd = ndarray.array(x, ctx), ndarray.array(w, ctx), ndarray.array(dy, ctx)
+    y, dx, dw = ndarray.empty(shape, ctx), ndarray.empty(x.shape, ctx), ndarray.empty(w.shape, ctx)
+    gpu_op.set_contraction_path(2)
+    for rep in range(2):
+        gpu_op.convolution_2d_forward(xd, wd, y, cell, cudnn, stream)
+        gpu_op.convolution_backward_data(xd, dyd, wd, dx, cell, cudnn, stream)
+        gpu_op.convolution_backward_filter(xd, dyd, wd, dw, cell, cudnn, stream)
+        got = (y.asnumpy(), dx.asnumpy(), dw.asnumpy())
+        if rep:
+            for a, b in zip(got, first):
+                assert np.array_equal(a, b), "two launches on the same operands disagree"
+        first = got
+    out["y%d" % i], out["dx%d" % i], out["dw%d" % i] = got
+np.savez(sys.argv[1], **out)
+"""
+
+
+def test_split_reductions_give_the_same_bits_every_time_and_both_ways_of_adding_agree(env, tmp_path):
+    """The last, partial wave of tiles is cut into per-CTA pieces whose partial sums are added in a fixed order - inside the
+    GEMM by whichever warp delivers the last piece, or by a second kernel when a tile has many pieces.  Two processes
+    must produce the same bits; forcing the second kernel everywhere (TINYFLOW_TAIL_FINISH_PIECES=0) changes only the
+    order of the final adds, i.e. the last bit or two."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = []
+    for tag, extra in (("a", {}), ("b", {}), ("second_kernel", {"TINYFLOW_TAIL_FINISH_PIECES": "0"})):
+        path = str(tmp_path / ("%s.npz" % tag))
+        envv = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""), **extra)
+        r = subprocess.run([sys.executable, "-c", _SPLIT_WORKER, path], env=envv, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+        files.append(np.load(path))
+    a, b, c = files
+    for k in a.files:
+        np.testing.assert_array_equal(a[k], b[k], err_msg="%s differs between two processes" % k)
+        scale = float(np.abs(a[k]).max())
+        assert float(np.abs(a[k].astype(np.float64) - c[k]).max()) <= 4e-6 * scale, "%s: in-kernel and second-kernel sums differ by more than rounding" % k

@@ -144,7 +144,7 @@ struct FRecip { __device__ float operator()(float x) const { return 1.f / x; } }
 struct FPow { float p; __device__ float operator()(float x) const { return powf(x, p); } };
 struct FSigmoid { __device__ float operator()(float x) const { return 1.f / (1.f + expf(-x)); } };
 struct FTanh { __device__ float operator()(float x) const { return tanhf(x); } };
-struct FAdd { __device__ float operator()(float a, float b) const { return a + b; } };
+struct FAdd { __device__ float operator()(float a, float b) const { return a + b; } };   // no max|y| on the side: the reduction costs the 36 sums of a ResNet-50 step what the 12 more fused ReLU packs it enables save
 struct FMul { __device__ float operator()(float a, float b) const { return a * b; } };
 struct FReluGrad { static constexpr bool kTrackAmax = true; __device__ float operator()(float x, float g) const { return x > 0.f ? g : 0.f; } };
 struct FSgd { static constexpr bool kTrackAmax = true; float lr; __device__ float operator()(float w, float g) const { return w - lr * g; } };
