@@ -829,3 +829,53 @@ def test_split_reductions_give_the_same_bits_every_time_and_both_ways_of_adding_
         np.testing.assert_array_equal(a[k], b[k], err_msg="%s differs between two processes" % k)
         scale = float(np.abs(a[k]).max())
         assert float(np.abs(a[k].astype(np.float64) - c[k]).max()) <= 4e-6 * scale, "%s: in-kernel and second-kernel sums differ by more than rounding" % k
+
+
+_PAIR_WORKER = r"""
+import sys, json, ctypes, numpy as np
+from tinyflow_b200 import gpu_op, ndarray
+from tinyflow_b200._base import _LIB
+ctx = ndarray.gpu(0)
+stream = gpu_op.create_cudaStream(); cudnn = gpu_op.create_cudnnHandle(stream)
+cases = json.loads(sys.argv[2])
+rng = np.random.RandomState(9)
+out = {}
+_LIB.TfKernelTimingEnable(2)
+gpu_op.set_contraction_path(2)
+for i, (N, C, H, W, K, R, S, pad) in enumerate(cases):
+    x = rng.randn(N, C, H, W).astype(np.float32); w = (0.2 * rng.randn(K, C, R, S)).astype(np.float32)
+    shape, cell = gpu_op.convolution_2d_forward_get_out_shape(x.shape, w.shape, "NCHW", pad, 1, 1)
+    dy = rng.randn(*shape).astype(np.float32)
+    xd, wd, dyd = ndarray.array(x, ctx), ndarray.array(w, ctx), ndarray.array(dy, ctx)
+    y, dx = ndarray.empty(shape, ctx), ndarray.empty(x.shape, ctx)
+    gpu_op.convolution_2d_forward(xd, wd, y, cell, cudnn, stream)
+    gpu_op.convolution_backward_data(xd, dyd, wd, dx, cell, cudnn, stream)
+    out["x%d" % i], out["w%d" % i], out["dy%d" % i], out["y%d" % i], out["dx%d" % i] = x, w, dy, y.asnumpy(), dx.asnumpy()
+buf = ctypes.create_string_buffer(1 << 16)
+_LIB.TfKernelTimingReport(buf, len(buf))
+out["kernels"] = np.array([r["name"] for r in json.loads(buf.value.decode() or "[]")])
+np.savez(sys.argv[1], **out)
+"""
+
+
+def test_cta_pair_kernel_matches_the_oracle(env, tmp_path):
+    """TINYFLOW_PAIRS=2 sends every 128-column convolution (forward and backward-data) through the cta_group::2 kernel:
+    clusters of two CTAs, each loading half of the B tile, one MMA stream for both SMs.  Same bound as the one-CTA
+    kernel, including an odd number of 128-row tiles (the second CTA of the last pair has nothing to store) and output
+    widths that are not multiples of 128."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cases = [(4, 128, 14, 14, 256, 3, 3, "SAME"), (8, 256, 9, 9, 128, 1, 1, "VALID"), (3, 64, 20, 20, 384, 3, 3, "SAME"), (4, 192, 8, 8, 320, 1, 3, "SAME")]
+    path = str(tmp_path / "pairs.npz")
+    envv = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""), TINYFLOW_PAIRS="2", TINYFLOW_TIMING_DETAIL="1")
+    r = subprocess.run([sys.executable, "-c", _PAIR_WORKER, path, json.dumps(cases)], env=envv, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    got = np.load(path)
+    assert any("pairs" in str(k) for k in got["kernels"]), "the pair kernel did not run: %s" % list(got["kernels"])
+    for i, (N, C, H, W, K, R, S, pad) in enumerate(cases):
+        x64, w64, dy64 = got["x%d" % i].astype(np.float64), got["w%d" % i].astype(np.float64), got["dy%d" % i].astype(np.float64)
+        g = env.ops.conv_geometry(x64.shape, w64.shape, pad, 1, 1)
+        close_dot(got["y%d" % i], env.ops.conv2d_fwd(x64, w64, g), env.ops.conv2d_fwd(np.abs(x64), np.abs(w64), g), what="pairs fwd %s" % (cases[i],))
+        close_dot(got["dx%d" % i], env.ops.conv2d_dgrad(dy64, w64, g), env.ops.conv2d_dgrad(np.abs(dy64), np.abs(w64), g), what="pairs dgrad %s" % (cases[i],))

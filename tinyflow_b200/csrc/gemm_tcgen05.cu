@@ -224,6 +224,52 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster on neighbouring SMs compute one 256-row tile; each loads its own 128
+// rows of A and HALF of the B tile, and the tensor cores of both SMs read both halves.  All of the pair's loads report to
+// the barrier of the pair's first CTA (rank 0), whose MMA warp issues for both.
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory object in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t smem_of_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_at(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// tiled load into this CTA's shared memory whose bytes are counted by the barrier at `bar_cluster_addr` (any CTA of the pair)
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr) : "memory");
+}
+// arrives, once the MMAs issued so far have completed, on the barrier at this shared-memory offset in BOTH CTAs of the
+// pair: one commit per CTA, each naming that CTA's barrier by its cluster address
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar) {
+  const uint32_t local = smem_u32(bar);
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_of_cta(local, 0)) : "memory");
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_of_cta(local, 1)) : "memory");
+}
+template <int AR>
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (AR == kArithF16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  }
+}
+
 // Shared-memory matrix descriptor, descriptor version 1 (Blackwell), 128-byte swizzle:
 //   K-major operand : rows of 128 B (64 halves / 32 floats of K), 16-byte atoms (layout type 2), 8-row groups 1024 B
 //                     apart (SBO); LBO unused (= 16 B); one MMA advances the start address by 32 B.
@@ -505,11 +551,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3x_kernel(const __grid_consta
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (lane == 0) {
-      // The B stage holds [B_hi ; B_lo] back to back, so ONE instruction with N = 2*BN computes A_hi*B_hi (columns
-      // 0..BN-1) and A_hi*B_lo (columns BN..2BN-1); a second one with N = BN adds A_lo*B_hi to the second block.  The
-      // two small cross terms share a block on purpose: every accumulation into TMEM truncates the sum, an error
-      // proportional to the accumulator's magnitude, and the cross terms are 2^-11 of the main one, so the large
-      // accumulator sees one truncation per K step instead of two.
+      // The B stage holds the two B tiles back to back ([B_lo ; B_hi] in the default accumulator layout 2), so ONE
+      // instruction with N = 2*BN computes A_hi*B_lo (TMEM columns 0..BN-1) and A_hi*B_hi (columns BN..2BN-1); a second
+      // one with N = BN adds A_lo*B_hi to the first block.  The two small cross terms share a block on purpose: every
+      // accumulation into TMEM truncates the sum, an error proportional to the accumulator's magnitude, and the cross
+      // terms are 2^-11 of the main one, so the large accumulator sees one truncation per K step instead of two.
       // instruction descriptor: D = f32 (bits 4-5 = 1), A format at bit 7, B format at bit 10, majors at bits 15 / 16,
       // N >> 3 at bit 17, M >> 4 at bit 24
       const uint32_t idesc_base = (1u << 4) | (T::kFormat << 7) | (T::kFormat << 10) | ((uint32_t)p.a_mn << 15) | ((uint32_t)p.b_mn << 16) |
@@ -726,6 +772,212 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3x_kernel(const __grid_consta
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same product on CTA pairs.  A cluster of two CTAs owns one 256 x 128 tile: CTA r loads rows [128 r, 128 r + 128)
+// of A and rows [64 r, 64 r + 64) of the B tile (hi and lo each), so a stage is 48 KB per CTA instead of 64 KB - the
+// operand traffic from L2, which is what bounds the one-CTA kernel, drops to three quarters per multiply - and four
+// stages fit.  Rank 0's MMA warp issues three instructions of M = 256, N = 128 per K step for both SMs (A_hi B_hi into
+// block 1; A_hi B_lo and A_lo B_hi into block 0: the N = 2 BN trick of the one-CTA kernel does not carry over, because
+// a pair instruction takes the first half of its N columns from rank 0's shared memory and the second from rank 1's,
+// which would interleave the blocks).  Each CTA's epilogue warps read their own 128 TMEM lanes.  K-major operands,
+// whole tiles only (no split tail); every wait is bounded as in the one-CTA kernel, and both CTAs meet at a cluster
+// barrier before either gives its shared memory and TMEM back.
+// ------------------------------------------------------------------------------------------------
+struct PairLayout {
+  static constexpr int kBN = 128, kHalfN = 64, kStages = 4;
+  static constexpr int kABytes = BM * 128, kBBytes = kHalfN * 128;
+  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;      // per CTA: 48 KiB
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;
+};
+
+template <int AR>
+__global__ void __launch_bounds__(kThreads, 1) gemm3x_pair_kernel(const __grid_constant__ GemmParams p) {
+  using T = Arith<AR>;
+  using L = PairLayout;
+  constexpr int BN = L::kBN;
+  constexpr int BK = T::kBK;
+  constexpr int kTmemCols = 512;                            // two accumulator sets of 2*BN fp32 columns
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kStages * L::kStageBytes);      // used in rank 0 only
+  uint64_t* empty = full + L::kStages;
+  uint64_t* acc_full = empty + L::kStages;
+  uint64_t* acc_empty = acc_full + 2;                                                    // used in rank 0 only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int pair_m_tiles = (p.m_tiles + 1) >> 1;
+  const int pair_tiles = pair_m_tiles * p.n_tiles * p.tap_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 16); }    // 8 epilogue warps of each CTA
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // one warp of each CTA, same destination offset: the allocation spans both SMs
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();       // the peer's barriers exist before anything is sent to them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  grid_dep_sync();
+
+  auto decode = [&](int tile, int& mt, int& nt, int& tap) {
+    nt = tile % p.n_tiles; tile /= p.n_tiles;
+    tap = tile % p.tap_tiles;
+    mt = 2 * (tile / p.tap_tiles) + (int)rank;
+  };
+
+  if (warp == 0) {
+    // ===================== TMA producer (both CTAs) =====================
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      int issued = 0;
+      for (int tile = pair; ok && tile < pair_tiles; tile += npairs) {
+        int mt, nt, tap;
+        decode(tile, mt, nt, tap);
+        const int m0 = mt * BM, n0 = nt * BN + (int)rank * L::kHalfN;
+        for (int it = 0; it < p.k_total; ++it) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* st = smem + stage * L::kStageBytes;
+          uint8_t *a_hi = st, *a_lo = st + L::kABytes, *b_hi = st + 2 * L::kABytes, *b_lo = b_hi + L::kBBytes;
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * L::kStageBytes);      // this CTA's bytes and the peer's
+          const uint32_t bar = smem_of_cta(smem_u32(&full[stage]), 0);
+          int a_col, a_row, b_col;
+          if (p.mode == kModeConv) {
+            const int t = it / p.chunks_per_tap, ch = it - t * p.chunks_per_tap;
+            a_col = p.tap_col[t] + ch * BK; a_row = m0 + p.tap_off[t];
+            b_col = p.tap_b[t] * p.b_tap_pitch + ch * BK;
+          } else {
+            a_col = it * BK; a_row = m0; b_col = it * BK;
+          }
+          tma_load_2d_pair(a_hi, &p.a_hi, a_col, a_row, bar);
+          tma_load_2d_pair(a_lo, &p.a_lo, a_col, a_row, bar);
+          tma_load_2d_pair(b_hi, &p.b_hi, b_col, n0, bar);
+          tma_load_2d_pair(b_lo, &p.b_lo, b_col, n0, bar);
+          ++issued;
+          if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      // Rank 0's MMA warp releases stages with arrivals that are sent to both CTAs.  Stay until every stage this CTA
+      // filled has been released, so that no arrival is still on its way when the CTA gives its shared memory back.
+      for (int s = 0; ok && s < L::kStages && s < issued; ++s) {
+        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+        if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer (rank 0 for both SMs) =====================
+    if (lane == 0 && rank == 0) {
+      // instruction descriptor: D = f32, A / B formats, K-major both, N = BN, M = 256 (both CTAs' 128 rows)
+      const uint32_t idesc = (1u << 4) | (T::kFormat << 7) | (T::kFormat << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+      int stage = 0; uint32_t phase = 0;
+      int group = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < pair_tiles; tile += npairs) {
+        for (int it0 = 0; it0 < p.k_total && ok; it0 += p.group_iters, ++group) {
+          const int acc = group & 1;
+          if (!mbar_wait(&acc_empty[acc], ((group >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t d_cross = tmem_base + acc * 2 * BN, d_main = d_cross + BN;
+          const int it1 = min(it0 + p.group_iters, p.k_total);
+          for (int it = it0; it < it1; ++it) {
+            if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+            tcgen05_fence_after();
+            const uint32_t st = smem_u32(smem + stage * L::kStageBytes);
+            const uint32_t a_hi = st, a_lo = st + L::kABytes, b_hi = st + 2 * L::kABytes, b_lo = b_hi + L::kBBytes;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint64_t ah = umma_desc(a_hi + k * 32, 16, 1024, 2), al = umma_desc(a_lo + k * 32, 16, 1024, 2);
+              const uint64_t bh = umma_desc(b_hi + k * 32, 16, 1024, 2), bl = umma_desc(b_lo + k * 32, 16, 1024, 2);
+              const uint32_t accum = (it > it0 || k > 0) ? 1u : 0u;
+              umma_pair<AR>(d_cross, ah, bl, idesc, accum);
+              umma_pair<AR>(d_main, ah, bh, idesc, accum);
+              umma_pair<AR>(d_cross, al, bh, idesc, 1u);
+            }
+            tcgen05_commit_pair(&empty[stage]);      // frees the stage in both CTAs
+            if (++stage == L::kStages) { stage = 0; phase ^= 1; }
+          }
+          if (ok) tcgen05_commit_pair(&acc_full[acc]);
+        }
+      }
+    }
+  } else {
+    // ===================== epilogue: warps 2..9 of both CTAs, each CTA its own 128 rows =====================
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int HC = BN / 2;
+    const int row_in_tile = quarter * 32 + lane;
+    const float inv_scale = (1.f / __ldg(p.a_scale)) * (1.f / __ldg(p.b_scale));
+    const uint32_t acc_empty_rank0 = smem_of_cta(smem_u32(&acc_empty[0]), 0);      // + 8 bytes for set 1
+    int group = 0;
+    bool ok = true;
+    for (int tile = pair; ok && tile < pair_tiles; tile += npairs) {
+      int mt, nt, tap;
+      decode(tile, mt, nt, tap);
+      const int n0 = nt * BN + half * HC;
+      const RowAddr ra = row_address(p, mt, tap, row_in_tile);
+      const bool row_ok = ra.ok && mt < p.m_tiles;
+      const uint32_t col_stride = ra.col_stride;
+      float* const row_out = p.out + ra.base + (long long)n0 * col_stride;
+      const int ncols = max(0, min(HC, p.N - n0));
+      const bool vec_ok = p.epi == kEpiRowMajor && ((ra.base + n0) & 3) == 0;
+      float accv[HC];
+#pragma unroll
+      for (int q = 0; q < HC; ++q) accv[q] = 0.f;
+      for (int it0 = 0; it0 < p.k_total && ok; it0 += p.group_iters, ++group) {
+        const int acc = group & 1;
+        int got = lane == 0 ? (int)mbar_wait(&acc_full[acc], (group >> 1) & 1, abort_flag) : 1;
+        if (__shfl_sync(0xffffffffu, got, 0) == 0) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t t_base = tmem_base + acc * 2 * BN + half * HC + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+        for (int c0 = 0; c0 < HC; c0 += 16) {
+          float v1[16], v2[16];
+          tmem_ld16(t_base + c0, v1);
+          tmem_ld16(t_base + BN + c0, v2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 16; ++q) accv[c0 + q] += v1[q] + v2[q];
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_at(acc_empty_rank0 + 8u * acc);
+      }
+      if (!ok) break;
+      if (!row_ok) continue;
+      if (vec_ok && ncols == HC) {
+        float4* dst = reinterpret_cast<float4*>(row_out);
+#pragma unroll
+        for (int q = 0; q < HC / 4; ++q) dst[q] = make_float4(accv[4 * q] * inv_scale, accv[4 * q + 1] * inv_scale, accv[4 * q + 2] * inv_scale, accv[4 * q + 3] * inv_scale);
+      } else {
+#pragma unroll
+        for (int q = 0; q < HC; ++q)
+          if (q < ncols) row_out[(size_t)((uint32_t)q * col_stride)] = accv[q] * inv_scale;
+      }
+    }
+  }
+
+  // ===================== teardown =====================
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();       // neither CTA's MMAs, commits or remote arrivals are outstanding past this point
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
   if (threadIdx.x == 0 && *abort_flag && p.err) atomicExch(p.err, 1);
 }
@@ -1331,6 +1583,50 @@ template <int BN, int AR> static int launch_gemm(const GemmParams& p, cudaStream
   }
   return 0;
 }
+// CTA-pair launch: 74 clusters of two CTAs, programmatic dependent launch as everywhere else.
+static bool g_pair_attr_done[2] = {false, false};
+template <int AR> static int launch_gemm_pair(const GemmParams& p, cudaStream_t s, double flops, const char* what) {
+  using L = PairLayout;
+  {
+    std::lock_guard<std::mutex> lk(g_tc_mu);
+    if (!g_pair_attr_done[AR]) {
+      TF_CUDA(cudaFuncSetAttribute(gemm3x_pair_kernel<AR>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      g_pair_attr_done[AR] = true;
+    }
+  }
+  TF_REQUIRE(tensor_path_error() == 0, "%s: an earlier tensor-core kernel timed out on a barrier; refusing to launch", what);
+  static const int group_iters = getenv("TINYFLOW_GROUP_ITERS") ? atoi(getenv("TINYFLOW_GROUP_ITERS")) : 0;
+  const_cast<GemmParams&>(p).group_iters = group_iters > 0 ? group_iters : (p.data_by_data ? kGroupItersDataByData : (AR == kArithTF32 ? kGroupItersTF32 : kGroupIters));
+  const int pair_tiles = ((p.m_tiles + 1) / 2) * p.n_tiles * p.tap_tiles;
+  const int pairs = std::min(device_sm_count() / 2, pair_tiles);
+  note_compute_stream(s);
+  static const bool detail = getenv("TINYFLOW_TIMING_DETAIL") != nullptr;
+  static const bool no_dep = getenv("TINYFLOW_NO_DEPENDENT_LAUNCH") != nullptr;
+  char name[192];
+  if (detail) snprintf(name, sizeof(name), "gemm3x%s pairs mode%d M%d N%d ktotal%d pairtiles%d %s", AR == kArithTF32 ? "tf32" : "f16", p.mode, p.M, p.N, p.k_total, pair_tiles, what + 5);
+  KernelTimer kt(detail ? name : (AR == kArithTF32 ? "gemm3xtf32_tcgen05" : "gemm3xf16_tcgen05"), s, flops, 0, 1);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = (size_t)L::kTotal; cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  memset(attrs, 0, sizeof(attrs));
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 2; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attrs; cfg.numAttrs = (no_dep || s == (cudaStream_t)0) ? 1 : 2;
+  TF_CUDA(cudaLaunchKernelEx(&cfg, gemm3x_pair_kernel<AR>, p));
+  TF_AFTER(s, what);
+  return 0;
+}
+// Pairs pay where the one-CTA kernel waits for operands: K-major operands, 128-column tiles, reductions of at least 8
+// stages, and enough 256-row tiles to occupy the 74 pairs.
+static int g_pairs_mode = [] { const char* e = getenv("TINYFLOW_PAIRS"); return e ? atoi(e) : 0; }();
+static bool pairs_wanted(int bn, int m_tiles, int n_tiles, int k_total) {
+  if (g_pairs_mode == 0 || bn != 128) return false;
+  if (g_pairs_mode >= 2) return true;                   // 2: wherever the kernel can run (tests)
+  return k_total >= 8 && ((m_tiles + 1) / 2) * n_tiles >= 60;
+}
 template <int AR> static int launch_gemm_ar(int bn, const GemmParams& p, cudaStream_t s, double flops, const char* what) {
   return bn == 64 ? launch_gemm<64, AR>(p, s, flops, what) : bn == 96 ? launch_gemm<96, AR>(p, s, flops, what) : launch_gemm<128, AR>(p, s, flops, what);
 }
@@ -1694,10 +1990,11 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, i
     rc = make_map(&g.a_hi, ar, act.hi, act.rows, act.cols, act.pitch, BM);
     if (!rc) rc = make_map(&g.a_lo, ar, act.lo, act.rows, act.cols, act.pitch, BM);
   }
-  if (!rc) rc = make_map(&g.b_hi, ar, filt.hi, filt.rows, filt.cols, filt.pitch, bn);
-  if (!rc) rc = make_map(&g.b_lo, ar, filt.lo, filt.rows, filt.cols, filt.pitch, bn);
-  if (rc) return -1;
   const long long m_rows = im ? (long long)im->N * im->box_w * im->box_h : act.rows;      // one GEMM row per output position
+  const bool pairs = !im && pairs_wanted(bn, (int)((m_rows + BM - 1) / BM), (ch_out + bn - 1) / bn, taps.n * ((ch_in + bk - 1) / bk));
+  if (!rc) rc = make_map(&g.b_hi, ar, filt.hi, filt.rows, filt.cols, filt.pitch, pairs ? bn / 2 : bn);      // a pair's CTAs load half a B tile each
+  if (!rc) rc = make_map(&g.b_lo, ar, filt.lo, filt.rows, filt.cols, filt.pitch, pairs ? bn / 2 : bn);
+  if (rc) return -1;
   g.M = (int)m_rows; g.N = ch_out;
   g.m_tiles = (int)((m_rows + BM - 1) / BM); g.n_tiles = (ch_out + bn - 1) / bn; g.tap_tiles = 1;
   g.ntaps = taps.n;
@@ -1709,6 +2006,7 @@ static int conv_like(const Pack& act, const Pack& filt, int ch_in, int ch_out, i
   g.a_scale = act.scale(); g.b_scale = filt.scale();
   g.frame_h = frame_h; g.frame_w = frame_w; g.valid_h = og.valid_h; g.valid_w = og.valid_w;
   g.out_c = ch_out; g.out_h = og.out_h; g.out_w = og.out_w; g.out_sh = og.out_sh; g.out_sw = og.out_sw; g.out_off_h = og.out_off_h; g.out_off_w = og.out_off_w;
+  if (pairs) return ar == kArithTF32 ? launch_gemm_pair<kArithTF32>(g, s, flops, what) : launch_gemm_pair<kArithF16>(g, s, flops, what);
   return launch_gemm_bn(bn, ar, g, s, flops, what, oom);
 }
 static double conv_flops(const ConvPlan* p) { return 2.0 * p->N * p->K * p->P * p->Q * p->C * p->R * p->S; }
