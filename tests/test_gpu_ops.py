@@ -453,6 +453,70 @@ def test_batchnorm(env, shape, mode):
     close(dx.asnumpy(), env.ops.bn_bwd(x64, dy.astype(np.float64), mode), what="bn bwd")
 
 
+@pytest.mark.parametrize("shape", [(64, 16, 28, 28), (32, 24, 17, 17), (8, 64, 56, 56)])
+@pytest.mark.parametrize("mask_is_bn_output", [True, False])
+def test_relu_backward_runs_inside_the_batchnorm_backward_that_follows(env, shape, mask_is_bn_output):
+    """DLGpuActivationBackward(relu) is held back for one call; when DLGpuBatchNormalizationBackward on its output comes
+    next, one kernel writes both gradients.  Both must be bit-identical to the two kernels run one after the other
+    (a synchronising call in between launches the held-back kernel on its own), and within tolerance of the oracle.  The
+    ReLU's mask comes from x-hat when its input is this layer's own forward output, else from the tensor itself."""
+    from tinyflow_b200._base import _LIB
+    x, dy = f32(*shape, scale=2.0) + np.float32(0.3), f32(*shape)
+    mean_p, var_p, cell = env.gpu_op.bn_get_cudnnlist(shape, "NCHW", "pre_activation")
+    xd, dyd = env.dev(x), env.dev(dy)
+    y = env.empty(shape)
+    assert env.gpu_op.bn_forward(xd, y, "pre_activation", 0, mean_p, var_p, cell, env.cudnn, env.stream) == 0
+    if mask_is_bn_output:
+        relu_in = y
+    else:                                   # a residual sum in between: the ReLU reads another tensor
+        relu_in = env.empty(shape)
+        env.gpu_op.matrix_elementwise_add(y, env.dev(f32(*shape)), relu_in, env.stream)
+    relu_out = env.empty(shape)
+    act = env.gpu_op.activation_get_cudnnlist(shape, "NCHW", "relu") if hasattr(env.gpu_op, "activation_get_cudnnlist") else None
+    env.gpu_op.activation_forward(relu_in, relu_out, "relu", act, env.cudnn, env.stream)
+    results = []
+    for fused in (True, False):
+        d_relu, d_bn = env.empty(shape), env.empty(shape)
+        before = env.gpu_op.fused_relu_bn_backward_count()
+        env.gpu_op.activation_backward(relu_in, d_relu, relu_out, dyd, "relu", act, env.cudnn, env.stream)
+        if not fused:
+            assert _LIB.TfDeviceSynchronize() == 0          # any other call launches the held-back kernel
+        assert env.gpu_op.bn_backward(xd, d_relu, d_bn, "pre_activation", mean_p, var_p, cell, env.cudnn, env.stream) == 0
+        assert env.gpu_op.fused_relu_bn_backward_count() - before == (1 if fused else 0)
+        results.append((d_relu.asnumpy(), d_bn.asnumpy()))
+    np.testing.assert_array_equal(results[0][0], results[1][0])
+    np.testing.assert_array_equal(results[0][1], results[1][1])
+    mask_src = relu_in.asnumpy()
+    want_relu = np.where(mask_src > 0, dy, 0).astype(np.float32)
+    np.testing.assert_array_equal(results[0][0], want_relu)
+    close(results[0][1], env.ops.bn_bwd(x.astype(np.float64), want_relu.astype(np.float64), "pre_activation"), what="fused bn bwd")
+
+
+def test_a_held_back_relu_backward_is_visible_to_every_other_reader(env):
+    """The held-back kernel must have run before anything else can look: a copy to the host right after the call, a free
+    of its operand, an unrelated operator on another tensor."""
+    shape = (16, 32, 28, 28)
+    x, dy = f32(*shape), f32(*shape)
+    want = np.where(x > 0, dy, 0).astype(np.float32)
+    act = env.gpu_op.activation_get_cudnnlist(shape, "NCHW", "relu") if hasattr(env.gpu_op, "activation_get_cudnnlist") else None
+    xd, out = env.dev(x), env.empty(shape)
+    # (a) read straight back
+    dx, dyd = env.empty(shape), env.dev(dy)
+    env.gpu_op.activation_backward(xd, dx, out, dyd, "relu", act, env.cudnn, env.stream)
+    np.testing.assert_array_equal(dx.asnumpy(), want)
+    # (b) the gradient operand is freed before anything else happens
+    dx, dyd = env.empty(shape), env.dev(dy)
+    env.gpu_op.activation_backward(xd, dx, out, dyd, "relu", act, env.cudnn, env.stream)
+    del dyd
+    other = env.dev(f32(*shape))
+    np.testing.assert_array_equal(dx.asnumpy(), want)
+    # (c) an unrelated operator overwrites the gradient operand in place right after
+    dx, dyd = env.empty(shape), env.dev(dy)
+    env.gpu_op.activation_backward(xd, dx, out, dyd, "relu", act, env.cudnn, env.stream)
+    env.gpu_op.matrix_elementwise_add(other, other, dyd, env.stream)
+    np.testing.assert_array_equal(dx.asnumpy(), want)
+
+
 # ---- dropout: the mask is bit-exact against the oracle's counter-based generator ------------------------------------
 @pytest.mark.parametrize("p", [0.0, 0.5, 0.3])
 def test_dropout_mask_consistency(env, p):

@@ -44,9 +44,28 @@ struct KernelTimer {
 
 // ---- streams ------------------------------------------------------------------
 // The caller's cell holds a cudaStream_t.  A null cell means the legacy default stream.
-inline cudaStream_t stream_of(void** cell) { return cell ? (cudaStream_t)(*cell) : (cudaStream_t)0; }
+// ---- a ReLU backward held back for one call -------------------------------------------------
+// DLGpuActivationBackward(relu) does not launch at once: the arguments wait here, and if the very next call into the
+// library is the per-activation batch-norm backward that consumes the ReLU's gradient, ONE kernel computes both
+// (reads x and dy once, writes both gradients).  Every other way into the library - stream_of(), which every operator
+// with a stream argument calls first, last_compute_stream(), which the stream-less operators and the copies call, the
+// array free, the synchronising calls - launches the held-back kernel first (flush_deferred), so no caller can observe
+// the difference.  One slot, guarded by a mutex; the fast path is one relaxed load.
+struct DeferredReluBwd { const float* x; const float* dy; float* dx; int64_t n; cudaStream_t stream; };
+extern std::atomic<int> g_deferred_pending;
+void flush_deferred_slow();
+inline void flush_deferred() { if (g_deferred_pending.load(std::memory_order_relaxed)) flush_deferred_slow(); }
+void defer_relu_bwd(const DeferredReluBwd& op);                 // the slot must be empty (flush first)
+bool take_deferred_relu_bwd(const float* dx, int64_t n, DeferredReluBwd* out);   // the held-back op if it writes `dx`; on true the slot stays locked ...
+void release_deferred();                                       // ... until the caller has enqueued the replacement and calls this
+bool deferral_enabled();
+int launch_relu_bwd_now(const DeferredReluBwd& op);       // the plain elementwise kernel, now
+long long fused_relu_bn_bwd_count();
+
+inline cudaStream_t stream_of(void** cell) { flush_deferred(); return cell ? (cudaStream_t)(*cell) : (cudaStream_t)0; }
+inline cudaStream_t stream_of_keep_deferred(void** cell) { return cell ? (cudaStream_t)(*cell) : (cudaStream_t)0; }
 void note_compute_stream(cudaStream_t s);   // remembered so side-stream copies can order after compute
-cudaStream_t last_compute_stream();
+cudaStream_t last_compute_stream();         // launches a held-back kernel first
 
 // ---- write versions -------------------------------------------------------------
 // Every entry point that writes a device array bumps the version of its data pointer; cached
@@ -194,6 +213,8 @@ struct BNPlan {
   float* save_mean;      // library-owned, sized to the statistic count
   float* save_inv;
   int64_t nstat;
+  const float* last_y;   // output of the last forward call and its write version: a ReLU gradient whose mask tensor is
+  uint64_t last_y_version;   // still exactly that output can take its mask from x-hat instead of reading the tensor
 };
 struct DropoutState {
   int kind;

@@ -424,6 +424,14 @@ int dp_adam_step(float* w, const float* m, const float* v, float c1, float c2, f
 static inline const float* F(const DLArrayHandle a) { return (const float*)a->data; }
 static inline float* FM(DLArrayHandle a) { return out_f32(a); }
 
+namespace tf {
+// The elementwise ReLU backward of a held-back call (the output's write version was bumped when the call was recorded).
+int launch_relu_bwd_now(const DeferredReluBwd& op) {
+  return run_map2(op.x, op.dy, op.dx, op.n, op.stream, "DLGpuActivationBackward(relu)", FReluGrad{});
+}
+
+}  // namespace tf
+
 extern "C" {
 
 int DLGpuArraySet(DLArrayHandle arr, float value, void** cudaStream) {
@@ -866,7 +874,13 @@ int DLGpuActivationBackward(const DLArrayHandle input, DLArrayHandle dinput, con
   int64_t n = numel(input);
   switch (activationMode) {
     case 0: return run_map2(F(output), F(doutput), FM(dinput), n, s, "DLGpuActivationBackward(sigmoid)", FSigmoidBwd{});
-    case 1: return run_map2(F(input), F(doutput), FM(dinput), n, s, "DLGpuActivationBackward(relu)", FReluGrad{});
+    case 1:
+      // Held back for one call: if the batch-norm backward that consumes this gradient comes next, one kernel does both.
+      if (deferral_enabled() && n >= (1 << 16)) {
+        defer_relu_bwd(DeferredReluBwd{F(input), F(doutput), FM(dinput), n, s});
+        return 0;
+      }
+      return run_map2(F(input), F(doutput), FM(dinput), n, s, "DLGpuActivationBackward(relu)", FReluGrad{});
     case 2: return run_map2(F(output), F(doutput), FM(dinput), n, s, "DLGpuActivationBackward(tanh)", FTanhBwd{});
     case 3: {
       TensorPlan* p = plan_of<TensorPlan>(cudnnlist, kPlanTensor);

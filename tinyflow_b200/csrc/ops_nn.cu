@@ -494,6 +494,77 @@ __global__ void __launch_bounds__(32 * kBnGroups) bn_pa_bwd_regs_kernel(const fl
   amax_commit(am, amax);
 }
 
+// ReLU backward and the batch-norm backward behind it in one pass: g = (mask > 0 ? dy : 0) is the ReLU's gradient (stored
+// to dg: other consumers of that tensor may exist) and the batch-norm's incoming gradient.  XHAT_MASK: the ReLU's input
+// is this layer's own forward output, which equals x-hat bit for bit (same subtraction and product of the same saved
+// statistics), so the mask tensor is not read at all.
+template <int VEC, bool XHAT_MASK>
+__global__ void __launch_bounds__(32 * kBnGroups) bn_pa_bwd_relu_regs_kernel(const float* __restrict__ x, const float* __restrict__ dy, const float* __restrict__ mask, float* __restrict__ dg, float* __restrict__ dx, const float* __restrict__ save_mean, const float* __restrict__ save_inv, int N, int64_t F, AmaxOut am) {
+  grid_dep_sync();
+  using V = typename VecT<VEC>::type;
+  __shared__ float red[kBnGroups][32][VEC];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t FV = F / VEC;
+  const int64_t fv = (int64_t)blockIdx.x * 32 + tx;
+  const bool live = fv < FV;
+  const V* xv = reinterpret_cast<const V*>(x);
+  const V* gv = reinterpret_cast<const V*>(dy);
+  const V* mv = reinterpret_cast<const V*>(mask);
+  V* dgv = reinterpret_cast<V*>(dg);
+  V* ov = reinterpret_cast<V*>(dx);
+  float m[VEC], inv[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) { m[k] = live ? save_mean[fv * VEC + k] : 0.f; inv[k] = live ? save_inv[fv * VEC + k] : 0.f; }
+  float xh[kBnPerThread][VEC], g[kBnPerThread][VEC];
+#pragma unroll
+  for (int i = 0; i < kBnPerThread; ++i) {
+    const int n = ty + i * kBnGroups;
+    const bool on = live && n < N;
+    V a = {}, b = {}, r = {};
+    if (on) {
+      a = xv[(int64_t)n * FV + fv]; b = gv[(int64_t)n * FV + fv];
+      if (!XHAT_MASK) r = mv[(int64_t)n * FV + fv];
+    }
+    const float* ap = reinterpret_cast<const float*>(&a);
+    const float* bp = reinterpret_cast<const float*>(&b);
+    const float* rp = reinterpret_cast<const float*>(&r);
+    V t;
+    float* tp = reinterpret_cast<float*>(&t);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      xh[i][k] = on ? (ap[k] - m[k]) * inv[k] : 0.f;
+      const float sel = XHAT_MASK ? xh[i][k] : rp[k];
+      g[i][k] = sel > 0.f ? bp[k] : 0.f;
+      tp[k] = g[i][k];
+    }
+    if (on) dgv[(int64_t)n * FV + fv] = t;
+  }
+  float s1[VEC], s2[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int i = 0; i < kBnPerThread; ++i) { a += g[i][k]; b += g[i][k] * xh[i][k]; }
+    s1[k] = a; s2[k] = b;
+  }
+  bn_group_sum<VEC>(s1, red, tx, ty);
+  bn_group_sum<VEC>(s2, red, tx, ty);
+  const float rn = 1.f / (float)N;
+  uint32_t amax = 0;
+#pragma unroll
+  for (int i = 0; i < kBnPerThread; ++i) {
+    int n = ty + i * kBnGroups;
+    if (live && n < N) {
+      V t;
+      float* tp = reinterpret_cast<float*>(&t);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) { tp[k] = inv[k] * (g[i][k] - s1[k] * rn - xh[i][k] * s2[k] * rn); amax = max(amax, amax_bits(tp[k])); }
+      ov[(int64_t)n * FV + fv] = t;
+    }
+  }
+  amax_commit(am, amax);
+}
+
 // Any batch size: three passes over the batch column (the re-reads are served by L2).
 __global__ void __launch_bounds__(128) bn_pa_fwd_loop_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ save_mean, float* __restrict__ save_inv, int N, int64_t F) {
   int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -567,6 +638,18 @@ static void launch_bn_bwd_regs(const float* x, const float* dy, float* dx, const
   else if (F % 4 == 0 && aligned16(x) && aligned16(dy) && aligned16(dx)) launch_dep(bn_pa_bwd_regs_kernel<4>, dim3((unsigned)((F / 4 + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, dy, dx, sm, si, N, F, am);
   else launch_dep(bn_pa_bwd_regs_kernel<1>, dim3((unsigned)((F + 31) / 32)), dim3(32 * kBnGroups), 0, s, x, dy, dx, sm, si, N, F, am);
 }
+// The fused pair (a held-back ReLU backward and this batch-norm backward).  Returns false when the operands do not allow
+// 8-byte vectors; the caller then runs the two kernels one after the other.
+static bool launch_bn_bwd_relu_regs(const float* x, const float* dy, const float* mask, bool xhat_mask, float* dg, float* dx, const float* sm, const float* si, int N, int64_t F, cudaStream_t s) {
+  if (!(F % 2 == 0 && aligned16(x) && aligned16(dy) && aligned16(mask) && aligned16(dg) && aligned16(dx))) return false;
+  AmaxOut am = amax_track_begin(dx);
+  const dim3 grid((unsigned)((F / 2 + 31) / 32)), block(32 * kBnGroups);
+  if (xhat_mask) launch_dep(bn_pa_bwd_relu_regs_kernel<2, true>, grid, block, 0, s, x, dy, mask, dg, dx, sm, si, N, F, am);
+  else launch_dep(bn_pa_bwd_relu_regs_kernel<2, false>, grid, block, 0, s, x, dy, mask, dg, dx, sm, si, N, F, am);
+  return true;
+}
+static std::atomic<long long> g_fused_relu_bn_bwd{0};
+long long fused_relu_bn_bwd_count() { return g_fused_relu_bn_bwd.load(); }
 
 }  // namespace tf
 
@@ -708,6 +791,7 @@ int DLGpuBatchNormalizationForward(const DLArrayHandle input, DLArrayHandle outp
   if (p->mode == 0) {
     int64_t F = p->nstat;
     int N = (int)p->N;
+    p->last_y = y; p->last_y_version = version_of(y);
     if (N <= kBnMaxBatchInRegs) launch_bn_fwd_regs(x, y, p->save_mean, p->save_inv, N, F, s);
     else bn_pa_fwd_loop_kernel<<<(unsigned)((F + 127) / 128), 128, 0, s>>>(x, y, p->save_mean, p->save_inv, N, F);
   } else {
@@ -724,9 +808,32 @@ int DLGpuBatchNormalizationBackward(const DLArrayHandle input, const DLArrayHand
   TF_REQUIRE(p && p->mode == batchNormMode, "DLGpuBatchNormalizationBackward: descriptor / mode mismatch");
   TF_REQUIRE(p->save_mean && p->save_inv, "DLGpuBatchNormalizationBackward: forward has not run for this descriptor");
   TF_REQUIRE(input && doutput && dinput && numel(input) == p->N * p->C * p->HW && numel(doutput) == numel(input) && numel(dinput) == numel(input), "DLGpuBatchNormalizationBackward: arrays do not match the descriptor");
-  cudaStream_t s = stream_of(cudaStream);
   const float* x = (const float*)input->data;
   const float* dy = (const float*)doutput->data;
+  // A ReLU backward that was held back and whose output is this call's incoming gradient runs inside this kernel.
+  DeferredReluBwd relu;
+  const cudaStream_t s_here = stream_of_keep_deferred(cudaStream);
+  if (p->mode == 0 && p->N <= kBnMaxBatchInRegs && take_deferred_relu_bwd((const float*)dy, numel(input), &relu)) {
+    // the slot is locked until release_deferred(): nothing below may call stream_of() / last_compute_stream()
+    bool fused = false;
+    float* dx_f = (float*)dinput->data;
+    if (relu.stream == s_here && dx_f != relu.dx && dx_f != relu.dy && dx_f != relu.x && dx_f != x) {
+      note_write(dx_f);
+      note_compute_stream(s_here);
+      // mask from x-hat when the ReLU's input is still exactly this layer's forward output
+      const bool xhat_mask = relu.x == p->last_y && version_of(relu.x) == p->last_y_version;
+      KernelTimer kt("ReluBackward+BatchNormalizationBackward", s_here, 0, (xhat_mask ? 16.0 : 20.0) * numel(input) + 8.0 * p->nstat);
+      fused = launch_bn_bwd_relu_regs(x, relu.dy, relu.x, xhat_mask, relu.dx, dx_f, p->save_mean, p->save_inv, (int)p->N, p->nstat, s_here);
+    }
+    if (!fused) launch_relu_bwd_now(relu);      // not a shape the fused kernel handles: the ReLU on its own, then as usual
+    release_deferred();
+    if (fused) {
+      g_fused_relu_bn_bwd.fetch_add(1);
+      TF_AFTER(s_here, "DLGpuBatchNormalizationBackward");
+      return 0;
+    }
+  }
+  cudaStream_t s = stream_of(cudaStream);
   float* dx = out_f32(dinput);
   note_compute_stream(s);
   KernelTimer kt("DLGpuBatchNormalizationBackward", s, 0, 12.0 * numel(input) + 8.0 * p->nstat);

@@ -96,7 +96,44 @@ void KernelTimer::end() {
 
 static std::atomic<cudaStream_t> g_compute_stream{(cudaStream_t)0};
 void note_compute_stream(cudaStream_t s) { g_compute_stream.store(s, std::memory_order_relaxed); }
-cudaStream_t last_compute_stream() { return g_compute_stream.load(std::memory_order_relaxed); }
+cudaStream_t last_compute_stream() { flush_deferred(); return g_compute_stream.load(std::memory_order_relaxed); }
+
+// ---- the held-back ReLU backward (see common.h) ------------------------------------------------
+std::atomic<int> g_deferred_pending{0};
+static std::mutex g_deferred_mu;
+static DeferredReluBwd g_deferred;
+bool deferral_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("TINYFLOW_FUSE_RELU_BN_BWD");
+    return (e ? atoi(e) != 0 : true) && getenv("TINYFLOW_SYNC") == nullptr;      // per-operator timing wants every operator launched in its own call
+  }();
+  return on;
+}
+void defer_relu_bwd(const DeferredReluBwd& op) {
+  std::lock_guard<std::mutex> lk(g_deferred_mu);
+  g_deferred = op;
+  g_deferred_pending.store(1, std::memory_order_release);
+}
+// Both ways out of the slot keep the mutex until the kernel that replaces the held-back one is ENQUEUED, and the flag
+// stays up until then: another thread (a swap worker about to copy the ReLU's gradient) that finds the flag up waits on
+// the mutex and so cannot order its own work in front of that kernel.
+bool take_deferred_relu_bwd(const float* dx, int64_t n, DeferredReluBwd* out) {
+  if (!g_deferred_pending.load(std::memory_order_acquire)) return false;
+  g_deferred_mu.lock();
+  if (!g_deferred_pending.load(std::memory_order_relaxed) || g_deferred.dx != dx || g_deferred.n != n) { g_deferred_mu.unlock(); return false; }
+  *out = g_deferred;
+  return true;        // still locked: the caller launches, then calls release_deferred()
+}
+void release_deferred() {
+  g_deferred_pending.store(0, std::memory_order_release);
+  g_deferred_mu.unlock();
+}
+void flush_deferred_slow() {
+  std::lock_guard<std::mutex> lk(g_deferred_mu);
+  if (!g_deferred_pending.load(std::memory_order_relaxed)) return;
+  launch_relu_bwd_now(g_deferred);      // a launch failure is recorded as the thread's last error and surfaces at the next synchronising call
+  g_deferred_pending.store(0, std::memory_order_release);
+}
 
 // ---------------------------------------------------------------------------------
 // Memory pools.  The executor allocates one array per graph node per step and drops
@@ -270,6 +307,7 @@ int DLArrayAlloc(const index_t* shape, index_t ndim_in, DLContext ctx, DLArrayHa
 // src/c_runtime_api.cc:121
 int DLArrayFree(DLArrayHandle handle) {
   if (!handle) return 0;
+  flush_deferred();            // a held-back kernel may read or write this array
   if (handle->data) {
     if (handle->ctx.device_type == kGPU) note_write(handle->data);   // a recycled block is new data
     bool ok = (handle->ctx.device_type == kGPU) ? device_pool(handle->ctx.device_id).free(handle->data)
@@ -284,6 +322,7 @@ int DLArrayFree(DLArrayHandle handle) {
 // src/c_runtime_api.cc:128 — `stream` is NULL (blocking copy) or the address of a cell
 // holding a cudaStream_t (asynchronous copy, then synchronise that stream only).
 int DLArrayCopyFromTo(DLArrayHandle from, DLArrayHandle to, DLStreamHandle stream) {
+  flush_deferred();
   TF_REQUIRE(from && to && from->data && to->data, "DLArrayCopyFromTo: null array");
   size_t bytes = data_bytes(from);
   TF_REQUIRE(bytes == data_bytes(to), "DLArrayCopyFromTo: size mismatch (%zu vs %zu bytes)", bytes, data_bytes(to));
@@ -412,6 +451,7 @@ int TfKernelTimingReport(char* buf, int buflen) {
 }
 
 int TfDeviceSynchronize(void) {
+  flush_deferred();
   TF_CUDA(cudaDeviceSynchronize());
   TF_REQUIRE(tensor_path_error() == 0, "a tensor-core kernel timed out waiting on a barrier (results of that launch are invalid)");
   return 0;

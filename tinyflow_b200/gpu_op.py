@@ -465,6 +465,13 @@ def clear_tensor_path_error():
     check_call(_LIB.TfClearTensorPathError())
 
 
+def fused_relu_bn_backward_count() -> int:
+    """How many ReLU backward calls so far were computed inside the batch-norm backward kernel that was called next."""
+    n = ctypes.c_longlong(0)
+    check_call(_LIB.TfFusedReluBnBackwardCount(ctypes.byref(n)))
+    return n.value
+
+
 def fused_relu_pack_count() -> int:
     """How many ReLU forward calls so far also wrote the packed operand of the convolution that reads their output."""
     n = ctypes.c_longlong(0)
