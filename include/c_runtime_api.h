@@ -307,6 +307,7 @@ int TfKernelTimingReport(char *buf, int buflen);  /* JSON rows {name, launches, 
 int TfLaunchCount(long long *count);      /* kernels launched by this library so far */
 int TfFusedReluPackCount(long long *count); /* ReLU forward calls that also wrote the next convolution's packed operand */
 int TfFusedReluBnBackwardCount(long long *count); /* ReLU backward calls that ran inside the batch-norm backward kernel called next */
+int TfFusedAddReluCount(long long *count);        /* elementwise sums that were computed by the ReLU forward kernel called next */
 int TfSetContractionPath(int path);       /* 0 = auto, 1 = force CUDA-core path, 2 = force tcgen05 path */
 int TfLastContractionPath(void);          /* engine that served this thread's last matmul / convolution: 1 = CUDA cores, 2 = tensor cores */
 /* Arithmetic of the tensor-core path: 0 = 3xFP16 (default; fp16 hi/lo pairs of the operand scaled by a per-tensor

@@ -492,6 +492,37 @@ def test_relu_backward_runs_inside_the_batchnorm_backward_that_follows(env, shap
     close(results[0][1], env.ops.bn_bwd(x.astype(np.float64), want_relu.astype(np.float64), "pre_activation"), what="fused bn bwd")
 
 
+@pytest.mark.parametrize("shape", [(64, 32, 28, 28), (7, 33, 19, 17)])
+def test_a_sum_is_computed_by_the_relu_forward_that_follows(env, shape):
+    """DLGpuMatrixElementwiseAdd is held back for one call; when the ReLU forward of the sum comes next (the end of a
+    residual block) one kernel writes the sum and its ReLU.  Both outputs are exact, the fusion is counted, and a
+    synchronising call in between (or an in-place ReLU) gives the same bits through the two plain kernels."""
+    from tinyflow_b200._base import _LIB
+    a, b = f32(*shape), f32(*shape)
+    act = env.gpu_op.activation_get_cudnnlist(shape, "NCHW", "relu")
+    ad, bd = env.dev(a), env.dev(b)
+    for fused in (True, False):
+        ssum, r = env.empty(shape), env.empty(shape)
+        before = env.gpu_op.fused_add_relu_count()
+        env.gpu_op.matrix_elementwise_add(ad, bd, ssum, env.stream)
+        if not fused:
+            assert _LIB.TfDeviceSynchronize() == 0
+        env.gpu_op.activation_forward(ssum, r, "relu", act, env.cudnn, env.stream)
+        assert env.gpu_op.fused_add_relu_count() - before == (1 if fused else 0)
+        np.testing.assert_array_equal(ssum.asnumpy(), a + b)
+        np.testing.assert_array_equal(r.asnumpy(), np.maximum(a + b, 0))
+    # the ReLU overwrites the sum in place: not fused, still right
+    ssum = env.empty(shape)
+    env.gpu_op.matrix_elementwise_add(ad, bd, ssum, env.stream)
+    env.gpu_op.activation_forward(ssum, ssum, "relu", act, env.cudnn, env.stream)
+    np.testing.assert_array_equal(ssum.asnumpy(), np.maximum(a + b, 0))
+    # a held-back sum is visible to a reader that is not a ReLU
+    ssum, twice = env.empty(shape), env.empty(shape)
+    env.gpu_op.matrix_elementwise_add(ad, bd, ssum, env.stream)
+    env.gpu_op.matrix_elementwise_multiply(ssum, ssum, twice, env.stream)
+    np.testing.assert_array_equal(twice.asnumpy(), (a + b) * (a + b))
+
+
 def test_a_held_back_relu_backward_is_visible_to_every_other_reader(env):
     """The held-back kernel must have run before anything else can look: a copy to the host right after the call, a free
     of its operand, an unrelated operator on another tensor."""

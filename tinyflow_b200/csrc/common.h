@@ -44,23 +44,28 @@ struct KernelTimer {
 
 // ---- streams ------------------------------------------------------------------
 // The caller's cell holds a cudaStream_t.  A null cell means the legacy default stream.
-// ---- a ReLU backward held back for one call -------------------------------------------------
-// DLGpuActivationBackward(relu) does not launch at once: the arguments wait here, and if the very next call into the
-// library is the per-activation batch-norm backward that consumes the ReLU's gradient, ONE kernel computes both
-// (reads x and dy once, writes both gradients).  Every other way into the library - stream_of(), which every operator
-// with a stream argument calls first, last_compute_stream(), which the stream-less operators and the copies call, the
-// array free, the synchronising calls - launches the held-back kernel first (flush_deferred), so no caller can observe
-// the difference.  One slot, guarded by a mutex; the fast path is one relaxed load.
-struct DeferredReluBwd { const float* x; const float* dy; float* dx; int64_t n; cudaStream_t stream; };
+// ---- an elementwise call held back for one call ----------------------------------------------
+// Two operators do not launch at once; their arguments wait in a one-entry slot:
+//  * DLGpuActivationBackward(relu): if the very next call into the library is the per-activation batch-norm backward that
+//    consumes the ReLU's gradient, ONE kernel computes both (reads x and dy once, writes both gradients);
+//  * DLGpuMatrixElementwiseAdd: if the very next call is the ReLU forward of the sum (the end of a residual block), ONE
+//    kernel writes the sum and its ReLU.
+// Every other way into the library - stream_of(), which every operator with a stream argument calls first,
+// last_compute_stream(), which the stream-less operators and the copies call, the array free, the synchronising calls -
+// launches the held-back kernel first (flush_deferred), so no caller can observe the difference.  One slot, guarded by
+// a mutex; the fast path is one relaxed load.
+enum { kDeferReluBwd = 1, kDeferAdd = 2 };
+struct DeferredOp { int kind; const float* a; const float* b; float* out; int64_t n; cudaStream_t stream; };   // relu-bwd: a = the ReLU's input (mask), b = dy
 extern std::atomic<int> g_deferred_pending;
 void flush_deferred_slow();
 inline void flush_deferred() { if (g_deferred_pending.load(std::memory_order_relaxed)) flush_deferred_slow(); }
-void defer_relu_bwd(const DeferredReluBwd& op);                 // the slot must be empty (flush first)
-bool take_deferred_relu_bwd(const float* dx, int64_t n, DeferredReluBwd* out);   // the held-back op if it writes `dx`; on true the slot stays locked ...
-void release_deferred();                                       // ... until the caller has enqueued the replacement and calls this
+void defer_op(const DeferredOp& op);                            // the slot must be empty (flush first)
+bool take_deferred(int kind, const float* out, int64_t n, DeferredOp* op);   // the held-back op if it is of this kind and writes `out`; on true the slot stays locked ...
+void release_deferred();                                        // ... until the caller has enqueued the replacement and calls this
 bool deferral_enabled();
-int launch_relu_bwd_now(const DeferredReluBwd& op);       // the plain elementwise kernel, now
+int launch_deferred_now(const DeferredOp& op);                  // the plain elementwise kernel, now
 long long fused_relu_bn_bwd_count();
+long long fused_add_relu_count();
 
 inline cudaStream_t stream_of(void** cell) { flush_deferred(); return cell ? (cudaStream_t)(*cell) : (cudaStream_t)0; }
 inline cudaStream_t stream_of_keep_deferred(void** cell) { return cell ? (cudaStream_t)(*cell) : (cudaStream_t)0; }

@@ -47,6 +47,7 @@ int TfTensorPathError(void) { return tensor_path_error(); }
 int TfClearTensorPathError(void) { tensor_path_error_clear(); return 0; }
 int TfFusedReluPackCount(long long* count) { if (count) *count = fused_relu_pack_count(); return 0; }
 int TfFusedReluBnBackwardCount(long long* count) { if (count) *count = fused_relu_bn_bwd_count(); return 0; }
+int TfFusedAddReluCount(long long* count) { if (count) *count = fused_add_relu_count(); return 0; }
 int TfTensorPathTimeoutProbe(long long limit_cycles, void** cudaStream) { return tensor_path_timeout_probe(limit_cycles, stream_of(cudaStream)); }
 
 int TfSetContractionPath(int path) {

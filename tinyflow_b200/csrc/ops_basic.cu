@@ -425,11 +425,48 @@ static inline const float* F(const DLArrayHandle a) { return (const float*)a->da
 static inline float* FM(DLArrayHandle a) { return out_f32(a); }
 
 namespace tf {
-// The elementwise ReLU backward of a held-back call (the output's write version was bumped when the call was recorded).
-int launch_relu_bwd_now(const DeferredReluBwd& op) {
-  return run_map2(op.x, op.dy, op.dx, op.n, op.stream, "DLGpuActivationBackward(relu)", FReluGrad{});
+// The plain kernel of a held-back call (the output's write version was bumped when the call was recorded).
+int launch_deferred_now(const DeferredOp& op) {
+  if (op.kind == kDeferAdd) return run_map2(op.a, op.b, op.out, op.n, op.stream, "DLGpuMatrixElementwiseAdd", FAdd{});
+  return run_map2(op.a, op.b, op.out, op.n, op.stream, "DLGpuActivationBackward(relu)", FReluGrad{});
 }
-
+// s = a + b and r = relu(s) in one pass (a residual block's sum and the ReLU behind it); max|r| tracked as FRelu does.
+__global__ void __launch_bounds__(kBlock) add_relu_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ sum, float* __restrict__ r, int64_t n, AmaxOut am) {
+  grid_dep_sync();
+  const int64_t nv = n >> 2, stride = (int64_t)gridDim.x * blockDim.x;
+  const float4* a4 = reinterpret_cast<const float4*>(a);
+  const float4* b4 = reinterpret_cast<const float4*>(b);
+  float4* s4 = reinterpret_cast<float4*>(sum);
+  float4* r4 = reinterpret_cast<float4*>(r);
+  const FRelu relu;
+  uint32_t m = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    const float4 x = a4[i], y = b4[i];
+    float4 t, u;
+    t.x = x.x + y.x; t.y = x.y + y.y; t.z = x.z + y.z; t.w = x.w + y.w;
+    u.x = relu(t.x); u.y = relu(t.y); u.z = relu(t.z); u.w = relu(t.w);
+    s4[i] = t;
+    r4[i] = u;
+    m = amax4(m, u);
+  }
+  for (int64_t i = (nv << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float t = a[i] + b[i], u = relu(t);
+    sum[i] = t; r[i] = u;
+    m = max(m, amax_bits(u));
+  }
+  amax_commit(am, m);
+}
+static std::atomic<long long> g_fused_add_relu{0};
+long long fused_add_relu_count() { return g_fused_add_relu.load(); }
+// The ReLU forward of a held-back sum: both in one kernel.  Called with the slot locked (take_deferred succeeded).
+static bool launch_add_relu(const DeferredOp& add, float* r, cudaStream_t s) {
+  if (!(aligned16(add.a) && aligned16(add.b) && aligned16(add.out) && aligned16(r))) return false;
+  note_compute_stream(s);
+  KernelTimer kt("Add+ReluForward", s, 0, 16.0 * add.n);
+  launch_dep(add_relu_kernel, dim3(grid_for(add.n, kBlock, 4)), dim3(kBlock), 0, s, add.a, add.b, add.out, r, add.n, amax_track_begin(r));
+  g_fused_add_relu.fetch_add(1);
+  return true;
+}
 }  // namespace tf
 
 extern "C" {
@@ -677,7 +714,13 @@ int DLGpuReduceSumAllBackward(const DLArrayHandle input, DLArrayHandle output) {
 
 int DLGpuMatrixElementwiseAdd(const DLArrayHandle matA, const DLArrayHandle matB, DLArrayHandle output, void** cudaStream) {
   TF_SAME(matA, matB, "DLGpuMatrixElementwiseAdd"); TF_SAME(matA, output, "DLGpuMatrixElementwiseAdd");
-  return run_map2(F(matA), F(matB), FM(output), numel(output), stream_of(cudaStream), "DLGpuMatrixElementwiseAdd", FAdd{});
+  cudaStream_t s = stream_of(cudaStream);
+  // Held back for one call: if the ReLU forward of this sum comes next, one kernel writes both.
+  if (deferral_enabled() && numel(output) >= (1 << 16)) {
+    defer_op(DeferredOp{kDeferAdd, F(matA), F(matB), FM(output), numel(output), s});
+    return 0;
+  }
+  return run_map2(F(matA), F(matB), FM(output), numel(output), s, "DLGpuMatrixElementwiseAdd", FAdd{});
 }
 int DLGpuMatrixElementwiseAddByConst(const DLArrayHandle input, float val, DLArrayHandle output, void** cudaStream) {
   TF_SAME(input, output, "DLGpuMatrixElementwiseAddByConst");
@@ -838,8 +881,29 @@ int DLGpuActivationGetCudnnlist(const int* input_shapes, const int sizeofshape, 
 int DLGpuActivationForward(const DLArrayHandle input, DLArrayHandle output, int activationMode, void*** cudnnlist, void** cudnnHandle, void** cudaStream) {
   (void)cudnnHandle;
   TF_SAME(input, output, "DLGpuActivationForward");
-  cudaStream_t s = stream_of(cudaStream);
   int64_t n = numel(input);
+  if (activationMode == 1) {
+    // the sum this ReLU reads was held back: one kernel writes the sum and its ReLU
+    DeferredOp add;
+    const cudaStream_t s_here = stream_of_keep_deferred(cudaStream);
+    if (take_deferred(kDeferAdd, F(input), n, &add)) {
+      // the slot is locked until release_deferred(): nothing below may call stream_of() / last_compute_stream()
+      float* r = (float*)output->data;
+      bool fused = false;
+      if (add.stream == s_here && r != add.out && r != add.a && r != add.b) {
+        note_write(r);
+        fused = launch_add_relu(add, r, s_here);
+      }
+      if (!fused) launch_deferred_now(add);
+      release_deferred();
+      if (fused) {
+        tc_note_relu_output(plan_of<TensorPlan>(cudnnlist, kPlanTensor), output->data);
+        TF_AFTER(s_here, "DLGpuActivationForward(relu)");
+        return 0;
+      }
+    }
+  }
+  cudaStream_t s = stream_of(cudaStream);
   switch (activationMode) {
     case 0: return run_map1(F(input), FM(output), n, s, "DLGpuActivationForward(sigmoid)", FSigmoid{});
     case 1: {
@@ -877,7 +941,7 @@ int DLGpuActivationBackward(const DLArrayHandle input, DLArrayHandle dinput, con
     case 1:
       // Held back for one call: if the batch-norm backward that consumes this gradient comes next, one kernel does both.
       if (deferral_enabled() && n >= (1 << 16)) {
-        defer_relu_bwd(DeferredReluBwd{F(input), F(doutput), FM(dinput), n, s});
+        defer_op(DeferredOp{kDeferReluBwd, F(input), F(doutput), FM(dinput), n, s});
         return 0;
       }
       return run_map2(F(input), F(doutput), FM(dinput), n, s, "DLGpuActivationBackward(relu)", FReluGrad{});

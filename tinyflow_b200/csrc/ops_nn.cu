@@ -811,21 +811,21 @@ int DLGpuBatchNormalizationBackward(const DLArrayHandle input, const DLArrayHand
   const float* x = (const float*)input->data;
   const float* dy = (const float*)doutput->data;
   // A ReLU backward that was held back and whose output is this call's incoming gradient runs inside this kernel.
-  DeferredReluBwd relu;
+  DeferredOp relu;
   const cudaStream_t s_here = stream_of_keep_deferred(cudaStream);
-  if (p->mode == 0 && p->N <= kBnMaxBatchInRegs && take_deferred_relu_bwd((const float*)dy, numel(input), &relu)) {
+  if (p->mode == 0 && p->N <= kBnMaxBatchInRegs && take_deferred(kDeferReluBwd, (const float*)dy, numel(input), &relu)) {
     // the slot is locked until release_deferred(): nothing below may call stream_of() / last_compute_stream()
     bool fused = false;
     float* dx_f = (float*)dinput->data;
-    if (relu.stream == s_here && dx_f != relu.dx && dx_f != relu.dy && dx_f != relu.x && dx_f != x) {
+    if (relu.stream == s_here && dx_f != relu.out && dx_f != relu.b && dx_f != relu.a && dx_f != x) {
       note_write(dx_f);
       note_compute_stream(s_here);
       // mask from x-hat when the ReLU's input is still exactly this layer's forward output
-      const bool xhat_mask = relu.x == p->last_y && version_of(relu.x) == p->last_y_version;
+      const bool xhat_mask = relu.a == p->last_y && version_of(relu.a) == p->last_y_version;
       KernelTimer kt("ReluBackward+BatchNormalizationBackward", s_here, 0, (xhat_mask ? 16.0 : 20.0) * numel(input) + 8.0 * p->nstat);
-      fused = launch_bn_bwd_relu_regs(x, relu.dy, relu.x, xhat_mask, relu.dx, dx_f, p->save_mean, p->save_inv, (int)p->N, p->nstat, s_here);
+      fused = launch_bn_bwd_relu_regs(x, relu.b, relu.a, xhat_mask, relu.out, dx_f, p->save_mean, p->save_inv, (int)p->N, p->nstat, s_here);
     }
-    if (!fused) launch_relu_bwd_now(relu);      // not a shape the fused kernel handles: the ReLU on its own, then as usual
+    if (!fused) launch_deferred_now(relu);      // not a shape the fused kernel handles: the ReLU on its own, then as usual
     release_deferred();
     if (fused) {
       g_fused_relu_bn_bwd.fetch_add(1);

@@ -98,30 +98,30 @@ static std::atomic<cudaStream_t> g_compute_stream{(cudaStream_t)0};
 void note_compute_stream(cudaStream_t s) { g_compute_stream.store(s, std::memory_order_relaxed); }
 cudaStream_t last_compute_stream() { flush_deferred(); return g_compute_stream.load(std::memory_order_relaxed); }
 
-// ---- the held-back ReLU backward (see common.h) ------------------------------------------------
+// ---- the held-back elementwise call (see common.h) ----------------------------------------------
 std::atomic<int> g_deferred_pending{0};
 static std::mutex g_deferred_mu;
-static DeferredReluBwd g_deferred;
+static DeferredOp g_deferred;
 bool deferral_enabled() {
   static const bool on = [] {
-    const char* e = getenv("TINYFLOW_FUSE_RELU_BN_BWD");
+    const char* e = getenv("TINYFLOW_DEFER");
     return (e ? atoi(e) != 0 : true) && getenv("TINYFLOW_SYNC") == nullptr;      // per-operator timing wants every operator launched in its own call
   }();
   return on;
 }
-void defer_relu_bwd(const DeferredReluBwd& op) {
+void defer_op(const DeferredOp& op) {
   std::lock_guard<std::mutex> lk(g_deferred_mu);
   g_deferred = op;
   g_deferred_pending.store(1, std::memory_order_release);
 }
 // Both ways out of the slot keep the mutex until the kernel that replaces the held-back one is ENQUEUED, and the flag
-// stays up until then: another thread (a swap worker about to copy the ReLU's gradient) that finds the flag up waits on
-// the mutex and so cannot order its own work in front of that kernel.
-bool take_deferred_relu_bwd(const float* dx, int64_t n, DeferredReluBwd* out) {
+// stays up until then: another thread (a swap worker about to copy the held-back call's output) that finds the flag up
+// waits on the mutex and so cannot order its own work in front of that kernel.
+bool take_deferred(int kind, const float* out, int64_t n, DeferredOp* op) {
   if (!g_deferred_pending.load(std::memory_order_acquire)) return false;
   g_deferred_mu.lock();
-  if (!g_deferred_pending.load(std::memory_order_relaxed) || g_deferred.dx != dx || g_deferred.n != n) { g_deferred_mu.unlock(); return false; }
-  *out = g_deferred;
+  if (!g_deferred_pending.load(std::memory_order_relaxed) || g_deferred.kind != kind || g_deferred.out != out || g_deferred.n != n) { g_deferred_mu.unlock(); return false; }
+  *op = g_deferred;
   return true;        // still locked: the caller launches, then calls release_deferred()
 }
 void release_deferred() {
@@ -131,7 +131,7 @@ void release_deferred() {
 void flush_deferred_slow() {
   std::lock_guard<std::mutex> lk(g_deferred_mu);
   if (!g_deferred_pending.load(std::memory_order_relaxed)) return;
-  launch_relu_bwd_now(g_deferred);      // a launch failure is recorded as the thread's last error and surfaces at the next synchronising call
+  launch_deferred_now(g_deferred);      // a launch failure is recorded as the thread's last error and surfaces at the next synchronising call
   g_deferred_pending.store(0, std::memory_order_release);
 }
 

@@ -472,6 +472,13 @@ def fused_relu_bn_backward_count() -> int:
     return n.value
 
 
+def fused_add_relu_count() -> int:
+    """How many elementwise sums so far were computed inside the ReLU forward kernel that was called next."""
+    n = ctypes.c_longlong(0)
+    check_call(_LIB.TfFusedAddReluCount(ctypes.byref(n)))
+    return n.value
+
+
 def fused_relu_pack_count() -> int:
     """How many ReLU forward calls so far also wrote the packed operand of the convolution that reads their output."""
     n = ctypes.c_longlong(0)
