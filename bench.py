@@ -540,6 +540,12 @@ def main():
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
         dp_identical = bool(torch.equal(lo, hi))
+    dp_stats = None
+    if world > 1:
+        c = [ctypes.c_longlong(0) for _ in range(4)]
+        check_call(_LIB.TfDpStats2(*[ctypes.byref(v) for v in c]))
+        dp_stats = {"bytes_reduced": c[0].value, "allreduces": c[1].value, "update_launches": c[2].value, "early_bucket_closes": c[3].value,
+                    "note": "totals of this rank since TfDpInit (warm-up, timed and instrumented steps)"}
 
     ms = torch.tensor([max(dev_ms, 0.0), wall * 1000.0, e2e_s * 1000.0], dtype=torch.float64, device="cuda:0")
     if dist is not None:
@@ -594,7 +600,7 @@ def main():
                        "dropout": (model.dropout_nodes[0].dropout if model.dropout_nodes else 0.0), "device_ms_per_step": dev_ms / args.steps, "host_ms_per_step": wall_ms / args.steps,
                        "algorithmic_tflop_per_step": flops / 1e12, "final_loss": final_loss, "memory_plan": plan_info,
                        "passive_swap_ins": ex.passive_swap_in, "arithmetic": gpu_op.tensor_arithmetic(),
-                       "dp_weights_identical": dp_identical},
+                       "dp_weights_identical": dp_identical, "dp_stats": dp_stats},
             "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(Xn.nbytes + Yn.nbytes), "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches),
             "clocks": clocks,
