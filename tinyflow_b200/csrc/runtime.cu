@@ -141,12 +141,20 @@ void flush_deferred_slow() {
 // are cached by exact (rounded) size and handed back without touching the driver.
 // Reuse is safe without per-block events because (a) all compute is enqueued on one
 // stream, and (b) copies on any other stream first wait for the compute stream's
-// tail (see DLArrayCopyFromTo).
+// tail (see DLArrayCopyFromTo).  Once a process has shown that it swaps (a host-to-device
+// copy on a side stream was seen), (b) is refined for those copies: every device block
+// records an event on the compute stream when it is freed, and a side-stream copy INTO a
+// recycled block waits for that event - the last possible reader of the block's previous
+// contents - instead of for everything queued at the time of the call, so that a swap-in
+// can run ahead of, and overlap with, the compute queued in front of its consumer.
 // ---------------------------------------------------------------------------------
+static std::atomic<bool> g_side_copies_seen{false};
 struct Pool {
   std::mutex mu;
   std::unordered_map<size_t, std::vector<void*>> free_by_size;
   std::unordered_map<void*, size_t> size_of;   // every block we own, in use or cached
+  struct Freed { cudaEvent_t ev = nullptr; int state = 0; };      // state 1: freed before events were kept, 2: ev marks the free
+  std::unordered_map<void*, Freed> freed;      // device blocks that have been freed at least once
   long long in_use = 0, cached = 0;
   bool host;
   explicit Pool(bool h) : host(h) {}
@@ -163,7 +171,11 @@ struct Pool {
 
   void release_cached_locked() {
     for (auto& kv : free_by_size) {
-      for (void* p : kv.second) { size_of.erase(p); raw_free(p); }
+      for (void* p : kv.second) {
+        auto f = freed.find(p);
+        if (f != freed.end()) { if (f->second.ev) cudaEventDestroy(f->second.ev); freed.erase(f); }
+        size_of.erase(p); raw_free(p);
+      }
       kv.second.clear();
     }
     cached = 0;
@@ -207,10 +219,30 @@ struct Pool {
     std::lock_guard<std::mutex> lk(mu);
     auto it = size_of.find(p);
     if (it == size_of.end()) return false;
+    if (!host) {
+      Freed& f = freed[p];
+      f.state = 1;
+      if (g_side_copies_seen.load(std::memory_order_relaxed)) {
+        if (!f.ev && cudaEventCreateWithFlags(&f.ev, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); f.ev = nullptr; }
+        if (f.ev && cudaEventRecord(f.ev, g_compute_stream.load(std::memory_order_relaxed)) == cudaSuccess) f.state = 2;
+        else cudaGetLastError();
+      }
+    }
     free_by_size[it->second].push_back(p);
     in_use -= (long long)it->second;
     cached += (long long)it->second;
     return true;
+  }
+  // Orders stream s after the last use of block p's previous contents.  0: done (fresh block, or waited on the event of
+  // its last free); 1: not known to this pool, or freed without an event - the caller falls back to the compute tail.
+  int order_after_last_use(void* p, cudaStream_t s) {
+    std::lock_guard<std::mutex> lk(mu);
+    if (size_of.find(p) == size_of.end()) return 1;
+    auto f = freed.find(p);
+    if (f == freed.end()) return 0;                       // never freed: nothing was ever queued on it before this owner
+    if (f->second.state != 2) return 1;
+    if (cudaStreamWaitEvent(s, f->second.ev, 0) != cudaSuccess) { cudaGetLastError(); return 1; }
+    return 0;
   }
 };
 
@@ -343,7 +375,14 @@ int DLArrayCopyFromTo(DLArrayHandle from, DLArrayHandle to, DLStreamHandle strea
   }
   cudaStream_t s = *(cudaStream_t*)stream;
   cudaStream_t cs = last_compute_stream();
-  if (s != cs) {
+  bool ordered = false;
+  if (s != cs && tg && !fg) {
+    // Swap-in: the destination is a pool block nobody reads yet; what has to be over is the last use of the block's
+    // PREVIOUS contents, which the pool marked with an event when the block was freed.
+    g_side_copies_seen.store(true, std::memory_order_relaxed);
+    ordered = device_pool(to->ctx.device_id).order_after_last_use(to->data, s) == 0;
+  }
+  if (s != cs && !ordered) {
     // A side stream (swap traffic): order the copy after the compute enqueued so far, so a
     // tensor being swapped out is fully written and a recycled block is no longer read.
     static thread_local cudaEvent_t ev = nullptr;

@@ -70,24 +70,28 @@ def swapadam(topoorder):
 
 
 class _SwapWorker(threading.Thread):
-    """Executes swap requests (index, to_gpu) for the executor on a side stream, in the order they were
-    submitted.  A reader of a tensor that still has requests queued waits for them (``wait_for``): it must not pick
-    up the device array of a tensor whose swap-out is about to free it."""
+    """Executes the swap requests of ONE direction for the executor on its own side stream, in the order they were
+    submitted.  Two workers (device -> host and host -> device) let the two copy engines run at the same time; a
+    swap-in first waits for the queued swap-out of the same tensor.  A reader of a tensor that still has requests
+    queued waits for them (``wait_for``): it must not pick up the device array of a tensor whose swap-out is about to
+    free it."""
 
-    def __init__(self, executor):
+    def __init__(self, executor, to_gpu, other=None):
         super().__init__(daemon=True)
         self.ex = executor
+        self.to_gpu = to_gpu
+        self.other = other             # the swap-out worker, for the swap-in worker
         self.q = queue.Queue()
         self.stream = None
         self.cond = threading.Condition()
         self.pending = 0
         self.pending_for = {}          # tensor index -> queued or running requests
 
-    def submit(self, wait_ms, index, to_gpu):
+    def submit(self, wait_ms, index):
         with self.cond:
             self.pending += 1
             self.pending_for[index] = self.pending_for.get(index, 0) + 1
-        self.q.put((wait_ms, index, to_gpu))
+        self.q.put((wait_ms, index))
 
     def run(self):
         self.stream = gpu_op.create_cudaStream()
@@ -95,11 +99,13 @@ class _SwapWorker(threading.Thread):
             item = self.q.get()
             if item is None:
                 return
-            wait_ms, index, to_gpu = item
+            wait_ms, index = item
             try:
                 if wait_ms > 0:
                     time.sleep(wait_ms / 1000.0)
-                self.ex._do_swap(index, to_gpu, self.stream)
+                if self.other is not None:
+                    self.other.wait_for(index)        # the tensor's way out has to be complete before its way back
+                self.ex._do_swap(index, self.to_gpu, self.stream)
             finally:
                 with self.cond:
                     self.pending -= 1
@@ -115,6 +121,27 @@ class _SwapWorker(threading.Thread):
         with self.cond:
             while self.pending > 0:
                 self.cond.wait()
+
+
+class _SwapWorkers(object):
+    """The pair of workers behind the executor's swap requests."""
+
+    def __init__(self, executor):
+        self.out = _SwapWorker(executor, False)
+        self.back = _SwapWorker(executor, True, other=self.out)
+        self.out.start()
+        self.back.start()
+
+    def submit(self, wait_ms, index, to_gpu):
+        (self.back if to_gpu else self.out).submit(wait_ms, index)
+
+    def wait_for(self, index):
+        self.out.wait_for(index)
+        self.back.wait_for(index)
+
+    def drain(self):
+        self.out.drain()
+        self.back.drain()
 
 
 class Executor(object):
@@ -191,8 +218,7 @@ class Executor(object):
             self.topo_order[start_node_index].recompute_list.append(tensor_index)
         self.have_plan = bool(swap_list or release_list or recompute_list)
         if swap_list and self._swap_worker is None:
-            self._swap_worker = _SwapWorker(self)
-            self._swap_worker.start()
+            self._swap_worker = _SwapWorkers(self)
 
     def _do_swap(self, index, to_gpu, stream):
         shape = self.node_to_shape_map[self.topo_order[index]]
