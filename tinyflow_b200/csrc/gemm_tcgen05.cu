@@ -303,11 +303,6 @@ struct alignas(64) GemmParams {
   // bit-identical from run to run).
   int full_tiles, tail_tiles, tail_share, slots_per_cta;
   float* workspace;               // [slot][BN columns][128 rows] fp32
-  // non-null: the pieces of a split tile are added up inside this kernel.  One counter per (tail tile, epilogue warp):
-  // every epilogue warp that has written its 32 rows x BN/2 columns of a piece bumps it, and the warp whose bump
-  // completes the count adds that sub-block of every piece, in piece order, and stores the result.  Null: a second
-  // kernel (reduce_partials_kernel) adds them.
-  int* tile_arrivals;
   int chunks_per_tap;             // kModeConv: K stages per tap
   int b_tap_pitch;                // kModeConv: columns per tap in the packed filter
   int ntaps;
@@ -707,57 +702,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm3x_kernel(const __grid_consta
         float* ws = p.workspace + ((size_t)w.slot * BN + half * HC) * BM + row_in_tile;
 #pragma unroll
         for (int q = 0; q < HC; ++q) ws[(size_t)q * BM] = accv[q];
-        if (p.tile_arrivals == nullptr) continue;
-        // Last arriver adds.  Which CTA's warp comes last varies from run to run; what it computes does not: the
-        // pieces are added in the order of the stage ranges they cover.
-        const int t = w.tile - p.full_tiles;
-        const int g_first = (int)(((long long)t * p.k_total) / p.tail_share);
-        const int g_last = (int)((((long long)t + 1) * p.k_total - 1) / p.tail_share);
-        __threadfence();                       // this lane's part of the piece is visible device-wide ...
-        __syncwarp();                          // ... for every lane, before lane 0 announces the warp's arrival
-        int last = 0;
-        if (lane == 0) {
-          int* counter = p.tile_arrivals + t * 8 + (warp - 2);
-          last = atomicAdd(counter, 1) == g_last - g_first;
-          if (last) *counter = 0;              // ready for the next launch (launches on a stream do not overlap here)
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (!last) continue;
-        __threadfence();
-        auto piece_of = [&](int g) -> const float* {
-          const int slot = g * p.slots_per_cta + (t - (int)(((long long)g * p.tail_share) / p.k_total));
-          return p.workspace + ((size_t)slot * BN + half * HC) * BM + row_in_tile;
-        };
-        // 32 columns at a time, four pieces per trip: 128 independent loads in flight, then the adds in piece order
-        constexpr int CW = HC < 32 ? HC : 32;
-#pragma unroll 1
-        for (int c0 = 0; c0 < HC; c0 += CW) {
-          float sum[CW];
-#pragma unroll
-          for (int q = 0; q < CW; ++q) sum[q] = 0.f;
-          int g = g_first;
-#pragma unroll 1
-          for (; g + 3 <= g_last; g += 4) {
-            const float *w0 = piece_of(g) + (size_t)c0 * BM, *w1 = piece_of(g + 1) + (size_t)c0 * BM, *w2 = piece_of(g + 2) + (size_t)c0 * BM, *w3 = piece_of(g + 3) + (size_t)c0 * BM;
-            float v0[CW], v1[CW], v2[CW], v3[CW];
-#pragma unroll
-            for (int q = 0; q < CW; ++q) { v0[q] = __ldcg(w0 + (size_t)q * BM); v1[q] = __ldcg(w1 + (size_t)q * BM); v2[q] = __ldcg(w2 + (size_t)q * BM); v3[q] = __ldcg(w3 + (size_t)q * BM); }
-#pragma unroll
-            for (int q = 0; q < CW; ++q) sum[q] = (((sum[q] + v0[q]) + v1[q]) + v2[q]) + v3[q];
-          }
-#pragma unroll 1
-          for (; g <= g_last; ++g) {
-            const float* w0 = piece_of(g) + (size_t)c0 * BM;
-            float v0[CW];
-#pragma unroll
-            for (int q = 0; q < CW; ++q) v0[q] = __ldcg(w0 + (size_t)q * BM);
-#pragma unroll
-            for (int q = 0; q < CW; ++q) sum[q] += v0[q];
-          }
-#pragma unroll
-          for (int q = 0; q < CW; ++q) sum[q] *= inv_scale;
-          store_cols(sum, c0, std::integral_constant<int, CW>{});
-        }
         continue;
       }
 #pragma unroll
@@ -1473,8 +1417,7 @@ static int* error_word_host() {
   return h;
 }
 int tensor_path_error() { int* h = error_word_host(); return h ? *(volatile int*)h : 0; }
-static void reset_arrival_counters();
-void tensor_path_error_clear() { int* h = error_word_host(); if (h) *(volatile int*)h = 0; reset_arrival_counters(); }
+void tensor_path_error_clear() { int* h = error_word_host(); if (h) *(volatile int*)h = 0; }
 
 int tensor_path_timeout_probe(long long limit_cycles, cudaStream_t s) {
   int* err = error_word();
@@ -1495,35 +1438,10 @@ void set_tensor_arithmetic(int a) { g_arith.store(a, std::memory_order_relaxed);
 // unbalanced and its reductions are long enough to share.
 static float g_tail_gain = [] { const char* e = getenv("TINYFLOW_TAIL_GAIN"); return e ? (float)atof(e) : 0.9f; }();
 static float g_tail_cost = [] { const char* e = getenv("TINYFLOW_TAIL_COST"); return e ? (float)atof(e) : 12.f; }();     // workspace round trip + second kernel, in stages
-static int g_finish_pieces = [] { const char* e = getenv("TINYFLOW_TAIL_FINISH_PIECES"); return e ? atoi(e) : 8; }();   // 0: always the second kernel
-// 8 arrival counters for each of the (fewer than one per SM) tail tiles a launch can have; zero between launches.
-static std::mutex g_arrivals_mu;
-static int* g_arrivals[64] = {nullptr};
-constexpr size_t kArrivalBytes = 1024 * 8 * sizeof(int);
-static int* arrival_counters(cudaStream_t s) {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
-  std::lock_guard<std::mutex> lk(g_arrivals_mu);
-  if (!g_arrivals[dev]) {
-    int* fresh = nullptr;
-    if (cudaMalloc((void**)&fresh, kArrivalBytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-    if (cudaMemsetAsync(fresh, 0, kArrivalBytes, s) != cudaSuccess) { cudaGetLastError(); cudaFree(fresh); return nullptr; }
-    g_arrivals[dev] = fresh;
-  }
-  return g_arrivals[dev];
-}
-// A kernel that gave up on a wait may have left counts behind: start from zero again (called with the device idle,
-// when the error word is cleared).
-static void reset_arrival_counters() {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return; }
-  std::lock_guard<std::mutex> lk(g_arrivals_mu);
-  if (g_arrivals[dev] && cudaMemset(g_arrivals[dev], 0, kArrivalBytes) != cudaSuccess) cudaGetLastError();
-}
 static int plan_schedule(GemmParams& g, int bn, cudaStream_t s, int* oom) {
   const int sms = device_sm_count();
   const int tiles = g.m_tiles * g.n_tiles * g.tap_tiles;
-  g.full_tiles = tiles; g.tail_tiles = 0; g.tail_share = 0; g.slots_per_cta = 0; g.workspace = nullptr; g.tile_arrivals = nullptr;
+  g.full_tiles = tiles; g.tail_tiles = 0; g.tail_share = 0; g.slots_per_cta = 0; g.workspace = nullptr;
   const int rem = tiles % sms;
   static const bool no_split = getenv("TINYFLOW_NO_TAIL_SPLIT") != nullptr;
   if (rem == 0 || g.k_total < 8 || no_split) return 0;
@@ -1538,11 +1456,7 @@ static int plan_schedule(GemmParams& g, int bn, cudaStream_t s, int* oom) {
   const size_t bytes = (size_t)ctas * g.slots_per_cta * bn * BM * sizeof(float);
   g.workspace = (float*)persistent_scratch(1, bytes);
   if (!g.workspace) { if (oom) *oom = bytes > 0x7fffffffu ? 0x7fffffff : (int)bytes; return 1; }
-  // Few pieces per tile: the last CTA to deliver one adds them up itself (a second kernel would cost more than the
-  // sum).  Many pieces (a long reduction cut over most of the GPU, e.g. the first layer's filter gradient with 74
-  // pieces per tile): the wide reduction kernel, which spreads each tile over BN/8 blocks.
-  const int pieces = (g.k_total + share - 1) / share + 1;
-  g.tile_arrivals = pieces <= g_finish_pieces ? arrival_counters(s) : nullptr;
+  (void)s;
   return 0;
 }
 
@@ -1577,7 +1491,7 @@ template <int BN, int AR> static int launch_gemm(const GemmParams& p, cudaStream
   KernelTimer kt(detail ? name : (AR == kArithTF32 ? "gemm3xtf32_tcgen05" : "gemm3xf16_tcgen05"), s, flops, 0, 1);
   launch_dep(gemm3x_kernel<BN, AR>, dim3(grid), dim3(kThreads), (size_t)L::kTotal, s, p);
   TF_AFTER(s, what);
-  if (p.tail_share > 0 && p.tile_arrivals == nullptr) {
+  if (p.tail_share > 0) {
     launch_dep(reduce_partials_kernel<BN>, dim3(p.tail_tiles, BN / kReduceCols), dim3(BM, kReduceWays), 0, s, p);
     TF_AFTER(s, what);
   }
