@@ -40,7 +40,7 @@ WORKLOADS = {
 # a few hundred MB on the device at a time), each layer's three launches weighted by how often the layer occurs in the graph.
 # The full step holds tens of GB and its counters need several replay passes, so it is not captured whole; a layer's
 # operands are the same size either way.  profiles/gemm3x_dram_traffic_resnet50_b64.md has the command and the table.
-CONTRACTION_DRAM_BYTES_PER_LAUNCH = {("resnet50", "3xfp16"): 89.4e6}
+CONTRACTION_DRAM_BYTES_PER_LAUNCH = {("resnet50", "3xfp16"): 89.3e6}
 
 
 def build_model(name, batch=None):
