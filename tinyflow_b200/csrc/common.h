@@ -59,6 +59,7 @@ struct DeferredOp { int kind; const float* a; const float* b; float* out; int64_
 extern std::atomic<int> g_deferred_pending;
 void flush_deferred_slow();
 inline void flush_deferred() { if (g_deferred_pending.load(std::memory_order_relaxed)) flush_deferred_slow(); }
+void flush_deferred_if_uses(const void* data);                  // the array free: only if `data` is an operand of the held-back call
 void defer_op(const DeferredOp& op);                            // the slot must be empty (flush first)
 bool take_deferred(int kind, const float* out, int64_t n, DeferredOp* op);   // the held-back op if it is of this kind and writes `out`; on true the slot stays locked ...
 void release_deferred();                                        // ... until the caller has enqueued the replacement and calls this

@@ -128,6 +128,15 @@ void release_deferred() {
   g_deferred_pending.store(0, std::memory_order_release);
   g_deferred_mu.unlock();
 }
+// Freeing an array only concerns the held-back call if the array is one of its operands.
+void flush_deferred_if_uses(const void* data) {
+  if (!g_deferred_pending.load(std::memory_order_acquire)) return;
+  std::lock_guard<std::mutex> lk(g_deferred_mu);
+  if (!g_deferred_pending.load(std::memory_order_relaxed)) return;
+  if (data != (const void*)g_deferred.a && data != (const void*)g_deferred.b && data != (const void*)g_deferred.out) return;
+  launch_deferred_now(g_deferred);
+  g_deferred_pending.store(0, std::memory_order_release);
+}
 void flush_deferred_slow() {
   std::lock_guard<std::mutex> lk(g_deferred_mu);
   if (!g_deferred_pending.load(std::memory_order_relaxed)) return;
@@ -339,7 +348,7 @@ int DLArrayAlloc(const index_t* shape, index_t ndim_in, DLContext ctx, DLArrayHa
 // src/c_runtime_api.cc:121
 int DLArrayFree(DLArrayHandle handle) {
   if (!handle) return 0;
-  flush_deferred();            // a held-back kernel may read or write this array
+  flush_deferred_if_uses(handle->data);      // a held-back kernel may read or write this array
   if (handle->data) {
     if (handle->ctx.device_type == kGPU) note_write(handle->data);   // a recycled block is new data
     bool ok = (handle->ctx.device_type == kGPU) ? device_pool(handle->ctx.device_id).free(handle->data)
